@@ -1,0 +1,404 @@
+// bf16 GEMM for sm_100a: D[M,N] = A (*) B with fp32 accumulation in tensor memory.
+//
+// One persistent CTA per SM, 256 threads, four roles:
+//   warp 0 (one lane)  TMA producer: cp.async.bulk.tensor tiles -> 128B-swizzled smem ring
+//   warp 1 (one lane)  MMA issuer:   tcgen05.mma kind::f16, 128 x BN x 16 per instruction,
+//                                     accumulator double-buffered in TMEM (2 x BN columns)
+//   warp 2             TMEM allocation / release
+//   warps 4..7         epilogue: tcgen05.ld -> registers -> global (bf16 or fp32,
+//                                 optional accumulate), overlapped with the next tile's MMAs
+//
+// Operand layouts (both bf16):
+//   A "K-major"  : memory [M, K] row-major      A "MN-major": memory [K, M] row-major
+//   B "K-major"  : memory [N, K] row-major      B "MN-major": memory [K, N] row-major
+// so the three training GEMMs need no transposes:
+//   forward  Y  = X W^T      : A K-major (X),   B K-major (W)
+//   dgrad    dX = dY W       : A K-major (dY),  B MN-major (W  [N_out, K_in] = [K_gemm, N_gemm])
+//   wgrad    dW = dY^T X     : A MN-major (dY), B MN-major (X)
+//
+// Replaces the cuBLAS calls behind every nn.Linear of the reference
+// (configs/models/transformer.py:124-177,292).
+#include "gemm.h"
+#include "sm100.cuh"
+
+namespace hb {
+
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;   // 64 bf16 = one 128-byte swizzle row
+constexpr int kUK = 16;   // K of one tcgen05.mma for 16-bit inputs
+constexpr int kThreads = 256;
+constexpr int kGroupM = 16;  // raster: kGroupM row-tiles share the same column sweep
+
+template <int BN>
+struct Cfg {
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // +1024 for alignment
+  static constexpr int kTmemCols = 2 * BN;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int per_group = kGroupM * tiles_n;
+  const int g = tile / per_group;
+  const int first_m = g * kGroupM;
+  const int gsz = min(kGroupM, tiles_m - first_m);
+  const int r = tile - g * per_group;
+  tm = first_m + r % gsz;
+  tn = r / gsz;
+}
+
+template <typename OutT>
+__device__ __forceinline__ void store_chunk(OutT* __restrict__ p, const uint32_t (&v)[32],
+                                            int valid, bool vec_ok, bool accumulate);
+
+template <>
+__device__ __forceinline__ void store_chunk<__nv_bfloat16>(__nv_bfloat16* __restrict__ p,
+                                                           const uint32_t (&v)[32], int valid,
+                                                           bool vec_ok, bool accumulate) {
+  if (valid == 32 && vec_ok) {
+    uint4* p4 = reinterpret_cast<uint4*>(p);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float f[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[i * 8 + j]);
+      if (accumulate) {
+        uint4 old = p4[i];
+        const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 o = __bfloat1622float2(o2[j]);
+          f[2 * j] += o.x;
+          f[2 * j + 1] += o.y;
+        }
+      }
+      uint4 out;
+      out.x = pack_bf16x2(f[0], f[1]);
+      out.y = pack_bf16x2(f[2], f[3]);
+      out.z = pack_bf16x2(f[4], f[5]);
+      out.w = pack_bf16x2(f[6], f[7]);
+      p4[i] = out;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if (j < valid) {
+        float x = __uint_as_float(v[j]);
+        if (accumulate) x += __bfloat162float(p[j]);
+        p[j] = __float2bfloat16_rn(x);
+      }
+    }
+  }
+}
+
+template <>
+__device__ __forceinline__ void store_chunk<float>(float* __restrict__ p, const uint32_t (&v)[32],
+                                                   int valid, bool vec_ok, bool accumulate) {
+  if (valid == 32 && vec_ok) {
+    float4* p4 = reinterpret_cast<float4*>(p);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float4 o = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                             __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+      if (accumulate) {
+        float4 old = p4[i];
+        o.x += old.x;
+        o.y += old.y;
+        o.z += old.z;
+        o.w += old.w;
+      }
+      p4[i] = o;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if (j < valid) {
+        float x = __uint_as_float(v[j]);
+        if (accumulate) x += p[j];
+        p[j] = x;
+      }
+    }
+  }
+}
+
+template <int BN, bool A_MN, bool B_MN, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
+                 const __grid_constant__ CUtensorMap tma_b, OutT* __restrict__ D, int M, int N,
+                 int K, int ldd, int accumulate, int* __restrict__ status) {
+  using C = Cfg<BN>;
+  constexpr int kStages = C::kStages;
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kStages];
+  __shared__ __align__(8) uint64_t bar_empty[kStages];
+  __shared__ __align__(8) uint64_t bar_tfull[2];
+  __shared__ __align__(8) uint64_t bar_tempty[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int tiles_m = (M + kBM - 1) / kBM;
+  const int tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&bar_tfull[s]), 1);
+      mbar_init(smem_u32(&bar_tempty[s]), 4);
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32(&tmem_slot), C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ------------------------------------------------------------ producer
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      const int m0 = tm * kBM, n0 = tn * BN;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1, &abort_flag, status, kTimeoutEmpty);
+        if (!ok) break;
+        const uint32_t full = smem_u32(&bar_full[stage]);
+        const uint32_t sa = smem_base + stage * C::kStageBytes;
+        const uint32_t sb = sa + C::kABytes;
+        mbar_expect_tx(full, C::kStageBytes);
+        const int k0 = kb * kBK;
+        if (!A_MN) {
+          tma_load_2d(sa, &tma_a, full, k0, m0);
+        } else {
+#pragma unroll
+          for (int c = 0; c < kBM / 64; ++c) tma_load_2d(sa + c * 8192, &tma_a, full, m0 + c * 64, k0);
+        }
+        if (!B_MN) {
+          tma_load_2d(sb, &tma_b, full, k0, n0);
+        } else {
+#pragma unroll
+          for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * 8192, &tma_b, full, n0 + c * 64, k0);
+        }
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc = make_idesc_bf16(kBM, BN, A_MN, B_MN);
+    int stage = 0;
+    uint32_t phase = 0;
+    int local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      ok = mbar_wait(smem_u32(&bar_tempty[acc]), acc_phase ^ 1, &abort_flag, status,
+                     kTimeoutTmemEmpty);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t tmem_d = tmem_base + acc * BN;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        ok = mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag, status, kTimeoutFull);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t sa = smem_base + stage * C::kStageBytes;
+        const uint32_t sb = sa + C::kABytes;
+#pragma unroll
+        for (int k = 0; k < kBK / kUK; ++k) {
+          // K-major: 16 k = 32 bytes inside the swizzled row; MN-major: 16 k rows = 2048 bytes
+          const uint64_t da = A_MN ? make_smem_desc(sa + k * 2048, 8192, 1024)
+                                   : make_smem_desc(sa + k * 32, 0, 1024);
+          const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, 8192, 1024)
+                                   : make_smem_desc(sb + k * 32, 0, 1024);
+          umma_bf16(tmem_d, da, db, idesc, (kb | k) != 0);
+        }
+        umma_commit(smem_u32(&bar_empty[stage]));  // frees the smem stage when the MMAs retire
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (ok) umma_commit(smem_u32(&bar_tfull[acc]));  // accumulator ready for the epilogue
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------ epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const bool vec_ok = (ldd % (16 / (int)sizeof(OutT)) == 0) &&
+                        ((reinterpret_cast<uintptr_t>(D) & 15) == 0);
+    int local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      const int m0 = tm * kBM, n0 = tn * BN;
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      ok = mbar_wait(smem_u32(&bar_tfull[acc]), acc_phase, &abort_flag, status, kTimeoutTmemFull);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + c * 32, v);
+        tmem_ld_wait();
+        const int col = n0 + c * 32;
+        if (row < M && col < N) {
+          store_chunk<OutT>(D + static_cast<size_t>(row) * ldd + col, v, min(32, N - col), vec_ok,
+                            accumulate != 0);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[acc]));
+    }
+  }
+
+  if (abort_flag) {
+    // a wait gave up: let copies that are still in flight land before the CTA's
+    // shared memory is handed to someone else
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres);
+  if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess) return nullptr;
+  fn = reinterpret_cast<EncodeTiledFn>(p);
+  return fn;
+}
+
+}  // namespace
+
+// 2-D bf16 tensor map over a row-major [rows, cols] array with leading dimension `ld`
+// (elements), box = [box_rows, box_cols], 128-byte swizzle, zero fill out of range.
+bool make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                       uint64_t ld, uint32_t box_rows, uint32_t box_cols) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+namespace {
+
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+template <int BN, bool A_MN, bool B_MN, typename OutT>
+cudaError_t launch(const GemmArgs& g) {
+  using C = Cfg<BN>;
+  CUtensorMap ta, tb;
+  bool ok;
+  if (!A_MN) ok = make_tmap_bf16_2d(&ta, g.a, g.M, g.K, g.lda, kBM, kBK);
+  else       ok = make_tmap_bf16_2d(&ta, g.a, g.K, g.M, g.lda, kBK, 64);
+  if (!ok) return cudaErrorInvalidValue;
+  if (!B_MN) ok = make_tmap_bf16_2d(&tb, g.b, g.N, g.K, g.ldb, BN, kBK);
+  else       ok = make_tmap_bf16_2d(&tb, g.b, g.K, g.N, g.ldb, kBK, 64);
+  if (!ok) return cudaErrorInvalidValue;
+
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, OutT>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         C::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  const int tiles = ((g.M + kBM - 1) / kBM) * ((g.N + BN - 1) / BN);
+  int grid = tiles < sm_count() ? tiles : sm_count();
+  if (g.max_ctas > 0 && grid > g.max_ctas) grid = g.max_ctas;
+  kern<<<grid, kThreads, C::kSmemBytes, g.stream>>>(ta, tb, static_cast<OutT*>(g.d), g.M, g.N, g.K,
+                                                    g.ldd, g.accumulate ? 1 : 0, g.status);
+  return cudaGetLastError();
+}
+
+template <int BN, typename OutT>
+cudaError_t dispatch_layout(const GemmArgs& g) {
+  if (!g.a_mn_major && !g.b_mn_major) return launch<BN, false, false, OutT>(g);
+  if (!g.a_mn_major && g.b_mn_major) return launch<BN, false, true, OutT>(g);
+  if (g.a_mn_major && g.b_mn_major) return launch<BN, true, true, OutT>(g);
+  return launch<BN, true, false, OutT>(g);
+}
+
+}  // namespace
+
+int gemm_pick_bn(int M, int N) {
+  if (N <= 128) return 128;
+  const int t256 = ((M + kBM - 1) / kBM) * ((N + 255) / 256);
+  // prefer the wide tile once it still fills the machine
+  return (t256 >= sm_count()) ? 256 : 128;
+}
+
+cudaError_t gemm_bf16(const GemmArgs& g) {
+  if (g.M <= 0 || g.N <= 0 || g.K <= 0) return cudaSuccess;
+  // TMA needs 16-byte aligned bases and row strides
+  if ((reinterpret_cast<uintptr_t>(g.a) & 15) || (reinterpret_cast<uintptr_t>(g.b) & 15) ||
+      (g.lda % 8) || (g.ldb % 8))
+    return cudaErrorInvalidValue;
+  const int bn = g.block_n > 0 ? g.block_n : gemm_pick_bn(g.M, g.N);
+  if (bn == 256) {
+    return g.out_f32 ? dispatch_layout<256, float>(g) : dispatch_layout<256, __nv_bfloat16>(g);
+  }
+  return g.out_f32 ? dispatch_layout<128, float>(g) : dispatch_layout<128, __nv_bfloat16>(g);
+}
+
+}  // namespace hb
