@@ -1,0 +1,193 @@
+"""Headline benchmark: Llama-3.2-3B pretraining step (bf16 compute, fp32 master weights and
+AdamW, FSDP over N GPUs of one node), sequence length 4096, 8 sequences per GPU per step
+(global batch 64 at 8 GPUs; weak scaling), synthetic uniform-random tokens, random-init weights.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 5 --warmup 3
+    python bench.py --impl reference ...      # the unmodified reference from baseline/_ref
+
+Rank 0 prints ONE JSON line. `value` is whole-job tokens/s from CUDA-event time (max over
+ranks) of exactly K steps; `e2e` repeats the measurement through the public training API
+with a per-step pinned-host -> device copy of the tokens and a device -> host read of the loss.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MODEL_NAME = "llama-3.2-3b"
+SEQ_LEN = 4096
+SEQS_PER_GPU = 8
+VOCAB = 128256
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
+    ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
+    ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (marks the run invalid)")
+    return ap.parse_args()
+
+
+def init_dist(n_gpus):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world,
+                                device_id=torch.device("cuda", local))
+    if world != n_gpus:
+        raise SystemExit(f"--gpus {n_gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    return rank, world, local
+
+
+def make_batches(n, seqs, seq_len, rank, pinned=True):
+    """n host batches of [seqs, seq_len + 1] uniform-random token ids (seeded per rank)."""
+    import torch
+
+    g = torch.Generator().manual_seed(1234 + rank)
+    out = []
+    for _ in range(n):
+        t = torch.randint(0, VOCAB, (seqs, seq_len + 1), generator=g, dtype=torch.int64)
+        out.append(t.pin_memory() if pinned else t)
+    return out
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    rank, world, local = init_dist(args.gpus)
+    dev = torch.device("cuda", local)
+
+    from halite_b200 import ops
+    from halite_b200.conf import instantiate, load_config
+    from halite_b200.optim import build_optimizer, cycle_scheduler
+    from halite_b200.parallel import ParallelDims, parallelize
+    from halite_b200.projects.common.train_fn import basic_train_step
+    from halite_b200.utils.timing import ClockSampler, DeviceTimer
+    from functools import partial
+
+    C = ops.ext()
+    conf = load_config(os.path.join(ROOT, "configs/models/llama/llama3_2_3b_bench.py"))
+    if args.layers:
+        conf.model.blocks = conf.model.blocks[: args.layers]
+    pd = ParallelDims(dp_replicate=1, dp_shard=world, tp=1, pp=1, world_size=world)
+    pd.build_mesh("cuda")
+    torch.manual_seed(0)
+    with torch.device("meta"):
+        model = instantiate(conf.model)
+    model = parallelize(model, pd, pd, param_dtype="bfloat16", reduce_dtype="float32", device=dev)
+    model.init_weights(dev)
+    model._hb_fsdp.sync_parameters()
+    optimizer = build_optimizer(partial(torch.optim.AdamW, lr=3e-4, betas=(0.9, 0.95), eps=1e-8), model,
+                                weight_decay=0.1)
+    scheduler = cycle_scheduler(optimizer, lr=3e-4, n_iter=10000, warmup=100)
+    model.train()
+
+    seqs, S = args.seqs_per_gpu, args.seq_len
+    W, K = args.warmup, args.steps
+    host = make_batches(W + 2 * K + 2, seqs, S, rank)
+
+    def step(tokens_dev):
+        batch = {"input": tokens_dev[:, :-1], "target": tokens_dev[:, 1:]}
+        return basic_train_step(model, batch, optimizer, scheduler, clip_grad_norm=1.0,
+                                calc_loss_in_model=True)
+
+    # ---- warm-up (untimed)
+    it = iter(host)
+    for _ in range(W):
+        out = step(next(it).to(dev, non_blocking=True))
+    torch.cuda.synchronize()
+    ops.check_status()
+
+    # ---- device-timed region: inputs staged on the device beforehand
+    staged = [next(it).to(dev) for _ in range(K)]
+    C.reset_launch_count()
+    with ClockSampler(local) as clocks:
+        with DeviceTimer() as t:
+            for i in range(K):
+                out = step(staged[i])
+        launches = C.launch_count()
+        ms = t.max_ms()
+        loss_dev = float(out["loss"].item())
+
+        # ---- end-to-end through the public API: H2D of the step's tokens + D2H of its loss
+        with DeviceTimer() as te:
+            for i in range(K):
+                tokens = next(it).to(dev, non_blocking=True)
+                o = step(tokens)
+                _ = float(o["loss"].item())
+        e2e_ms = te.max_ms()
+    ops.check_status()
+
+    tokens_per_step = seqs * S * world
+    value = tokens_per_step * K / (ms / 1e3)
+    e2e = tokens_per_step * K / (e2e_ms / 1e3)
+    n_params = sum(u.numel for u in model._hb_fsdp.units)
+    n_matmul = n_params - model.embedding.embed_weight.numel()   # the embedding lookup is no GEMM
+    flops_per_token = 6 * n_matmul + 6 * len(model.blocks) * S * 3072  # causal attention: 12*L*S*D/2
+    peak_mem = torch.cuda.max_memory_allocated() / 2 ** 30
+    if rank == 0:
+        result = {
+            "metric": "train tokens/s (Llama-3.2-3B FSDP, seq 4096)", "value": value, "unit": "tokens/s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic uniform-random tokens, random-init weights",
+            "impl": "ours",
+            "config": {"model": MODEL_NAME if not args.layers else f"{MODEL_NAME}-{args.layers}layers-INVALID",
+                       "global_batch": seqs * world, "seq_len": S,
+                       "parallelism": f"fsdp{world}", "optimizer": "AdamW fp32 master, clip 1.0",
+                       "l2": "inputs larger than L2 (activations of 32768 tokens/GPU)",
+                       "attention": "torch SDPA core inside packed-QKV op"},
+            "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": e2e_ms / K,
+                    "h2d_bytes_per_step": seqs * (S + 1) * 8, "d2h_bytes_per_step": 4},
+            "gpu_launches": int(launches),
+            "clocks": clocks.summary(),
+            "loss": loss_dev,
+            "mfu_of_measured_sustained": None,
+            "model_tflops_per_gpu": flops_per_token * seqs * S / (ms / K / 1e3) / 1e12,
+            "peak_mem_gib": peak_mem,
+        }
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                peaks = json.load(f)
+            result["mfu_of_measured_sustained"] = result["model_tflops_per_gpu"] / peaks["bf16_tflops_sustained"]
+        except Exception:
+            pass
+        print(json.dumps(result), flush=True)
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        from baseline import reference_bench
+
+        reference_bench.run(args)
+        return
+    run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -191,7 +191,30 @@ def wrap_lazy(val, path):
         return val
     if isinstance(val, (list, tuple, dict, set)):
         return val
-    return Lazy(val, path)
+    return Lazy(val, canonical_path(val, path))
+
+
+_canon_cache: dict = {}
+
+
+def canonical_path(val, fallback: str) -> str:
+    """Name classes and functions by their defining module when that name resolves back to
+    the same object, so `nn.Linear` and `from torch.nn import Linear` record the same target."""
+    if not (isinstance(val, type) or inspect.isfunction(val) or inspect.isbuiltin(val)):
+        return fallback
+    key = id(val)
+    hit = _canon_cache.get(key)
+    if hit is not None and hit[0] is val:
+        return hit[1]
+    path = fallback
+    try:
+        real = object_path(val)
+        if real != fallback and "<locals>" not in real and _try_locate(real) is val:
+            path = real
+    except TypeError:
+        pass
+    _canon_cache[key] = (val, path)
+    return path
 
 
 def unwrap(obj):

@@ -6,6 +6,7 @@
 #include <torch/extension.h>
 
 #include "gemm.h"
+#include "launch_count.h"
 #include "ops.h"
 
 namespace {
@@ -16,6 +17,7 @@ namespace {
   do {                                                                                \
     cudaError_t _e = (expr);                                                          \
     TORCH_CHECK(_e == cudaSuccess, "halite_b200 launch failed: ", cudaGetErrorString(_e)); \
+    hb::launch_counter().fetch_add(1, std::memory_order_relaxed);                          \
   } while (0)
 
 cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
@@ -65,5 +67,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, "bf16 tcgen05 GEMM", py::arg("a"), py::arg("b"), py::arg("out"),
         py::arg("a_mn") = false, py::arg("b_mn") = false, py::arg("accumulate") = false,
         py::arg("block_n") = 0, py::arg("max_ctas") = 0, py::arg("status") = py::none());
+  m.def("launch_count", []() { return hb::launch_counter().load(); },
+        "kernel launches issued through this extension so far");
+  m.def("reset_launch_count", []() { hb::launch_counter().store(0); });
   register_elementwise(m);
 }

@@ -465,6 +465,32 @@ ce_kernel(CEArgs a) {
   }
 }
 
+// Backward of (log-prob of target, entropy) w.r.t. logits, one CTA per row:
+//   d logit_i = scale * [ g_lp * (1[i == t] - p_i) - g_ent * p_i * (log p_i + H) ]
+template <typename T>
+__global__ void __launch_bounds__(kCEThreads)
+logprob_entropy_bwd_kernel(LogprobBwdArgs a) {
+  const long row = blockIdx.x;
+  const T* lg = static_cast<const T*>(a.logits) + row * a.ld;
+  T* dl = static_cast<T*>(a.dlogits) + row * a.ld;
+  const float scale = a.logit_scale * (a.row_scale ? a.row_scale[row] : 1.f);
+  const float lse = a.lse[row];
+  const float H = a.entropy ? a.entropy[row] : 0.f;
+  const int64_t tgt = a.targets[row];
+  const bool ignored = (tgt == a.ignore_index);
+  const float glp = (a.g_logprob && !ignored) ? a.g_logprob[row] : 0.f;
+  const float gen = a.g_entropy ? a.g_entropy[row] : 0.f;
+  const long tl = static_cast<long>(tgt) - a.vocab_start;
+  for (int i = threadIdx.x; i < a.vocab; i += kCEThreads) {
+    const float x = ld_logit<T>(lg, i) * scale;
+    const float logp = x - lse;
+    const float p = __expf(logp);
+    float g = -glp * p - gen * p * (logp + H);
+    if (i == tl) g += glp;
+    st_logit<T>(dl, i, g * scale);
+  }
+}
+
 // ------------------------------------------------------------------ AdamW / norms / casts
 template <bool GRAD_F32>
 __global__ void adamw_kernel(AdamWArgs a, float bc1, float bc2) {
@@ -734,6 +760,15 @@ cudaError_t cross_entropy_fwd(const CEArgs& a, cudaStream_t stream) {
     ce_kernel<float><<<a.rows, kCEThreads, 0, stream>>>(a);
   else
     ce_kernel<__nv_bfloat16><<<a.rows, kCEThreads, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
+cudaError_t logprob_entropy_bwd(const LogprobBwdArgs& a, cudaStream_t stream) {
+  if (a.rows == 0) return cudaSuccess;
+  if (a.logits_f32)
+    logprob_entropy_bwd_kernel<float><<<a.rows, kCEThreads, 0, stream>>>(a);
+  else
+    logprob_entropy_bwd_kernel<__nv_bfloat16><<<a.rows, kCEThreads, 0, stream>>>(a);
   return cudaGetLastError();
 }
 

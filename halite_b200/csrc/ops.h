@@ -59,6 +59,26 @@ struct CEArgs {
 };
 cudaError_t cross_entropy_fwd(const CEArgs& a, cudaStream_t stream);
 
+// Gradient of per-row (log p[target], entropy) w.r.t. the logits; replaces the backward of the
+// reference's Triton entropy kernel (nn/entropy.py:146) and of its log-prob cross entropy.
+struct LogprobBwdArgs {
+  const void* logits = nullptr;
+  bool logits_f32 = false;
+  const int64_t* targets = nullptr;
+  const float* lse = nullptr;        // [rows] from the forward
+  const float* entropy = nullptr;    // [rows] from the forward (needed when g_entropy is set)
+  const float* g_logprob = nullptr;  // [rows] optional upstream gradient of log p[target]
+  const float* g_entropy = nullptr;  // [rows] optional upstream gradient of the entropy
+  const float* row_scale = nullptr;  // [rows] optional 1 / temperature
+  void* dlogits = nullptr;           // may alias logits
+  int rows = 0, vocab = 0;
+  long ld = 0;
+  int64_t ignore_index = -100;
+  float logit_scale = 1.f;
+  int vocab_start = 0;
+};
+cudaError_t logprob_entropy_bwd(const LogprobBwdArgs& a, cudaStream_t stream);
+
 // ---- fused AdamW on a flat fp32 master shard with bf16 (or fp32) gradient, writes the bf16
 // working copy in the same pass. grad_scale_ptr (device) multiplies the gradient
 // (clip coefficient / loss scale); step is the 1-based step count.

@@ -3,6 +3,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include "launch_count.h"
 #include "ops.h"
 
 namespace {
@@ -11,6 +12,7 @@ namespace {
   do {                                                                                     \
     cudaError_t _e = (expr);                                                               \
     TORCH_CHECK(_e == cudaSuccess, "halite_b200 launch failed: ", cudaGetErrorString(_e)); \
+    hb::launch_counter().fetch_add(1, std::memory_order_relaxed);                          \
   } while (0)
 
 cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
@@ -193,6 +195,42 @@ std::vector<at::Tensor> cross_entropy(const at::Tensor& logits,
   return out;
 }
 
+void logprob_entropy_bwd_(const at::Tensor& logits, const at::Tensor& targets, const at::Tensor& lse,
+                          const c10::optional<at::Tensor>& entropy,
+                          const c10::optional<at::Tensor>& g_logprob,
+                          const c10::optional<at::Tensor>& g_entropy,
+                          const c10::optional<at::Tensor>& row_scale, at::Tensor& dlogits,
+                          int64_t ignore_index, double logit_scale, int64_t vocab_start) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1);
+  TORCH_CHECK(logits.scalar_type() == at::kBFloat16 || logits.scalar_type() == at::kFloat);
+  TORCH_CHECK(dlogits.scalar_type() == logits.scalar_type() && dlogits.stride(1) == 1 &&
+              dlogits.stride(0) == logits.stride(0) && dlogits.sizes() == logits.sizes());
+  TORCH_CHECK(targets.is_cuda() && targets.scalar_type() == at::kLong && targets.is_contiguous());
+  check_f32(lse, "lse");
+  c10::cuda::CUDAGuard guard(logits.device());
+  hb::LogprobBwdArgs a;
+  a.logits = logits.data_ptr();
+  a.logits_f32 = logits.scalar_type() == at::kFloat;
+  a.targets = targets.data_ptr<int64_t>();
+  a.lse = lse.data_ptr<float>();
+  if (entropy.has_value()) { check_f32(*entropy, "entropy"); a.entropy = entropy->data_ptr<float>(); }
+  if (g_logprob.has_value()) { check_f32(*g_logprob, "g_logprob"); a.g_logprob = g_logprob->data_ptr<float>(); }
+  if (g_entropy.has_value()) {
+    check_f32(*g_entropy, "g_entropy");
+    TORCH_CHECK(entropy.has_value(), "g_entropy needs the forward entropy");
+    a.g_entropy = g_entropy->data_ptr<float>();
+  }
+  if (row_scale.has_value()) { check_f32(*row_scale, "row_scale"); a.row_scale = row_scale->data_ptr<float>(); }
+  a.dlogits = dlogits.data_ptr();
+  a.rows = (int)logits.size(0);
+  a.vocab = (int)logits.size(1);
+  a.ld = logits.stride(0);
+  a.ignore_index = ignore_index;
+  a.logit_scale = (float)logit_scale;
+  a.vocab_start = (int)vocab_start;
+  HB_CUDA_OK(hb::logprob_entropy_bwd(a, cur_stream()));
+}
+
 void adamw_(at::Tensor& master, at::Tensor& exp_avg, at::Tensor& exp_avg_sq, const at::Tensor& grad,
             const c10::optional<at::Tensor>& param_bf16, double lr, double beta1, double beta2,
             double eps, double weight_decay, int64_t step, double grad_scale,
@@ -298,6 +336,10 @@ void register_elementwise(pybind11::module_& m) {
         py::arg("grad_scale") = 1.0, py::arg("grad_scale_t") = py::none(),
         py::arg("row_scale") = py::none(), py::arg("want_entropy") = false,
         py::arg("vocab_start") = 0);
+  m.def("logprob_entropy_bwd_", &logprob_entropy_bwd_, py::arg("logits"), py::arg("targets"),
+        py::arg("lse"), py::arg("entropy"), py::arg("g_logprob"), py::arg("g_entropy"),
+        py::arg("row_scale"), py::arg("dlogits"), py::arg("ignore_index") = -100,
+        py::arg("logit_scale") = 1.0, py::arg("vocab_start") = 0);
   m.def("adamw_", &adamw_, py::arg("master"), py::arg("exp_avg"), py::arg("exp_avg_sq"),
         py::arg("grad"), py::arg("param_bf16"), py::arg("lr"), py::arg("beta1"), py::arg("beta2"),
         py::arg("eps"), py::arg("weight_decay"), py::arg("step"), py::arg("grad_scale") = 1.0,

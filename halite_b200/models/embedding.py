@@ -1,0 +1,100 @@
+"""Input embeddings (reference: transformers/embedding.py:7-139)."""
+
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+
+class TextEmbedding(nn.Module):
+    def __init__(self, embed_input_ids, dropout=0, embed_init=None, multiplier=None):
+        super().__init__()
+        self.embed_input_ids = embed_input_ids
+        self.dropout = nn.Dropout(dropout)
+        self.embed_init = embed_init
+        self.multiplier = multiplier
+        self.tie_weight_key = "embed_input_ids.weight"
+
+    def init_weights(self):
+        if self.embed_init is not None:
+            self.embed_init(self.embed_input_ids.weight)
+
+    def get_input_embeddings(self):
+        return self.embed_input_ids
+
+    @property
+    def embed_weight(self):
+        return self.embed_input_ids.weight
+
+    def forward(self, input_ids):
+        word = self.embed_input_ids(input_ids)
+        if self.multiplier is not None:
+            word = word * self.multiplier
+        return self.dropout(word)
+
+    def tp_plan(self):
+        return {"embed_input_ids": "vocab"}
+
+
+class MultiModalEmbedding(nn.Module):
+    """Text embedding whose rows at `image_mask_token_id` are replaced by image embeddings."""
+
+    def __init__(self, text_embedding, image_embedding, image_mask_token_id):
+        super().__init__()
+        self.text_embedding = text_embedding
+        self.image_embedding = image_embedding
+        self.image_mask_token_id = image_mask_token_id
+
+    @property
+    def tie_weight_key(self):
+        return "text_embedding." + self.text_embedding.tie_weight_key
+
+    @property
+    def embed_weight(self):
+        return self.text_embedding.embed_weight
+
+    def get_input_embeddings(self):
+        return self.text_embedding.get_input_embeddings()
+
+    def init_weights(self):
+        pass  # children are visited by the model-level walk
+
+    def forward(self, input_ids, images=None):
+        out = self.text_embedding(input_ids)
+        if images is None:
+            return out
+        img = self.image_embedding(images).to(out.dtype)
+        mask = (input_ids == self.image_mask_token_id).unsqueeze(-1).expand_as(out)
+        return out.masked_scatter(mask, img.reshape(-1, out.shape[-1]))
+
+
+class PatchEmbedding(nn.Module):
+    """Image -> patch tokens, by strided convolution or unfold + linear."""
+
+    def __init__(self, in_channels, dim, patch_size, use_conv=True, bias=True, proj_init=None):
+        super().__init__()
+        self.patch_size = patch_size
+        self.use_conv = use_conv
+        self.proj_init = proj_init
+        if use_conv:
+            self.proj = nn.Conv2d(in_channels, dim, patch_size, patch_size, bias=bias)
+        else:
+            self.proj = nn.Linear(in_channels * patch_size * patch_size, dim, bias=bias)
+
+    def init_weights(self):
+        w = self.proj.weight
+        if self.proj_init is not None:
+            self.proj_init(w.view(w.shape[0], -1) if w.dim() > 2 else w)
+        else:
+            nn.init.xavier_uniform_(w.view(w.shape[0], -1))
+        if self.proj.bias is not None:
+            nn.init.zeros_(self.proj.bias)
+
+    def forward(self, images):
+        if self.use_conv:
+            return self.proj(images).flatten(2).transpose(1, 2)
+        p = self.patch_size
+        B, C, H, W = images.shape
+        x = images.unfold(2, p, p).unfold(3, p, p)           # B,C,h,w,p,p
+        x = x.permute(0, 2, 3, 1, 4, 5).reshape(B, (H // p) * (W // p), C * p * p)
+        return self.proj(x)

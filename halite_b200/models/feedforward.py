@@ -1,0 +1,186 @@
+"""Feed-forward blocks and output heads (reference: transformers/feedforward.py:16-225)."""
+
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from halite_b200 import ops
+from halite_b200.models.initialize import init_weights
+from halite_b200.nn.activation import GEGLU, SwiGLU
+from halite_b200.ops.activation import gated_act, gated_act_packed
+
+
+class FusedLinearCrossEntropy(nn.Module):
+    """Head that returns the loss directly: the [tokens, vocab] logits are produced and
+    consumed chunk by chunk (`ops.fused_linear_cross_entropy`)."""
+
+    def __init__(self, linear, linear_init=None, ignore_index=-100, z_loss=0):
+        super().__init__()
+        self.linear = linear
+        self.linear_init = linear_init
+        self.ignore_index = ignore_index
+        self.z_loss = z_loss
+        self.tie_weight_key = "linear.weight"
+
+    def init_weights(self):
+        init_weights(self.linear, self.linear_init)
+
+    def tie_weight(self, weight):
+        self.linear.weight = weight
+
+    @property
+    def weight(self):
+        return self.linear.weight
+
+    def forward(self, input, target=None):
+        if target is None:
+            return ops.linear(input, self.linear.weight, self.linear.bias)
+        losses, z_losses = ops.fused_linear_cross_entropy(
+            input.reshape(-1, input.shape[-1]), self.linear.weight, target.reshape(-1),
+            ignore_index=self.ignore_index, z_loss=self.z_loss)
+        # mean over all positions, as the reference's head does (ignored rows contribute 0)
+        loss = losses.mean()
+        loss_dict = {"cross entropy": loss.detach()}
+        if self.z_loss > 0:
+            z = z_losses.detach().mean()
+            loss_dict["z-loss"] = z
+            loss_dict["cross entropy"] = (losses.detach() - z_losses.detach()).mean()
+        return loss, loss_dict
+
+    def tp_plan(self):
+        return {"linear": "vocab_head"}
+
+
+class VocabParallelLinear(nn.Module):
+    def __init__(self, linear, linear_init=None, scale=None):
+        super().__init__()
+        self.linear = linear
+        self.linear_init = linear_init
+        self.scale = None
+        if scale:
+            self.scale = nn.Parameter(torch.ones(self.linear.out_features))
+        self.tie_weight_key = "linear.weight"
+
+    def init_weights(self):
+        init_weights(self.linear, self.linear_init)
+        if self.scale is not None:
+            nn.init.ones_(self.scale)
+
+    def forward(self, input):
+        out = ops.linear(input, self.linear.weight, self.linear.bias)
+        if self.scale is not None:
+            out = out * self.scale
+        return out
+
+    def tie_weight(self, weight):
+        self.linear.weight = weight
+
+    @property
+    def n_vocab(self):
+        return self.linear.weight.shape[0]
+
+    @property
+    def weight(self):
+        return self.linear.weight
+
+    @property
+    def bias(self):
+        return self.linear.bias
+
+    def tp_plan(self):
+        return {"linear": "vocab_head"}
+
+
+class SequenceParallelWrapper(nn.Module):
+    """Marks a module (the final norm) as running on sequence-sharded activations under TP."""
+
+    def __init__(self, module):
+        super().__init__()
+        self.module = module
+
+    def forward(self, input, residual=None):
+        if residual is not None:
+            return self.module(input + residual)
+        return self.module(input)
+
+    def tp_plan(self):
+        return {"module": "sequence"}
+
+
+class FeedForward(nn.Module):
+    """linear2(act(linear1(x))); with a gated activation, linear1 emits [gate | up]."""
+
+    def __init__(self, linear1, activation, linear2, dropout=0, linear1_init=None, linear2_init=None):
+        super().__init__()
+        self.linear1 = linear1
+        self.activation = activation
+        self.dropout = nn.Dropout(dropout)
+        self.linear2 = linear2
+        self.linear1_init = linear1_init
+        self.linear2_init = linear2_init
+
+    def init_weights(self):
+        init_weights(self.linear1, self.linear1_init)
+        init_weights(self.linear2, self.linear2_init)
+
+    def forward(self, input):
+        out = ops.linear(input, self.linear1.weight, self.linear1.bias)
+        out = self.activation(out)
+        out = self.dropout(out)
+        return ops.linear(out, self.linear2.weight, self.linear2.bias)
+
+    def tp_plan(self):
+        gated = isinstance(self.activation, (SwiGLU, GEGLU))
+        return {"linear1": "colwise_gated" if gated else "colwise", "linear2": "rowwise"}
+
+
+class GatedFeedForward(nn.Module):
+    """linear_out(linear_proj(x) * act(linear_gate(x)))."""
+
+    def __init__(self, linear_proj, linear_gate, activation, linear_out, dropout=0,
+                 linear_proj_init=None, linear_gate_init=None, linear_out_init=None):
+        super().__init__()
+        self.linear_proj = linear_proj
+        self.linear_gate = linear_gate
+        self.activation = activation
+        self.dropout = nn.Dropout(dropout)
+        self.linear_out = linear_out
+        self.linear_proj_init = linear_proj_init
+        self.linear_gate_init = linear_gate_init
+        self.linear_out_init = linear_out_init
+
+    def init_weights(self):
+        init_weights(self.linear_proj, self.linear_proj_init)
+        init_weights(self.linear_gate, self.linear_gate_init)
+        init_weights(self.linear_out, self.linear_out_init)
+
+    def fusable_linears(self):
+        return {"proj_gate": ("linear_proj", "linear_gate")}
+
+    def _act_kind(self):
+        if isinstance(self.activation, nn.SiLU):
+            return "silu"
+        if isinstance(self.activation, nn.GELU) and self.activation.approximate == "tanh":
+            return "gelu_tanh"
+        return None
+
+    def forward(self, input):
+        kind = self._act_kind()
+        fused = getattr(self, "_hb_fused", {}).get("proj_gate")
+        if fused is not None and kind is not None and ops.use_sm100(input):
+            # one GEMM for [up | gate], one pass for act(gate) * up
+            pg = ops.linear(input, fused)
+            out = gated_act_packed(pg, kind, gate_first=False)
+        else:
+            proj = ops.linear(input, self.linear_proj.weight, self.linear_proj.bias)
+            gate = ops.linear(input, self.linear_gate.weight, self.linear_gate.bias)
+            if kind is not None:
+                out = gated_act(gate, proj, kind)
+            else:
+                out = proj * self.activation(gate)
+        out = self.dropout(out)
+        return ops.linear(out, self.linear_out.weight, self.linear_out.bias)
+
+    def tp_plan(self):
+        return {"linear_proj": "colwise", "linear_gate": "colwise", "linear_out": "rowwise"}

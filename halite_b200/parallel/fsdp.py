@@ -1,0 +1,396 @@
+"""Sharded data parallelism on flat per-block buffers (the job FSDP2 does in the reference,
+parallel/fsdp.py:8-60), laid out for a 180 GB GPU.
+
+Each unit (one transformer block, or the root remainder: embedding, final norm, head) owns
+
+* `full_param`  low-precision (bf16) flat buffer holding every parameter of the unit; the
+                module's `nn.Parameter`s are views into it, so linears that read the same
+                input (q|k|v, up|gate) are contiguous and run as ONE GEMM;
+* `full_grad`   reduce-dtype (fp32) flat buffer; wgrad GEMMs accumulate straight into views of
+                it (`param._hb_grad`), other gradients are copied in after the unit's backward;
+* `master`, `exp_avg`, `exp_avg_sq`: fp32 shards (1 / dp_shard of the unit) for the optimizer.
+
+Step schedule: reduce-scatter of a unit's gradient is launched on the communication stream
+the moment the unit's backward ends and overlaps the next unit's backward; after the fused
+AdamW has rewritten the rank's bf16 shard inside `full_param`, one all-gather per unit is
+issued in forward order and each forward waits only for its own unit. Parameters stay
+gathered between forward and backward (no second all-gather): 2 bytes / parameter of HBM
+buys one collective per step instead of two. `reshard_after_forward=True` restores the
+memory-lean schedule.
+
+With dp_replicate > 1 (HSDP) gradient shards are additionally all-reduced across replicas;
+with dp_shard == 1 (DDP) a unit's "shard" is the whole buffer.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Iterable
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from halite_b200.parallel import comm
+
+_ALIGN = 128  # elements: keeps every shard 256-byte aligned in bf16 and 512 in fp32
+
+
+class _UnitBoundary(torch.autograd.Function):
+    """Identity placed on a unit's input: its backward runs after every gradient inside the
+    unit has been produced."""
+
+    @staticmethod
+    def forward(ctx, x, unit):
+        ctx.unit = unit
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        ctx.unit.post_backward()
+        return g, None
+
+
+class FlatUnit:
+    def __init__(self, name, module_params, shard_group, replicate_group, param_dtype, reduce_dtype,
+                 device, comm_stream=None):
+        self.name = name
+        self.shard_group = shard_group
+        self.replicate_group = replicate_group
+        self.ws = dist.get_world_size(shard_group) if shard_group is not None else 1
+        self.rank = dist.get_rank(shard_group) if shard_group is not None else 0
+        self.param_dtype = param_dtype
+        self.reduce_dtype = reduce_dtype
+        self.device = torch.device(device)
+        self.comm_stream = comm_stream
+        # decay parameters first, then no-decay (ndim < 2), so weight decay is a range split
+        decay = [(m, n, p) for (m, n, p) in module_params if p.ndim >= 2]
+        no_decay = [(m, n, p) for (m, n, p) in module_params if p.ndim < 2]
+        self.entries = []   # (module, attr name, param, offset, numel)
+        off = 0
+        for group in (decay, no_decay):
+            for m, n, p in group:
+                off = (off + 7) // 8 * 8          # 16-byte aligned starts (TMA bases)
+                self.entries.append((m, n, p, off, p.numel()))
+                off += p.numel()
+            if group is decay:
+                self.decay_end = off
+        self.numel = off
+        chunk = self.ws * _ALIGN
+        self.padded = max(chunk, (off + chunk - 1) // chunk * chunk)
+        self.shard_numel = self.padded // self.ws
+        self.lo = self.rank * self.shard_numel
+        self.hi = self.lo + self.shard_numel
+
+        self.full_param = torch.zeros(self.padded, dtype=param_dtype, device=self.device)
+        self.full_grad = torch.zeros(self.padded, dtype=reduce_dtype, device=self.device)
+        self.grad_shard = (self.full_grad if self.ws == 1
+                           else torch.zeros(self.shard_numel, dtype=reduce_dtype, device=self.device))
+        self.master = None        # fp32 shard, created by `init_master`
+        self._written = set()
+        self._gather_event = None
+        self._reduce_event = None
+        self._reduce_work = None
+        self._gather_work = None
+        self._backward_done = False
+        self._adopt_params()
+
+    # ------------------------------------------------------------------ parameter views
+    def _adopt_params(self):
+        for m, n, p, off, numel in self.entries:
+            view = self.full_param[off:off + numel].view(p.shape)
+            if p.device.type != "meta":
+                view.copy_(p.detach().to(view.dtype))
+            new_p = nn.Parameter(view, requires_grad=p.requires_grad)
+            new_p._hb_grad = self.full_grad[off:off + numel].view(p.shape)
+            new_p._hb_grad_owner = self
+            new_p._hb_unit_range = (off, numel)
+            # keep initialiser-visible attributes
+            m._parameters[n] = new_p
+
+    def params(self):
+        return [m._parameters[n] for m, n, _, _, _ in self.entries]
+
+    def named_views(self):
+        """[(module, name, offset, numel, shape)] for checkpointing and resharding."""
+        return [(m, n, off, numel, m._parameters[n].shape) for m, n, _, off, numel in self.entries]
+
+    def fused_view(self, module, names):
+        """One [sum(out_features), in_features] view over consecutive linear weights, or None
+        when they are not adjacent in the flat buffer."""
+        found = []
+        for sub in names:
+            lin = getattr(module, sub)
+            if getattr(lin, "bias", None) is not None:
+                return None
+            hit = [(off, numel, m._parameters[n]) for m, n, _, off, numel in self.entries
+                   if m is lin and n == "weight"]
+            if not hit:
+                return None
+            found.append(hit[0])
+        start = found[0][0]
+        cur = start
+        cols = found[0][2].shape[1]
+        rows = 0
+        for off, numel, p in found:
+            if off != cur or p.shape[1] != cols:
+                return None
+            cur += numel
+            rows += p.shape[0]
+        w = self.full_param[start:cur].view(rows, cols)
+        # a leaf that "requires grad" so autograd always visits the wgrad; the gradient
+        # itself goes to the flat buffer through the main-grad protocol
+        w.requires_grad_(any(p.requires_grad for _, _, p in found))
+        w._hb_grad = self.full_grad[start:cur].view(rows, cols)
+        w._hb_grad_owner = self
+        w._hb_members = tuple(p for _, _, p in found)
+        return w
+
+    # ------------------------------------------------------------------ gradient bookkeeping
+    def mark_written(self, param) -> bool:
+        """Called by a wgrad that is about to write `param._hb_grad`; returns True when the
+        buffer already holds this step's partial sum (so the GEMM must accumulate)."""
+        members = getattr(param, "_hb_members", None) or (param,)
+        acc = all(id(p) in self._written for p in members)
+        if not acc and any(id(p) in self._written for p in members):
+            # mixed state (one member written separately): cannot overwrite; caller accumulates
+            # after we zero the unwritten members
+            for p in members:
+                if id(p) not in self._written:
+                    p._hb_grad.zero_()
+            acc = True
+        for p in members:
+            self._written.add(id(p))
+        return acc
+
+    def pre_forward(self):
+        self.wait_gather()
+        self._backward_done = False
+
+    def wait_gather(self):
+        if self._gather_event is not None:
+            torch.cuda.current_stream().wait_event(self._gather_event)
+            self._gather_event = None
+        if self._gather_work is not None:
+            self._gather_work.wait()
+            self._gather_work = None
+
+    def post_backward(self):
+        """Collect stray `.grad`s, zero what was not written, start the gradient reduction."""
+        if self._backward_done:
+            return
+        self._backward_done = True
+        for m, n, _, off, numel in self.entries:
+            p = m._parameters[n]
+            if p.grad is not None:
+                if id(p) in self._written:
+                    p._hb_grad.add_(p.grad.to(self.reduce_dtype))
+                else:
+                    p._hb_grad.copy_(p.grad)
+                    self._written.add(id(p))
+                p.grad = None
+            elif id(p) not in self._written:
+                p._hb_grad.zero_()
+        self._written.clear()
+        self.start_reduce()
+
+    def start_reduce(self):
+        if self.ws == 1 and self.replicate_group is None:
+            return
+        if self.device.type == "cuda" and self.comm_stream is not None:
+            ev = torch.cuda.Event()
+            ev.record()
+            with torch.cuda.stream(self.comm_stream):
+                self.comm_stream.wait_event(ev)
+                self._reduce()
+                self._reduce_event = torch.cuda.Event()
+                self._reduce_event.record()
+        else:
+            self._reduce()
+
+    def _reduce(self):
+        if self.ws > 1:
+            comm.reduce_scatter_flat(self.grad_shard, self.full_grad, self.shard_group, average=True)
+        if self.replicate_group is not None:
+            comm.all_reduce(self.grad_shard, self.replicate_group, average=True)
+
+    def wait_reduce(self):
+        if self._reduce_event is not None:
+            torch.cuda.current_stream().wait_event(self._reduce_event)
+            self._reduce_event = None
+
+    # ------------------------------------------------------------------ optimizer side
+    def init_master(self):
+        """fp32 master copy of this rank's shard, taken from the current low-precision values."""
+        self.master = self.full_param[self.lo:self.hi].float().clone()
+        return self.master
+
+    def param_shard(self):
+        return self.full_param[self.lo:self.hi]
+
+    def decay_split(self):
+        """Element ranges of this rank's shard with / without weight decay:
+        ((lo, hi) decay, (lo, hi) no-decay) in shard coordinates."""
+        d_hi = min(max(self.decay_end - self.lo, 0), self.shard_numel)
+        return (0, d_hi), (d_hi, self.shard_numel)
+
+    def start_gather(self):
+        """All-gather the updated shard into `full_param` (in place) on the comm stream."""
+        if self.ws == 1:
+            return
+        if self.device.type == "cuda" and self.comm_stream is not None:
+            ev = torch.cuda.Event()
+            ev.record()
+            with torch.cuda.stream(self.comm_stream):
+                self.comm_stream.wait_event(ev)
+                comm.all_gather_flat(self.full_param, self.param_shard(), self.shard_group)
+                self._gather_event = torch.cuda.Event()
+                self._gather_event.record()
+        else:
+            comm.all_gather_flat(self.full_param, self.param_shard(), self.shard_group)
+
+    def sync_from_rank_shards(self):
+        """Make `full_param` identical everywhere (used once after initialisation)."""
+        if self.ws > 1:
+            comm.all_gather_flat(self.full_param, self.param_shard().clone(), self.shard_group)
+        if self.replicate_group is not None:
+            dist.broadcast(self.full_param, src=dist.get_global_rank(self.replicate_group, 0),
+                           group=self.replicate_group)
+
+
+class ShardedModel:
+    """Book-keeping object attached to a wrapped model as `model._hb_fsdp`."""
+
+    def __init__(self, model, units, root_unit, shard_group, replicate_group, comm_stream):
+        self.model = model
+        self.units: list[FlatUnit] = units        # forward order; root unit last
+        self.root_unit = root_unit
+        self.shard_group = shard_group
+        self.replicate_group = replicate_group
+        self.comm_stream = comm_stream
+
+    def finish_backward(self):
+        """Run after `loss.backward()`: closes the root unit (and any unit whose boundary did
+        not fire, e.g. one whose input needed no gradient)."""
+        for u in self.units:
+            u.post_backward()
+
+    def wait_reductions(self):
+        for u in self.units:
+            u.wait_reduce()
+
+    def sync_parameters(self):
+        for u in self.units:
+            u.sync_from_rank_shards()
+
+    def refresh_fused_views(self):
+        _install_fused_views(self.model, self.units)
+
+    def all_group(self):
+        return self.shard_group
+
+
+def _install_fused_views(model, units):
+    by_module = {}
+    for u in units:
+        for m, n, _, _, _ in u.entries:
+            by_module[id(m)] = u
+    for mod in model.modules():
+        groups = getattr(mod, "fusable_linears", None)
+        if groups is None:
+            continue
+        fused = {}
+        for key, names in groups().items():
+            lin = getattr(mod, names[0], None)
+            u = by_module.get(id(lin))
+            if u is None:
+                continue
+            w = u.fused_view(mod, names)
+            if w is not None:
+                fused[key] = w
+        mod._hb_fused = fused
+
+
+def _unit_params(module: nn.Module, exclude: set[int]):
+    out = []
+    seen = set()
+    for m in module.modules():
+        for n, p in m._parameters.items():
+            if p is None or id(p) in exclude or id(p) in seen:
+                continue
+            seen.add(id(p))
+            out.append((m, n, p))
+    return out
+
+
+def apply_fsdp(model, mesh=None, param_dtype=torch.bfloat16, reduce_dtype=torch.float32,
+               reshard_after_forward=False, device=None, blocks_attr="blocks", force_fsdp=False):
+    """Shard `model` over the mesh's data-parallel dimensions. Returns the same module, with
+    parameters re-homed into flat unit buffers and `model._hb_fsdp` set.
+
+    `mesh` is a `ParallelDims` after `build_mesh()` (or None for a single process).
+    """
+    shard_group = mesh.group("dp_shard") if mesh is not None else None
+    replicate_group = mesh.group("dp_replicate") if mesh is not None else None
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() \
+            else torch.device("cpu")
+    device = torch.device(device)
+    comm_stream = torch.cuda.Stream(device) if device.type == "cuda" else None
+
+    units = []
+    taken: set[int] = set()
+    blocks = getattr(model, blocks_attr, None)
+    block_units = {}
+    if blocks is not None:
+        for key, block in blocks.items():
+            ps = _unit_params(block, taken)
+            taken.update(id(p) for _, _, p in ps)
+            u = FlatUnit(f"{blocks_attr}.{key}", ps, shard_group, replicate_group, param_dtype,
+                         reduce_dtype, device, comm_stream)
+            units.append(u)
+            block_units[int(key)] = u
+            taken.update(id(p) for p in u.params())   # the re-homed Parameter objects
+    # tied head/embedding weights are one parameter: `_unit_params` de-duplicates by identity
+    root_ps = _unit_params(model, taken)
+    root = FlatUnit("root", root_ps, shard_group, replicate_group, param_dtype, reduce_dtype, device,
+                    comm_stream)
+    units.append(root)
+    if getattr(model, "tie_embeds", False) and getattr(model, "head", None) is not None:
+        model.head.tie_weight(model.embedding.embed_weight)
+
+    # move remaining buffers
+    for mod in model.modules():
+        for n, b in list(mod._buffers.items()):
+            if b is not None and b.device != device:
+                mod._buffers[n] = torch.empty_like(b, device=device) if b.device.type == "meta" \
+                    else b.to(device)
+
+    state = ShardedModel(model, units, root, shard_group, replicate_group, comm_stream)
+    model._hb_fsdp = state
+    _install_fused_views(model, units)
+
+    def pre_block(i, x):
+        u = block_units[i]
+        u.pre_forward()
+        if torch.is_grad_enabled() and x.requires_grad:
+            x = _UnitBoundary.apply(x, u)
+        return x
+
+    def post_block(i, x):
+        return x
+
+    model.block_hooks = (pre_block, post_block)
+
+    def root_pre_forward(module, args, kwargs):
+        root.pre_forward()
+        return None
+
+    model.register_forward_pre_hook(root_pre_forward, with_kwargs=True)
+    return model
+
+
+def apply_ddp(model, mesh=None, **kwargs):
+    """Replicated data parallelism: same flat-buffer machinery with a shard group of one rank
+    and gradient all-reduce over the replicate dimension."""
+    return apply_fsdp(model, mesh, **kwargs)
