@@ -56,7 +56,12 @@ void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& out, bool a_mn, 
   g.block_n = (int)block_n; g.max_ctas = (int)max_ctas;
   g.status = status_ptr(status);
   g.stream = cur_stream();
-  HB_CUDA_OK(hb::gemm_bf16(g));
+  cudaError_t err = hb::gemm_bf16(g);
+  TORCH_CHECK(err == cudaSuccess, "halite_b200 gemm failed: ", cudaGetErrorString(err), " (M=", M,
+              " N=", N, " K=", K, " lda=", g.lda, " ldb=", g.ldb, " ldd=", g.ldd, " a_mn=", a_mn,
+              " b_mn=", b_mn, " out_f32=", g.out_f32, " a%16=", (uintptr_t)g.a % 16, " b%16=",
+              (uintptr_t)g.b % 16, " d%16=", (uintptr_t)g.d % 16, ")");
+  hb::launch_counter().fetch_add(1, std::memory_order_relaxed);
 }
 
 }  // namespace

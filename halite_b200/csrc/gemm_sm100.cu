@@ -18,6 +18,8 @@
 //
 // Replaces the cuBLAS calls behind every nn.Linear of the reference
 // (configs/models/transformer.py:124-177,292).
+#include <stdio.h>
+
 #include "gemm.h"
 #include "sm100.cuh"
 
@@ -321,6 +323,16 @@ bool make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64
                        uint64_t ld, uint32_t box_rows, uint32_t box_cols) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return false;
+  // The encode call is a driver-API entry point: it needs the primary context current in the
+  // calling thread. Threads that have not issued a runtime call yet (autograd's backward
+  // workers) get it bound here, once.
+  thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) return false;
+    (void)cudaFree(nullptr);
+    ctx_bound = true;
+  }
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {ld * 2};
   cuuint32_t box[2] = {box_cols, box_rows};
@@ -328,6 +340,10 @@ bool make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    fprintf(stderr, "halite_b200: cuTensorMapEncodeTiled failed (%d): rows=%llu cols=%llu ld=%llu box=%ux%u base=%p\n",
+            (int)r, (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)ld,
+            box_rows, box_cols, base);
   return r == CUDA_SUCCESS;
 }
 
@@ -350,19 +366,23 @@ cudaError_t launch(const GemmArgs& g) {
   bool ok;
   if (!A_MN) ok = make_tmap_bf16_2d(&ta, g.a, g.M, g.K, g.lda, kBM, kBK);
   else       ok = make_tmap_bf16_2d(&ta, g.a, g.K, g.M, g.lda, kBK, 64);
-  if (!ok) return cudaErrorInvalidValue;
+  if (!ok) return cudaErrorInvalidPitchValue;
   if (!B_MN) ok = make_tmap_bf16_2d(&tb, g.b, g.N, g.K, g.ldb, BN, kBK);
   else       ok = make_tmap_bf16_2d(&tb, g.b, g.K, g.N, g.ldb, kBK, 64);
-  if (!ok) return cudaErrorInvalidValue;
+  if (!ok) return cudaErrorInvalidPitchValue;
 
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, OutT>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          C::kSmemBytes);
-    if (e != cudaSuccess) return e;
+    if (e != cudaSuccess) {
+      fprintf(stderr, "halite_b200: cudaFuncSetAttribute failed: %s\n", cudaGetErrorString(e));
+      return e;
+    }
     attr_set = true;
   }
+  (void)cudaGetLastError();  // do not report an error left behind by an earlier, unrelated call
   const int tiles = ((g.M + kBM - 1) / kBM) * ((g.N + BN - 1) / BN);
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (g.max_ctas > 0 && grid > g.max_ctas) grid = g.max_ctas;

@@ -1,0 +1,326 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 reference of the same op."""
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def C():
+    from halite_b200 import ops
+
+    return ops.ext()
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    from halite_b200 import ops
+
+    ops.check_status()
+
+
+def rel_err(a, b):
+    return ((a.float() - b.float()).abs().max() / b.float().abs().max().clamp(min=1e-6)).item()
+
+
+@pytest.mark.parametrize("layout", ["tn", "nn", "tt", "nt_a_mn"])
+@pytest.mark.parametrize("shape", [(128, 128, 64), (512, 768, 1024), (1000, 520, 264), (2048, 1024, 3072), (77, 3072, 4096)])
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_layouts(C, layout, shape, bn):
+    from halite_b200.ops import gemm
+
+    M, N, K = shape
+    a_mn = layout in ("tt", "nt_a_mn")
+    b_mn = layout in ("nn", "tt")
+    if (a_mn and M % 8) or (b_mn and N % 8):
+        pytest.skip("MN-major operands need 16-byte aligned rows")
+    torch.manual_seed(0)
+    A = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    B = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    a = A.t().contiguous() if a_mn else A
+    b = B.t().contiguous() if b_mn else B
+    out = gemm(a, b, a_mn=a_mn, b_mn=b_mn, block_n=bn)
+    ref = A.float() @ B.float().t()
+    assert rel_err(out, ref) < 6e-3
+
+
+def test_gemm_fp32_out_and_accumulate(C):
+    from halite_b200.ops import gemm
+
+    torch.manual_seed(1)
+    A = torch.randn(1024, 640, device="cuda", dtype=torch.bfloat16)
+    B = torch.randn(768, 640, device="cuda", dtype=torch.bfloat16)
+    ref = A.float() @ B.float().t()
+    out = gemm(A, B, out_dtype=torch.float32)
+    assert rel_err(out, ref) < 1e-5
+    gemm(A, B, out=out, accumulate=True)
+    assert rel_err(out, 2 * ref) < 1e-5
+    ob = torch.ones(1024, 768, device="cuda", dtype=torch.bfloat16)
+    gemm(A, B, out=ob, accumulate=True)
+    assert rel_err(ob, ref + 1) < 6e-3
+    # strided output view (columns of a wider buffer)
+    wide = torch.zeros(1024, 1024, device="cuda", dtype=torch.bfloat16)
+    gemm(A, B, out=wide[:, 128:896])
+    assert rel_err(wide[:, 128:896], ref) < 6e-3 and wide[:, :128].abs().max() == 0
+
+
+def test_linear_autograd_matches_torch(C):
+    from halite_b200 import ops
+
+    torch.manual_seed(2)
+    x = torch.randn(4, 96, 512, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(384, 512, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    b = torch.randn(384, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = ops.linear(x, w, b)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr, br = (t.detach().float().requires_grad_(True) for t in (x, w, b))
+    yr = torch.nn.functional.linear(xr, wr, br)
+    yr.backward(g.float())
+    assert rel_err(y, yr) < 1e-2
+    assert rel_err(x.grad, xr.grad) < 1e-2
+    assert rel_err(w.grad, wr.grad) < 1e-2
+    assert rel_err(b.grad, br.grad) < 1e-2
+
+
+@pytest.mark.parametrize("dim", [256, 3072, 4096, 8192])
+@pytest.mark.parametrize("residual", [False, True])
+def test_rmsnorm(C, dim, residual):
+    from halite_b200 import ops
+    from halite_b200.ops.norm import rms_norm_reference
+
+    torch.manual_seed(3)
+    x = torch.randn(3, 67, dim, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    r = torch.randn_like(x).requires_grad_(True) if residual else None
+    w = (1 + 0.1 * torch.randn(dim, device="cuda")).bfloat16().requires_grad_(True)
+    out = ops.rms_norm(x, w, 1e-5, r)
+    y, h = out if residual else (out, None)
+    gy = torch.randn_like(y)
+    gh = torch.randn_like(y) if residual else None
+    if residual:
+        torch.autograd.backward([y, h], [gy, gh])
+    else:
+        y.backward(gy)
+    xr = x.detach().float().requires_grad_(True)
+    rr = r.detach().float().requires_grad_(True) if residual else None
+    wr = w.detach().float().requires_grad_(True)
+    hf = xr + rr if residual else xr
+    if residual:
+        hf = hf.detach().bfloat16().float() + (hf - hf.detach())   # the kernel rounds the stream to bf16
+    yr = hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + 1e-5) * wr
+    if residual:
+        torch.autograd.backward([yr, hf], [gy.float(), gh.float()])
+    else:
+        yr.backward(gy.float())
+    assert rel_err(y, yr) < 1e-2
+    assert rel_err(x.grad, xr.grad) < 2e-2
+    assert rel_err(w.grad, wr.grad) < 2e-2
+    if residual:
+        assert rel_err(r.grad, rr.grad) < 2e-2
+        assert rel_err(h, hf) < 1e-2
+
+
+@pytest.mark.parametrize("interleaved", [True, False])
+def test_rope_forward_backward(C, interleaved):
+    from halite_b200 import ops
+    from halite_b200.ops.rope import apply_rope_reference, rope_tables
+
+    torch.manual_seed(4)
+    B, S, H, Hk, D = 2, 129, 12, 4, 128
+    inv = 1.0 / (500000 ** (torch.arange(0, D, 2).float() / D))
+    cos, sin = rope_tables(inv, 512, "cuda")
+    pos = torch.randint(0, 512, (B, S), device="cuda")
+    q = torch.randn(B, S, H, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(B, S, Hk, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    q2, k2 = ops.apply_rope(q.clone(), k.clone(), cos, sin, pos, interleaved)
+    gq, gk = torch.randn_like(q2), torch.randn_like(k2)
+    torch.autograd.backward([q2, k2], [gq, gk])
+    qr = q.detach().float().requires_grad_(True)
+    kr = k.detach().float().requires_grad_(True)
+    q3 = apply_rope_reference(qr, cos, sin, pos, interleaved)
+    k3 = apply_rope_reference(kr, cos, sin, pos, interleaved)
+    torch.autograd.backward([q3, k3], [gq.float(), gk.float()])
+    assert rel_err(q2, q3) < 1e-2 and rel_err(k2, k3) < 1e-2
+    assert rel_err(q.grad, qr.grad) < 1e-2 and rel_err(k.grad, kr.grad) < 1e-2
+
+
+@pytest.mark.parametrize("kind", ["silu", "gelu_tanh"])
+def test_gated_activation(C, kind):
+    from halite_b200.ops.activation import gated_act, gated_act_packed
+
+    torch.manual_seed(5)
+    p = torch.randn(5, 33, 2 * 1024, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    out = gated_act_packed(p, kind, gate_first=False)
+    g = torch.randn_like(out)
+    out.backward(g)
+    pr = p.detach().float().requires_grad_(True)
+    up, gate = pr[..., :1024], pr[..., 1024:]
+    act = torch.nn.functional.silu(gate) if kind == "silu" else torch.nn.functional.gelu(gate, approximate="tanh")
+    ref = act * up
+    ref.backward(g.float())
+    assert rel_err(out, ref) < 1e-2 and rel_err(p.grad, pr.grad) < 2e-2
+    a = torch.randn(7, 512, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    b = torch.randn(7, 512, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    o2 = gated_act(a, b, kind)
+    o2.sum().backward()
+    assert a.grad is not None and b.grad is not None and o2.shape == a.shape
+
+
+@pytest.mark.parametrize("vocab", [1000, 32000, 128256])
+def test_cross_entropy_rows(C, vocab):
+    from halite_b200 import ops
+    from halite_b200.ops.loss import cross_entropy_rows_reference
+
+    torch.manual_seed(6)
+    R = 65
+    logits = (2 * torch.randn(R, vocab, device="cuda")).bfloat16().requires_grad_(True)
+    tgt = torch.randint(0, vocab, (R,), device="cuda")
+    tgt[3] = -100
+    loss, z, lse = ops.cross_entropy_rows(logits, tgt, z_loss=1e-4)
+    w = torch.rand(R, device="cuda")
+    (loss * w).sum().backward()
+    lr = logits.detach().float().requires_grad_(True)
+    loss_r, z_r, lse_r = cross_entropy_rows_reference(lr, tgt, z_loss=1e-4)
+    (loss_r * w).sum().backward()
+    assert torch.allclose(loss, loss_r, atol=2e-3, rtol=1e-4)
+    assert torch.allclose(lse, lse_r, atol=1e-3)
+    assert torch.allclose(z, z_r, atol=1e-4)
+    assert (logits.grad.float() - lr.grad).abs().max() < 2e-2 * lr.grad.abs().max()
+    assert logits.grad[3].abs().max() == 0
+
+
+def test_cross_entropy_softcap_smoothing(C):
+    from halite_b200 import ops
+    from halite_b200.ops.loss import cross_entropy_rows_reference
+
+    torch.manual_seed(7)
+    logits = (3 * torch.randn(33, 5000, device="cuda")).float().requires_grad_(True)
+    tgt = torch.randint(0, 5000, (33,), device="cuda")
+    loss, _, _ = ops.cross_entropy_rows(logits, tgt, softcap=30.0, label_smoothing=0.1)
+    loss.sum().backward()
+    lr = logits.detach().clone().requires_grad_(True)
+    loss_r, _, _ = cross_entropy_rows_reference(lr, tgt, softcap=30.0, label_smoothing=0.1)
+    loss_r.sum().backward()
+    assert torch.allclose(loss, loss_r, atol=1e-4, rtol=1e-5)
+    assert torch.allclose(logits.grad, lr.grad, atol=1e-5)
+
+
+def test_fused_linear_cross_entropy(C):
+    from halite_b200 import ops
+
+    torch.manual_seed(8)
+    T, D, V = 700, 256, 9000
+    x = torch.randn(T, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (0.05 * torch.randn(V, D, device="cuda")).bfloat16().requires_grad_(True)
+    tgt = torch.randint(0, V, (T,), device="cuda")
+    tgt[::7] = -100
+    losses, z = ops.fused_linear_cross_entropy(x, w, tgt, z_loss=1e-4, chunk_rows=256)
+    losses.mean().backward()
+    xr = x.detach().float().requires_grad_(True)
+    wr = w.detach().float().requires_grad_(True)
+    logits = xr @ wr.t()
+    lse = torch.logsumexp(logits, -1)
+    ce = torch.nn.functional.cross_entropy(logits, tgt, reduction="none", ignore_index=-100)
+    ref = ce + 1e-4 * lse.square() * (tgt != -100)
+    ref.mean().backward()
+    assert torch.allclose(losses, ref, atol=3e-2, rtol=1e-2)
+    assert rel_err(x.grad, xr.grad) < 3e-2
+    assert rel_err(w.grad, wr.grad) < 3e-2
+
+
+def test_logprob_entropy(C):
+    from halite_b200 import ops
+
+    torch.manual_seed(9)
+    T, D, V = 300, 128, 5000
+    h = torch.randn(T, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (0.1 * torch.randn(V, D, device="cuda")).bfloat16().requires_grad_(True)
+    tgt = torch.randint(0, V, (T,), device="cuda")
+    inv_t = 1.0 / (0.5 + torch.rand(T, device="cuda"))
+    logp, ent = ops.logprob_entropy(h, w, tgt, inv_t, chunk_rows=128)
+    gl, ge = torch.randn(T, device="cuda"), torch.randn(T, device="cuda")
+    torch.autograd.backward([logp, ent], [gl, ge])
+    hr = h.detach().float().requires_grad_(True)
+    wr = w.detach().float().requires_grad_(True)
+    logits = (hr @ wr.t()).bfloat16().float() * inv_t[:, None]
+    lp_all = torch.log_softmax(logits, -1)
+    logits2 = (hr @ wr.t()) * inv_t[:, None]
+    lp2 = torch.log_softmax(logits2, -1)
+    lpr = lp2.gather(-1, tgt[:, None]).squeeze(-1)
+    entr = -(lp2.exp() * lp2).sum(-1)
+    torch.autograd.backward([lpr, entr], [gl, ge])
+    assert torch.allclose(logp, lpr, atol=3e-2)
+    assert torch.allclose(ent, entr, atol=3e-2)
+    assert rel_err(h.grad, hr.grad) < 4e-2
+    assert rel_err(w.grad, wr.grad) < 4e-2
+
+
+def test_adamw_clip_and_casts(C):
+    from halite_b200 import ops
+
+    torch.manual_seed(10)
+    n = 100003
+    master = torch.randn(n, device="cuda")
+    ref = master.clone().requires_grad_(True)
+    m, v = torch.zeros_like(master), torch.zeros_like(master)
+    low = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    opt = torch.optim.AdamW([ref], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    for step in range(1, 5):
+        g = torch.randn(n, device="cuda")
+        ss = torch.zeros(1, device="cuda")
+        ops.grad_sumsq(g, ss)
+        coef = torch.empty(2, device="cuda")
+        C.clip_coef_(ss, 1.0, coef)
+        assert abs(coef[1].item() - g.norm().item()) / g.norm().item() < 1e-5
+        ref.grad = g.clone()
+        torch.nn.utils.clip_grad_norm_([ref], 1.0)
+        opt.step()
+        ops.fused_adamw_step(master, m, v, g, low, 1e-2, (0.9, 0.95), 1e-8, 0.1, step, 1.0, coef)
+    assert (master - ref.detach()).abs().max() < 1e-5
+    assert torch.equal(low, master.bfloat16())
+    gb = torch.randn(n, device="cuda").bfloat16()
+    ss = torch.zeros(1, device="cuda")
+    ops.grad_sumsq(gb, ss)
+    assert abs(ss.item() - gb.float().square().sum().item()) / ss.item() < 1e-5
+
+
+def test_gae(C):
+    from halite_b200 import ops
+    from halite_b200.ops.rl import gae_reference
+
+    torch.manual_seed(11)
+    r, v = torch.randn(17, 93, device="cuda"), torch.randn(17, 93, device="cuda")
+    mask = (torch.rand(17, 93, device="cuda") > 0.2).float()
+    for m in (None, mask):
+        adv, ret = ops.gae(r, v, 0.99, 0.95, m)
+        adv_r, ret_r = gae_reference(r, v, 0.99, 0.95, m)
+        assert torch.allclose(adv, adv_r, atol=1e-4) and torch.allclose(ret, ret_r, atol=1e-4)
+
+
+def test_packed_qkv_attention_matches_eager(C):
+    from halite_b200.ops.attention import attention_reference, packed_qkv_attention
+    from halite_b200.ops.rope import apply_rope_reference, rope_tables
+
+    torch.manual_seed(12)
+    B, S, H, Hk, D = 2, 256, 8, 2, 64
+    inv = 1.0 / (10000 ** (torch.arange(0, D, 2).float() / D))
+    cos, sin = rope_tables(inv, 512, "cuda")
+    pos = torch.arange(S, device="cuda").unsqueeze(0)
+    qkv = torch.randn(B, S, (H + 2 * Hk) * D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    out = packed_qkv_attention(qkv.clone(), H, Hk, D, cos, sin, pos, True, True, None)
+    g = torch.randn_like(out)
+    out.backward(g)
+    qr = qkv.detach().float().requires_grad_(True)
+    q = qr[..., : H * D].unflatten(-1, (H, D))
+    k = qr[..., H * D:(H + Hk) * D].unflatten(-1, (Hk, D))
+    v = qr[..., (H + Hk) * D:].unflatten(-1, (Hk, D))
+    q = apply_rope_reference(q, cos, sin, pos, True)
+    k = apply_rope_reference(k, cos, sin, pos, True)
+    ref = attention_reference(q, k, v, causal=True, q_offset=None).reshape(B, S, H * D)
+    ref.backward(g.float())
+    assert rel_err(out, ref) < 2e-2
+    assert rel_err(qkv.grad, qr.grad) < 3e-2
