@@ -129,80 +129,81 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   }
 }
 
-// One CTA walks rows blockIdx.x, blockIdx.x + gridDim.x, ... and keeps dw partials in registers.
+// Backward, split in two bandwidth-shaped kernels.
+// (1) dx: one warp per row (no block-level sync); the row is read twice, the second time from L1.
 template <bool HAS_DRES>
-__global__ void __launch_bounds__(kNormThreads)
-rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
-                   const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
-                   const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
-                   float* __restrict__ dw_partial, int rows, int dim, float w_offset) {
-  __shared__ float red[33];
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
+                      const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                      const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                      int rows, int dim, float w_offset) {
+  const int lane = threadIdx.x & 31;
+  const long row = static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
   const int nvec = dim >> 3;
+  const bf16x8* dyr = reinterpret_cast<const bf16x8*>(dy + row * dim);
+  const bf16x8* hr = reinterpret_cast<const bf16x8*>(h + row * dim);
   const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
-  float wv[kNormMaxVec][8];
-  float dw[kNormMaxVec][8];
+  const float rs = rstd[row];
+  float dot = 0.f;
+  for (int v = lane; v < nvec; v += 32) {
+    float d[8], hv[8], wv[8];
+    unpack8(dyr[v], d);
+    unpack8(hr[v], hv);
+    unpack8(wr[v], wv);
 #pragma unroll
-  for (int i = 0; i < kNormMaxVec; ++i) {
-    const int v = threadIdx.x + i * kNormThreads;
+    for (int j = 0; j < 8; ++j) dot += d[j] * (wv[j] + w_offset) * hv[j];
+  }
+  dot = warp_sum(dot) * rs / dim;  // mean(g * xhat)
+  bf16x8* dxr = reinterpret_cast<bf16x8*>(dx + row * dim);
+  const bf16x8* drr = HAS_DRES ? reinterpret_cast<const bf16x8*>(dres + row * dim) : nullptr;
+  for (int v = lane; v < nvec; v += 32) {
+    float d[8], hv[8], wv[8], o[8];
+    unpack8(dyr[v], d);
+    unpack8(hr[v], hv);
+    unpack8(wr[v], wv);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) dw[i][j] = 0.f;
-    if (v < nvec) {
-      unpack8(wr[v], wv[i]);
+    for (int j = 0; j < 8; ++j) o[j] = rs * (d[j] * (wv[j] + w_offset) - hv[j] * rs * dot);
+    if (HAS_DRES) {
+      float r[8];
+      unpack8(drr[v], r);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) wv[i][j] += w_offset;
+      for (int j = 0; j < 8; ++j) o[j] += r[j];
+    }
+    dxr[v] = pack8(o);
+  }
+}
+
+// (2) dw partials: CTA (x, y) sums dy * h * rstd over its row slice for 256 columns.
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_dw_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
+                      const float* __restrict__ rstd, float* __restrict__ dw_partial, int rows,
+                      int dim) {
+  __shared__ float red[8][256];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col = blockIdx.x * 256 + lane * 8;
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  if (col < dim) {
+    for (long r = static_cast<long>(blockIdx.y) * 8 + warp; r < rows; r += static_cast<long>(gridDim.y) * 8) {
+      float d[8], hv[8];
+      unpack8(*reinterpret_cast<const bf16x8*>(dy + r * dim + col), d);
+      unpack8(*reinterpret_cast<const bf16x8*>(h + r * dim + col), hv);
+      const float rs = rstd[r];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += d[j] * hv[j] * rs;
     }
   }
-  for (long row = blockIdx.x; row < rows; row += gridDim.x) {
-    const bf16x8* dyr = reinterpret_cast<const bf16x8*>(dy + row * dim);
-    const bf16x8* hr = reinterpret_cast<const bf16x8*>(h + row * dim);
-    const float rs = rstd[row];
-    float g[kNormMaxVec][8], xh[kNormMaxVec][8];
-    float dot = 0.f;
 #pragma unroll
-    for (int i = 0; i < kNormMaxVec; ++i) {
-      const int v = threadIdx.x + i * kNormThreads;
-      if (v < nvec) {
-        float d[8], hv[8];
-        unpack8(dyr[v], d);
-        unpack8(hr[v], hv);
+  for (int j = 0; j < 8; ++j) red[warp][lane * 8 + j] = acc[j];
+  __syncthreads();
+  const int c = threadIdx.x;
+  if (blockIdx.x * 256 + c < dim) {
+    float s = 0.f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          xh[i][j] = hv[j] * rs;
-          g[i][j] = d[j] * wv[i][j];
-          dot += g[i][j] * xh[i][j];
-          dw[i][j] += d[j] * xh[i][j];
-        }
-      }
-    }
-    dot = block_sum(dot, red) / dim;
-    bf16x8* dxr = reinterpret_cast<bf16x8*>(dx + row * dim);
-    const bf16x8* drr = HAS_DRES ? reinterpret_cast<const bf16x8*>(dres + row * dim) : nullptr;
-#pragma unroll
-    for (int i = 0; i < kNormMaxVec; ++i) {
-      const int v = threadIdx.x + i * kNormThreads;
-      if (v < nvec) {
-        float o[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = rs * (g[i][j] - xh[i][j] * dot);
-        if (HAS_DRES) {
-          float r[8];
-          unpack8(drr[v], r);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] += r[j];
-        }
-        dxr[v] = pack8(o);
-      }
-    }
-  }
-  float* out = dw_partial + static_cast<long>(blockIdx.x) * dim;
-#pragma unroll
-  for (int i = 0; i < kNormMaxVec; ++i) {
-    const int v = threadIdx.x + i * kNormThreads;
-    if (v < nvec) {
-      float4* o4 = reinterpret_cast<float4*>(out + v * 8);
-      o4[0] = make_float4(dw[i][0], dw[i][1], dw[i][2], dw[i][3]);
-      o4[1] = make_float4(dw[i][4], dw[i][5], dw[i][6], dw[i][7]);
-    }
+    for (int wi = 0; wi < 8; ++wi) s += red[wi][c];
+    dw_partial[static_cast<long>(blockIdx.y) * dim + blockIdx.x * 256 + c] = s;
   }
 }
 
@@ -450,8 +451,8 @@ ce_kernel(CEArgs a) {
   if (ignored) gs = 0.f;
   const float pz = 1.f + 2.f * a.z_loss * lse;
   const float eps_ls = a.label_smoothing;
-  for (int i = threadIdx.x; i < V; i += kCEThreads) {
-    const float raw = ld_logit<T>(lg, i) * scale;
+  auto grad_of = [&](float raw_logit, int i) {
+    const float raw = raw_logit * scale;
     float x = raw, dcap = 1.f;
     if (a.softcap > 0.f) {
       const float t = tanhf(raw / a.softcap);
@@ -461,8 +462,28 @@ ce_kernel(CEArgs a) {
     const float p = __expf(x - lse);
     float g = p * pz - eps_ls / V;
     if (i == tl && own_target) g -= (1.f - eps_ls);
-    st_logit<T>(dl, i, g * gs * dcap * scale);
+    return g * gs * dcap * scale;
+  };
+  const bool vec2 = vec_ok && ((reinterpret_cast<uintptr_t>(dl) & 15) == 0);
+  const int nv2 = vec2 ? V / VEC : 0;
+  for (int v = threadIdx.x; v < nv2; v += kCEThreads) {
+    if constexpr (sizeof(T) == 2) {
+      float f[8];
+      unpack8(reinterpret_cast<const bf16x8*>(lg)[v], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = grad_of(f[j], v * 8 + j);
+      reinterpret_cast<bf16x8*>(dl)[v] = pack8(f);
+    } else {
+      float4 t4 = reinterpret_cast<const float4*>(lg)[v];
+      t4.x = grad_of(t4.x, v * 4);
+      t4.y = grad_of(t4.y, v * 4 + 1);
+      t4.z = grad_of(t4.z, v * 4 + 2);
+      t4.w = grad_of(t4.w, v * 4 + 3);
+      reinterpret_cast<float4*>(dl)[v] = t4;
+    }
   }
+  for (int i = nv2 * VEC + threadIdx.x; i < V; i += kCEThreads)
+    st_logit<T>(dl, i, grad_of(ld_logit<T>(lg, i), i));
 }
 
 // Backward of (log-prob of target, entropy) w.r.t. logits, one CTA per row:
@@ -690,19 +711,21 @@ cudaError_t rmsnorm_bwd(const void* dy, const void* h, const void* w, const floa
   if (rows == 0) return cudaSuccess;
   if (dim % 8 != 0 || dim > kNormThreads * 8 * kNormMaxVec || partial_rows < 1)
     return cudaErrorInvalidValue;
-  const int grid = partial_rows < rows ? partial_rows : rows;
   auto DY = static_cast<const __nv_bfloat16*>(dy);
   auto H = static_cast<const __nv_bfloat16*>(h);
   auto W = static_cast<const __nv_bfloat16*>(w);
   auto DR = static_cast<const __nv_bfloat16*>(dres);
   auto DX = static_cast<__nv_bfloat16*>(dx);
-  if (grid < partial_rows)
-    cudaMemsetAsync(dw_partial + static_cast<long>(grid) * dim, 0,
-                    sizeof(float) * static_cast<long>(partial_rows - grid) * dim, stream);
+  const int grid_dx = (rows + 7) / 8;
   if (DR)
-    rmsnorm_bwd_kernel<true><<<grid, kNormThreads, 0, stream>>>(DY, H, W, rstd, DR, DX, dw_partial, rows, dim, w_offset);
+    rmsnorm_bwd_dx_kernel<true><<<grid_dx, 256, 0, stream>>>(DY, H, W, rstd, DR, DX, rows, dim, w_offset);
   else
-    rmsnorm_bwd_kernel<false><<<grid, kNormThreads, 0, stream>>>(DY, H, W, rstd, DR, DX, dw_partial, rows, dim, w_offset);
+    rmsnorm_bwd_dx_kernel<false><<<grid_dx, 256, 0, stream>>>(DY, H, W, rstd, DR, DX, rows, dim, w_offset);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  // every one of the `partial_rows` rows is written (row slices may be empty -> zeros)
+  dim3 grid_dw((dim + 255) / 256, partial_rows);
+  rmsnorm_bwd_dw_kernel<<<grid_dw, 256, 0, stream>>>(DY, H, rstd, dw_partial, rows, dim);
   return cudaGetLastError();
 }
 

@@ -1,0 +1,227 @@
+"""Owns the model, the KV / request pools and the forward paths of the engine (reference:
+infer/engine/model_runner.py:14-252).
+
+Decode runs `n` steps ahead of the host: sampled tokens, positions, sequence lengths and KV
+slots are advanced on the device between steps (the page table already holds the pages those
+steps will open), so the host reads tokens once per `n` steps instead of once per token.
+With `use_cudagraph` each step replays a captured graph of the model forward for the batch
+bucket.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from halite_b200.infer.batch import ForwardBatch, ForwardMode
+from halite_b200.infer.memory_pool import PagedKVPool, RequestToPagePool
+from halite_b200.infer.sampler import Sampler
+from halite_b200.infer.types import ModelConfig, ServerConfig
+from halite_b200.utils import get_torch_dtype
+
+
+def get_gpu_memory(device, gpu_id=0, distributed=False):
+    """(available, total) GiB on the device; with `distributed` the minimum over ranks."""
+    dev = torch.device(device)
+    if dev.type != "cuda":
+        return 4.0, 4.0
+    free, total = torch.cuda.mem_get_info(gpu_id if dev.index is None else dev.index)
+    t = torch.tensor([free / 2 ** 30, total / 2 ** 30], dtype=torch.float32, device=dev)
+    if distributed and torch.distributed.is_initialized():
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MIN)
+    return float(t[0]), float(t[1])
+
+
+class ModelRunner:
+    def __init__(self, model, model_config: ModelConfig, server_config: ServerConfig):
+        self.model = model
+        self.model_config = model_config
+        self.server_config = server_config
+        self.sampler = Sampler(seed=server_config.seed)
+        self.device = torch.device(model_config.device)
+        if self.device.type == "cuda" and self.device.index is None:
+            self.device = torch.device("cuda", model_config.gpu_id)
+        self.page_size = server_config.page_size
+        dtype = model_config.kv_cache_dtype
+        if dtype == "auto":
+            dtype = getattr(model, "dtype", torch.float32)
+            if dtype is None or (self.device.type == "cuda" and dtype == torch.float32 and False):
+                dtype = torch.bfloat16
+        self.kv_cache_dtype = get_torch_dtype(dtype)
+        self.req_pool = None
+        self.kv_pool = None
+        self.graphs = {}
+        self.graph_state = None
+        self.workspace = None
+        self.initialize()
+
+    # ------------------------------------------------------------------ lifecycle
+    def estimate_max_tokens(self):
+        mc = self.model_config
+        if self.server_config.max_total_tokens is not None:
+            return int(self.server_config.max_total_tokens)
+        avail, total = get_gpu_memory(self.device, mc.gpu_id, mc.distributed)
+        cell = (mc.n_key_value_heads // mc.tp_size if mc.n_key_value_heads >= mc.tp_size else 1) \
+            * mc.head_dim * mc.n_layers * 2 * torch.empty(0, dtype=self.kv_cache_dtype).element_size()
+        rest = avail - total * (1 - mc.memory_fraction_static)
+        n = int(rest * (1 << 30) // cell)
+        if n <= 0:
+            raise RuntimeError("not enough device memory for a KV cache: raise memory_fraction_static")
+        return n
+
+    def initialize(self):
+        mc, sc = self.model_config, self.server_config
+        self.max_total_tokens = self.estimate_max_tokens() // self.page_size * self.page_size
+        n_pages = self.max_total_tokens // self.page_size
+        self.max_running_requests = min(sc.max_running_requests, max(self.max_total_tokens // 2, 1))
+        self.max_requests = min(max(int(self.max_total_tokens / mc.context_len * 512), 2048), 4096)
+        max_pages_per_req = (mc.context_len + 4 + self.page_size - 1) // self.page_size
+        # one extra, never allocated row: padded CUDA-graph entries point at it (all page 0)
+        self.req_pool = RequestToPagePool(self.max_requests + 1, max_pages_per_req, self.device)
+        self.req_pool.free_slots = list(range(self.max_requests))
+        self.pad_slot = self.max_requests
+        kv_heads = max(mc.n_key_value_heads // mc.tp_size, 1)
+        self.kv_pool = PagedKVPool(n_pages, self.page_size, mc.n_layers, kv_heads, mc.head_dim,
+                                   self.kv_cache_dtype, self.device)
+        if hasattr(self.model, "set_kv_pool"):
+            self.model.set_kv_pool(self.kv_pool)
+        self.graphs = {}
+        self.graph_state = None
+        if self.device.type == "cuda":
+            q_heads = max(mc.n_heads // mc.tp_size, 1)
+            self.workspace = torch.empty(self.decode_workspace_numel(q_heads, mc.head_dim),
+                                         dtype=torch.float32, device=self.device)
+
+    def decode_workspace_numel(self, q_heads, head_dim, max_batch=None, max_splits=32):
+        b = max_batch or min(self.max_running_requests, 4096)
+        return b * q_heads * max_splits * (head_dim + 2)
+
+    def cleanup(self):
+        """Give the device memory back (weights and pools) so training can use it."""
+        self.model.to("meta")
+        self.req_pool = None
+        self.kv_pool = None
+        self.graphs = {}
+        self.graph_state = None
+        self.workspace = None
+        if self.device.type == "cuda":
+            torch.cuda.empty_cache()
+
+    def load_state_dict(self, state_dict, assign=True):
+        from halite_b200.distributed.state_dict import reshard_state_dict
+
+        self.model.to("meta")
+        target = self.model.state_dict()
+        sd = reshard_state_dict(state_dict, target, device=self.device)
+        if not assign:
+            self.model.to_empty(device=self.device)
+        self.model.load_state_dict(sd, assign=assign)
+        if hasattr(self.model, "init_buffers"):
+            self.model.init_buffers(self.device)
+        if hasattr(self.model, "set_kv_pool") and self.kv_pool is not None:
+            self.model.set_kv_pool(self.kv_pool)
+        self.graphs = {}
+
+    # ------------------------------------------------------------------ forward
+    @torch.no_grad()
+    def forward(self, fb: ForwardBatch):
+        fb.workspace = self.workspace
+        return self.model(fb)
+
+    @torch.no_grad()
+    def forward_and_sample(self, batch):
+        logits = self.forward(batch.forward_batch)
+        ids, logprobs = self.sampler(logits, batch.sampling)
+        return logits, ids, logprobs
+
+    @torch.no_grad()
+    def decode_steps(self, batch, n_steps, last_tokens=None):
+        """Run `n_steps` decode steps without a host round trip. The batch has already had
+        `alloc_for_decode(n_steps)` applied. Returns (ids [n, B], logprobs [n, B]) on device."""
+        fb = batch.prepare_for_decode(last_tokens)
+        ps = self.page_size
+        B = fb.batch_size
+        all_ids, all_lp = [], []
+        slots64 = fb.req_slots.long()
+        graph = self._graph_for(B) if self.server_config.use_cudagraph else None
+        for s in range(n_steps):
+            if graph is not None:
+                logits = self._replay(graph, fb)
+            else:
+                logits = self.forward(fb)
+            ids, lp = self.sampler(logits, batch.sampling)
+            all_ids.append(ids)
+            all_lp.append(lp)
+            if s + 1 < n_steps:
+                positions = fb.positions + 1
+                pages = fb.page_table[slots64, positions // ps].long()
+                fb = ForwardBatch(
+                    mode=ForwardMode.DECODE, input_ids=ids, positions=positions,
+                    out_cache_loc=pages * ps + positions % ps, req_slots=fb.req_slots,
+                    seq_lens=fb.seq_lens + 1, page_table=fb.page_table, max_seq_len=fb.max_seq_len + 1,
+                    max_extend_len=1, page_size=ps,
+                    seq_lens_cpu=[x + 1 for x in fb.seq_lens_cpu] if fb.seq_lens_cpu else None)
+        for r in batch.requests:
+            r.pending_tokens += n_steps
+        return torch.stack(all_ids), torch.stack(all_lp)
+
+    # ------------------------------------------------------------------ CUDA graphs
+    def graph_sizes(self):
+        sc = self.server_config
+        sizes = set(sc.cudagraph_additonal_batch_size) | set(
+            range(sc.cudagraph_step, sc.cudagraph_max_batch_size + 1, sc.cudagraph_step))
+        return sorted(s for s in sizes if s > 0)
+
+    def _graph_for(self, batch_size):
+        if self.device.type != "cuda":
+            return None
+        sizes = self.graph_sizes()
+        bucket = next((s for s in sizes if s >= batch_size), None)
+        if bucket is None:
+            return None
+        if bucket not in self.graphs:
+            self.graphs[bucket] = self._capture(bucket)
+        return self.graphs[bucket]
+
+    def _static_batch(self, bucket):
+        dev = self.device
+        fb = ForwardBatch(
+            mode=ForwardMode.DECODE,
+            input_ids=torch.zeros(bucket, dtype=torch.int64, device=dev),
+            positions=torch.zeros(bucket, dtype=torch.int64, device=dev),
+            out_cache_loc=torch.zeros(bucket, dtype=torch.int64, device=dev),
+            req_slots=torch.full((bucket,), self.pad_slot, dtype=torch.int32, device=dev),
+            seq_lens=torch.ones(bucket, dtype=torch.int32, device=dev),
+            page_table=self.req_pool.req_to_pages, max_seq_len=self.model_config.context_len,
+            max_extend_len=1, page_size=self.page_size)
+        fb.workspace = self.workspace
+        return fb
+
+    def _capture(self, bucket):
+        fb = self._static_batch(bucket)
+        # warm up on a side stream (allocator, lazy init), then capture
+        s = torch.cuda.Stream(self.device)
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(2):
+                self.model(fb)
+        torch.cuda.current_stream().wait_stream(s)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            out = self.model(fb)
+        return {"graph": g, "fb": fb, "out": out, "bucket": bucket}
+
+    def _replay(self, graph, fb):
+        st = graph["fb"]
+        B = fb.batch_size
+        st.input_ids[:B].copy_(fb.input_ids)
+        st.positions[:B].copy_(fb.positions)
+        st.out_cache_loc[:B].copy_(fb.out_cache_loc)
+        st.req_slots[:B].copy_(fb.req_slots)
+        st.seq_lens[:B].copy_(fb.seq_lens)
+        if B < graph["bucket"]:
+            st.req_slots[B:].fill_(self.pad_slot)
+            st.seq_lens[B:].fill_(1)
+            st.positions[B:].zero_()
+            st.out_cache_loc[B:].zero_()
+        graph["graph"].replay()
+        return graph["out"][:B]
