@@ -29,9 +29,76 @@ int* status_ptr(const c10::optional<at::Tensor>& status) {
 }
 
 // out[M,N] (=|+=) op(a) * op(b). a: [M,K] (or [K,M] when a_mn), b: [N,K] (or [K,N] when b_mn).
+// Optional fused gather description, filled from a Python dict (see hb::GatherParams).
+bool fill_gather(const c10::optional<py::dict>& d, hb::GatherParams& gp) {
+  if (!d.has_value()) return false;
+  const py::dict& g = *d;
+  auto srcs = g["src_ptrs"].cast<std::vector<int64_t>>();
+  TORCH_CHECK((int)srcs.size() <= hb::kMaxPeers, "too many gather chunks");
+  gp.n_chunks = (int)srcs.size();
+  for (int i = 0; i < gp.n_chunks; ++i) gp.src[i] = reinterpret_cast<const void*>(srcs[i]);
+  if (g.contains("peer_done_ptrs")) {
+    auto pd = g["peer_done_ptrs"].cast<std::vector<int64_t>>();
+    for (int i = 0; i < (int)pd.size() && i < hb::kMaxPeers; ++i) gp.peer_done[i] = reinterpret_cast<int*>(pd[i]);
+  }
+  gp.dst_base = reinterpret_cast<void*>(g["dst_ptr"].cast<int64_t>());
+  gp.chunk_bytes = g["chunk_bytes"].cast<int64_t>();
+  gp.granule_bytes = g["granule_bytes"].cast<int64_t>();
+  gp.n_copy_ctas = g["n_copy_ctas"].cast<int>();
+  gp.flags = reinterpret_cast<int*>(g["flags_ptr"].cast<int64_t>());
+  gp.ready = g.contains("ready_ptr") ? reinterpret_cast<const int*>(g["ready_ptr"].cast<int64_t>()) : nullptr;
+  gp.done_counter = g.contains("done_counter_ptr") ? reinterpret_cast<int*>(g["done_counter_ptr"].cast<int64_t>()) : nullptr;
+  gp.epoch = g["epoch"].cast<int>();
+  gp.dep = g["dep"].cast<int>();
+  gp.dep_row_bytes = g["dep_row_bytes"].cast<int64_t>();
+  gp.dep_base_offset = g.contains("dep_base_offset") ? g["dep_base_offset"].cast<int64_t>() : 0;
+  gp.m_rot = g.contains("m_rot") ? g["m_rot"].cast<int>() : 0;
+  gp.first_chunk = g.contains("first_chunk") ? g["first_chunk"].cast<int>() : 0;
+  return true;
+}
+
+bool fill_scatter(const c10::optional<py::dict>& d, hb::ScatterParams& sp) {
+  if (!d.has_value()) return false;
+  const py::dict& g = *d;
+  auto dst = g["dst_ptrs"].cast<std::vector<int64_t>>();
+  auto recv = g["recv_ptrs"].cast<std::vector<int64_t>>();
+  auto pf = g["peer_flag_ptrs"].cast<std::vector<int64_t>>();
+  TORCH_CHECK((int)dst.size() <= hb::kMaxPeers && dst.size() == recv.size() && dst.size() == pf.size(),
+              "scatter pointer lists must have one entry per rank");
+  sp.n_chunks = (int)dst.size();
+  for (int i = 0; i < sp.n_chunks; ++i) {
+    sp.dst[i] = reinterpret_cast<void*>(dst[i]);
+    sp.recv[i] = reinterpret_cast<const void*>(recv[i]);
+    sp.peer_flag[i] = reinterpret_cast<int*>(pf[i]);
+  }
+  sp.my_flags = reinterpret_cast<const int*>(g["my_flags_ptr"].cast<int64_t>());
+  sp.out = reinterpret_cast<void*>(g["out_ptr"].cast<int64_t>());
+  sp.cta_counter = reinterpret_cast<int*>(g["cta_counter_ptr"].cast<int64_t>());
+  sp.rows_per_chunk = g["rows_per_chunk"].cast<int>();
+  sp.rank = g["rank"].cast<int>();
+  sp.epoch = g["epoch"].cast<int>();
+  return true;
+}
+
+void signal_flags(const std::vector<int64_t>& ptrs, int64_t epoch) {
+  cudaError_t e = hb::signal_flags(ptrs.data(), (int)ptrs.size(), (int)epoch, cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "signal_flags failed: ", cudaGetErrorString(e));
+  hb::launch_counter().fetch_add(1, std::memory_order_relaxed);
+}
+
+void wait_flags(const at::Tensor& flags, int64_t epoch, const c10::optional<at::Tensor>& status) {
+  TORCH_CHECK(flags.is_cuda() && flags.scalar_type() == at::kInt && flags.is_contiguous());
+  c10::cuda::CUDAGuard guard(flags.device());
+  cudaError_t e = hb::wait_flags(flags.data_ptr<int>(), (int)flags.numel(), (int)epoch,
+                                 status_ptr(status), cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "wait_flags failed: ", cudaGetErrorString(e));
+  hb::launch_counter().fetch_add(1, std::memory_order_relaxed);
+}
+
 void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& out, bool a_mn, bool b_mn,
           bool accumulate, int64_t block_n, int64_t max_ctas,
-          const c10::optional<at::Tensor>& status) {
+          const c10::optional<at::Tensor>& status, const c10::optional<py::dict>& gather,
+          const c10::optional<py::dict>& scatter) {
   HB_CHECK_CUDA(a); HB_CHECK_CUDA(b); HB_CHECK_CUDA(out);
   HB_CHECK_BF16(a); HB_CHECK_BF16(b);
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && out.dim() == 2, "gemm wants 2-D tensors");
@@ -44,7 +111,10 @@ void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& out, bool a_mn, 
   const int64_t N = b_mn ? b.size(1) : b.size(0);
   const int64_t Kb = b_mn ? b.size(0) : b.size(1);
   TORCH_CHECK(K == Kb, "gemm inner dimensions differ: ", K, " vs ", Kb);
-  TORCH_CHECK(out.size(0) == M && out.size(1) == N, "gemm output shape mismatch");
+  if (scatter.has_value())
+    TORCH_CHECK(out.size(1) == N && out.is_contiguous(), "scatter mode wants a contiguous [rows, N] partial buffer");
+  else
+    TORCH_CHECK(out.size(0) == M && out.size(1) == N, "gemm output shape mismatch");
   c10::cuda::CUDAGuard guard(a.device());
   hb::GemmArgs g;
   g.a = a.data_ptr(); g.b = b.data_ptr(); g.d = out.data_ptr();
@@ -56,6 +126,10 @@ void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& out, bool a_mn, 
   g.block_n = (int)block_n; g.max_ctas = (int)max_ctas;
   g.status = status_ptr(status);
   g.stream = cur_stream();
+  hb::GatherParams gp;
+  if (fill_gather(gather, gp)) g.gather = &gp;
+  hb::ScatterParams sp;
+  if (fill_scatter(scatter, sp)) g.scatter = &sp;
   cudaError_t err = hb::gemm_bf16(g);
   TORCH_CHECK(err == cudaSuccess, "halite_b200 gemm failed: ", cudaGetErrorString(err), " (M=", M,
               " N=", N, " K=", K, " lda=", g.lda, " ldb=", g.ldb, " ldd=", g.ldd, " a_mn=", a_mn,
@@ -67,13 +141,18 @@ void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& out, bool a_mn, 
 }  // namespace
 
 void register_elementwise(pybind11::module_& m);  // ops_bindings.cpp
+void register_infer(pybind11::module_& m);        // infer_bindings.cpp
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, "bf16 tcgen05 GEMM", py::arg("a"), py::arg("b"), py::arg("out"),
         py::arg("a_mn") = false, py::arg("b_mn") = false, py::arg("accumulate") = false,
-        py::arg("block_n") = 0, py::arg("max_ctas") = 0, py::arg("status") = py::none());
+        py::arg("block_n") = 0, py::arg("max_ctas") = 0, py::arg("status") = py::none(),
+        py::arg("gather") = py::none(), py::arg("scatter") = py::none());
+  m.def("signal_flags", &signal_flags, "write epoch to flag words (possibly in peer memory)");
+  m.def("wait_flags", &wait_flags, py::arg("flags"), py::arg("epoch"), py::arg("status") = py::none());
   m.def("launch_count", []() { return hb::launch_counter().load(); },
         "kernel launches issued through this extension so far");
   m.def("reset_launch_count", []() { hb::launch_counter().store(0); });
   register_elementwise(m);
+  register_infer(m);
 }

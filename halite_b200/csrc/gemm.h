@@ -7,6 +7,55 @@
 
 namespace hb {
 
+constexpr int kMaxPeers = 8;
+
+// Side job that a GEMM launch can carry: a few CTAs copy `n_chunks` equal chunks (each from a
+// peer GPU's memory, or from local memory) into one contiguous local destination while the
+// remaining CTAs compute; a tile whose operand rows lie in the destination waits only for the
+// granules it reads. This is how an all-gather is fused into the GEMM that consumes it:
+//   dep = 1: the A operand (M rows) is the gathered buffer  (TP all-gather -> GEMM)
+//   dep = 2: the B operand (N rows) lies inside the gathered buffer (FSDP parameter all-gather
+//            fused into the first GEMM that uses the unit's parameters)
+// Remote data is pulled with plain loads into local memory and fed to the tensor cores by TMA
+// from there; no TMA load ever names remote memory.
+struct GatherParams {
+  const void* src[kMaxPeers] = {};   // chunk i comes from src[i]; nullptr = already in place
+  int* peer_done[kMaxPeers] = {};    // written with `epoch` (system scope) once chunk i was read
+  void* dst_base = nullptr;          // chunk i lands at dst_base + i * chunk_bytes
+  long chunk_bytes = 0;
+  long granule_bytes = 0;            // flag granularity (multiple of 16)
+  int n_chunks = 0;
+  int n_copy_ctas = 0;
+  int* flags = nullptr;              // [n_chunks * granules_per_chunk] local; set to `epoch`
+  const int* ready = nullptr;        // [n_chunks] local; chunk i may be read once ready[i] >= epoch
+  int* done_counter = nullptr;       // local scratch counter (zeroed by the launcher)
+  int epoch = 1;
+  int dep = 0;
+  long dep_row_bytes = 0;            // bytes between consecutive operand rows in the destination
+  long dep_base_offset = 0;          // byte offset of operand row 0 inside the destination
+  int m_rot = 0;                     // first M tile to compute (start on the local chunk)
+  int first_chunk = 0;               // chunk handled first by the copy CTAs (the local one)
+};
+
+// Fused GEMM -> reduce-scatter over the M dimension. Output rows are split into `n_chunks`
+// equal chunks, chunk c belonging to rank c. The epilogue stores each tile straight to its
+// owner: the local partial buffer for the own chunk, the owner's receive slot (peer memory)
+// for the others. When all tiles are out, the CTAs tell every peer (one flag each), wait for
+// the peers' flags and sum own partial + received partials into `out` (bf16), all in the same
+// launch. `dst` / `recv` buffers are bf16 [rows_per_chunk, N] with leading dimension N.
+struct ScatterParams {
+  void* dst[kMaxPeers] = {};        // where this rank's partial of chunk c goes (peer memory for c != rank)
+  const void* recv[kMaxPeers] = {}; // local slots holding rank p's partial of this rank's chunk (nullptr for p == rank)
+  int* peer_flag[kMaxPeers] = {};   // flag word on rank p that announces "my partials for you are written"
+  const int* my_flags = nullptr;    // local flag words, one per peer, written by the peers
+  void* out = nullptr;              // [rows_per_chunk, N] bf16 reduced result
+  int* cta_counter = nullptr;       // local scratch (zeroed by the launcher)
+  int rows_per_chunk = 0;
+  int n_chunks = 0;                 // 0 = scatter disabled
+  int rank = 0;
+  int epoch = 1;
+};
+
 struct GemmArgs {
   const void* a = nullptr;  // bf16
   const void* b = nullptr;  // bf16
@@ -20,10 +69,14 @@ struct GemmArgs {
   int block_n = 0;          // 0 = choose, else 128 or 256
   int max_ctas = 0;         // 0 = one per SM; >0 caps the grid (leaves SMs for a concurrent copy)
   int* status = nullptr;    // device int: set to a WaitCode when a bounded wait gave up
+  const GatherParams* gather = nullptr;  // optional fused gather (see above)
+  const ScatterParams* scatter = nullptr;  // optional fused reduce-scatter (bf16 output only)
   cudaStream_t stream = nullptr;
 };
 
 cudaError_t gemm_bf16(const GemmArgs& args);
+cudaError_t signal_flags(const int64_t* ptrs, int n, int epoch, cudaStream_t stream);
+cudaError_t wait_flags(const int* flags, int n, int epoch, int* status, cudaStream_t stream);
 int gemm_pick_bn(int M, int N);
 
 bool make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,

@@ -127,11 +127,123 @@ __device__ __forceinline__ void store_chunk<float>(float* __restrict__ p, const 
   }
 }
 
+// ---- fused gather helpers ------------------------------------------------------------
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(int* p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Bounded spin until *flag >= want. `sys` selects system scope (flags written by other GPUs).
+__device__ __forceinline__ bool wait_flag(const int* flag, int want, bool sys,
+                                          volatile int* abort_flag, int* status) {
+  unsigned long long t0 = 0;
+  uint32_t spins = 0;
+  while (true) {
+    const int v = sys ? ld_acquire_sys(flag) : ld_acquire_gpu(flag);
+    if (v >= want) return true;
+    if ((++spins & 0xff) == 0) {
+      if (*abort_flag) return false;
+      const unsigned long long now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > kWaitBudgetNs) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, 0, (int)kTimeoutPeerFlag);
+        return false;
+      }
+    }
+    __nanosleep(64);
+  }
+}
+
+// Wait for the granules covering operand rows [row0, row0 + nrows) of the gathered buffer.
+__device__ __forceinline__ bool wait_rows(const GatherParams& gp, long row0, long nrows, long total_rows,
+                                          volatile int* abort_flag, int* status) {
+  const long r1 = min(row0 + nrows, total_rows);
+  if (r1 <= row0) return true;
+  const long lo = gp.dep_base_offset + row0 * gp.dep_row_bytes;
+  const long hi = gp.dep_base_offset + r1 * gp.dep_row_bytes - 1;
+  const long total = gp.chunk_bytes * gp.n_chunks;
+  if (hi < 0 || lo >= total) return true;
+  const long g0 = max(lo, 0L) / gp.granule_bytes;
+  const long g1 = min(hi, total - 1) / gp.granule_bytes;
+  for (long g = g0; g <= g1; ++g)
+    if (!wait_flag(gp.flags + g, gp.epoch, false, abort_flag, status)) return false;
+  return true;
+}
+
+// Body of a copy CTA: granules are dealt round-robin over the copy CTAs, in address order.
+__device__ __forceinline__ void gather_copy_cta(const GatherParams& gp, int cta, volatile int* abort_flag,
+                                                int* status) {
+  const long gpc = (gp.chunk_bytes + gp.granule_bytes - 1) / gp.granule_bytes;  // granules per chunk
+  const long n_gran = gpc * gp.n_chunks;
+  __shared__ int s_ok;
+  // Chunks are visited in the order the tiles consume them: the local chunk first (nothing to
+  // copy, its flags go up at once), then the following ranks' chunks, so each GPU starts on a
+  // different peer.
+  for (long it = cta; it < n_gran; it += gp.n_copy_ctas) {
+    const int chunk = static_cast<int>((it / gpc + gp.first_chunk) % gp.n_chunks);
+    const long off = (it % gpc) * gp.granule_bytes;
+    const long gi = chunk * gpc + it % gpc;
+    const long bytes = min(gp.granule_bytes, gp.chunk_bytes - off);
+    if (gp.src[chunk] != nullptr) {
+      if (threadIdx.x == 0) {
+        s_ok = 1;
+        if (gp.ready && !wait_flag(gp.ready + chunk, gp.epoch, true, abort_flag, status)) s_ok = 0;
+      }
+      __syncthreads();
+      if (s_ok) {
+        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(gp.src[chunk]) + off);
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(gp.dst_base) + chunk * gp.chunk_bytes + off);
+        const long n16 = bytes >> 4;
+        long i = threadIdx.x;
+        for (; i + 3 * blockDim.x < n16; i += 4 * blockDim.x) {
+          const uint4 a = src[i], b = src[i + blockDim.x], c = src[i + 2 * blockDim.x],
+                      d = src[i + 3 * blockDim.x];
+          dst[i] = a;
+          dst[i + blockDim.x] = b;
+          dst[i + 2 * blockDim.x] = c;
+          dst[i + 3 * blockDim.x] = d;
+        }
+        for (; i < n16; i += blockDim.x) dst[i] = src[i];
+      }
+      __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+      __threadfence();
+      st_release_gpu(gp.flags + gi, gp.epoch);
+    }
+  }
+  // the last copy CTA to finish tells every source owner that its chunk has been read
+  __syncthreads();
+  if (threadIdx.x == 0 && gp.done_counter) {
+    __threadfence();
+    const int prev = atomicAdd(gp.done_counter, 1);
+    if (prev == gp.n_copy_ctas - 1) {
+      for (int c = 0; c < gp.n_chunks; ++c)
+        if (gp.peer_done[c]) st_release_sys(gp.peer_done[c], gp.epoch);
+    }
+  }
+}
+
 template <int BN, bool A_MN, bool B_MN, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
                  const __grid_constant__ CUtensorMap tma_b, OutT* __restrict__ D, int M, int N,
-                 int K, int ldd, int accumulate, int* __restrict__ status) {
+                 int K, int ldd, int accumulate, int* __restrict__ status,
+                 const __grid_constant__ GatherParams gp,
+                 const __grid_constant__ ScatterParams sp) {
   using C = Cfg<BN>;
   constexpr int kStages = C::kStages;
 
@@ -175,15 +287,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
 
-  if (warp == 0 && lane == 0) {
+  // With a fused gather the first `n_copy` CTAs only copy; the rest share the tiles.
+  const int n_copy = gp.n_copy_ctas;
+  const int first_tile = static_cast<int>(blockIdx.x) - n_copy;
+  const int tile_step = static_cast<int>(gridDim.x) - n_copy;
+
+  if (first_tile < 0) {
+    gather_copy_cta(gp, blockIdx.x, &abort_flag, status);
+  } else if (warp == 0 && lane == 0) {
     // ------------------------------------------------------------ producer
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
       int tm, tn;
       tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      if (gp.m_rot) tm = (tm + gp.m_rot) % tiles_m;
       const int m0 = tm * kBM, n0 = tn * BN;
+      if (gp.dep == 1) ok = wait_rows(gp, m0, kBM, M, &abort_flag, status);
+      if (gp.dep == 2) ok = wait_rows(gp, n0, BN, N, &abort_flag, status);
+      if (!ok) break;
+      if (gp.dep) fence_proxy_async();  // copied data was written by generic stores; TMA reads it
       for (int kb = 0; kb < num_kb; ++kb) {
         ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1, &abort_flag, status, kTimeoutEmpty);
         if (!ok) break;
@@ -210,14 +334,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
         }
       }
     }
-  } else if (warp == 1 && lane == 0) {
+  } else if (first_tile >= 0 && warp == 1 && lane == 0) {
     // ------------------------------------------------------------ MMA issuer
     constexpr uint32_t idesc = make_idesc_bf16(kBM, BN, A_MN, B_MN);
     int stage = 0;
     uint32_t phase = 0;
     int local = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+    for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++local) {
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       ok = mbar_wait(smem_u32(&bar_tempty[acc]), acc_phase ^ 1, &abort_flag, status,
@@ -248,16 +372,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
       }
       if (ok) umma_commit(smem_u32(&bar_tfull[acc]));  // accumulator ready for the epilogue
     }
-  } else if (warp >= 4) {
+  } else if (first_tile >= 0 && warp >= 4) {
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const bool vec_ok = (ldd % (16 / (int)sizeof(OutT)) == 0) &&
                         ((reinterpret_cast<uintptr_t>(D) & 15) == 0);
     int local = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+    for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++local) {
       int tm, tn;
       tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      if (gp.m_rot) tm = (tm + gp.m_rot) % tiles_m;
       const int m0 = tm * kBM, n0 = tn * BN;
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
@@ -274,13 +399,79 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
         tmem_ld_wait();
         const int col = n0 + c * 32;
         if (row < M && col < N) {
-          store_chunk<OutT>(D + static_cast<size_t>(row) * ldd + col, v, min(32, N - col), vec_ok,
-                            accumulate != 0);
+          OutT* base = D + static_cast<size_t>(row) * ldd;
+          bool vok = vec_ok;
+          if (sp.n_chunks > 0) {
+            // reduce-scatter: the row's owner receives this partial directly
+            const int owner = row / sp.rows_per_chunk;
+            base = static_cast<OutT*>(sp.dst[owner]) +
+                   static_cast<size_t>(row - owner * sp.rows_per_chunk) * ldd;
+            vok = (ldd % (16 / (int)sizeof(OutT)) == 0) && ((reinterpret_cast<uintptr_t>(base) & 15) == 0);
+          }
+          store_chunk<OutT>(base + col, v, min(32, N - col), vok, accumulate != 0 && sp.n_chunks == 0);
         }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[acc]));
+    }
+  }
+
+  if (sp.n_chunks > 0 && first_tile >= 0) {
+    // ---- reduce-scatter tail: announce, wait for the peers, reduce the own chunk
+    __threadfence_system();  // every thread: its tile stores (some to peer memory) are visible
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      const int prev = atomicAdd(sp.cta_counter, 1);
+      if (prev == tile_step - 1) {
+        for (int p = 0; p < sp.n_chunks; ++p)
+          if (p != sp.rank && sp.peer_flag[p]) st_release_sys(sp.peer_flag[p], sp.epoch);
+      }
+      bool ok = true;
+      for (int p = 0; p < sp.n_chunks && ok; ++p)
+        if (p != sp.rank) ok = wait_flag(sp.my_flags + p, sp.epoch, true, &abort_flag, status);
+      // the own partial is complete once every local CTA has passed the counter
+      if (ok) ok = wait_flag(sp.cta_counter, tile_step, false, &abort_flag, status);
+    }
+    __syncthreads();
+    if (!abort_flag) {
+      if constexpr (sizeof(OutT) == 2) {
+        const long nvec = static_cast<long>(sp.rows_per_chunk) * N / 8;  // N % 8 == 0 is required
+        const uint4* own = reinterpret_cast<const uint4*>(sp.dst[sp.rank]);
+        uint4* outp = reinterpret_cast<uint4*>(sp.out);
+        for (long i = static_cast<long>(first_tile) * kThreads + threadIdx.x; i < nvec;
+             i += static_cast<long>(tile_step) * kThreads) {
+          float f[8];
+          {
+            const uint4 raw = own[i];
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 t = __bfloat1622float2(h2[j]);
+              f[2 * j] = t.x;
+              f[2 * j + 1] = t.y;
+            }
+          }
+          for (int p = 0; p < sp.n_chunks; ++p) {
+            if (p == sp.rank) continue;
+            const uint4 raw = reinterpret_cast<const uint4*>(sp.recv[p])[i];
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 t = __bfloat1622float2(h2[j]);
+              f[2 * j] += t.x;
+              f[2 * j + 1] += t.y;
+            }
+          }
+          uint4 o;
+          o.x = pack_bf16x2(f[0], f[1]);
+          o.y = pack_bf16x2(f[2], f[3]);
+          o.z = pack_bf16x2(f[4], f[5]);
+          o.w = pack_bf16x2(f[6], f[7]);
+          outp[i] = o;
+        }
+      }
     }
   }
 
@@ -384,10 +575,30 @@ cudaError_t launch(const GemmArgs& g) {
   }
   (void)cudaGetLastError();  // do not report an error left behind by an earlier, unrelated call
   const int tiles = ((g.M + kBM - 1) / kBM) * ((g.N + BN - 1) / BN);
-  int grid = tiles < sm_count() ? tiles : sm_count();
-  if (g.max_ctas > 0 && grid > g.max_ctas) grid = g.max_ctas;
+  GatherParams gp;
+  if (g.gather) gp = *g.gather;
+  int grid;
+  if (gp.n_copy_ctas > 0) {
+    // every CTA must be resident at once (compute CTAs wait on copy CTAs): one CTA per SM
+    if (gp.n_copy_ctas >= sm_count() || gp.granule_bytes % 16 || gp.chunk_bytes % 16)
+      return cudaErrorInvalidValue;
+    const int compute = tiles < sm_count() - gp.n_copy_ctas ? tiles : sm_count() - gp.n_copy_ctas;
+    grid = compute + gp.n_copy_ctas;
+    if (gp.done_counter) cudaMemsetAsync(gp.done_counter, 0, sizeof(int), g.stream);
+  } else {
+    grid = tiles < sm_count() ? tiles : sm_count();
+    if (g.max_ctas > 0 && grid > g.max_ctas) grid = g.max_ctas;
+  }
+  ScatterParams sp;
+  if (g.scatter) {
+    sp = *g.scatter;
+    if (sizeof(OutT) != 2 || sp.n_chunks > kMaxPeers || g.N % 8 || g.ldd != g.N ||
+        sp.rows_per_chunk * sp.n_chunks != g.M || !sp.cta_counter)
+      return cudaErrorInvalidValue;
+    cudaMemsetAsync(sp.cta_counter, 0, sizeof(int), g.stream);
+  }
   kern<<<grid, kThreads, C::kSmemBytes, g.stream>>>(ta, tb, static_cast<OutT*>(g.d), g.M, g.N, g.K,
-                                                    g.ldd, g.accumulate ? 1 : 0, g.status);
+                                                    g.ldd, g.accumulate ? 1 : 0, g.status, gp, sp);
   return cudaGetLastError();
 }
 
@@ -400,6 +611,48 @@ cudaError_t dispatch_layout(const GemmArgs& g) {
 }
 
 }  // namespace
+
+namespace {
+
+struct FlagPtrs {
+  int* p[kMaxPeers * 2];
+};
+
+__global__ void signal_flags_kernel(FlagPtrs ptrs, int n, int epoch) {
+  if (threadIdx.x < n && ptrs.p[threadIdx.x]) {
+    __threadfence_system();
+    st_release_sys(ptrs.p[threadIdx.x], epoch);
+  }
+}
+
+__global__ void wait_flags_kernel(const int* flags, int n, int epoch, int* status) {
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) abort_flag = 0;
+  __syncthreads();
+  if (threadIdx.x < n) wait_flag(flags + threadIdx.x, epoch, true, &abort_flag, status);
+}
+
+}  // namespace
+
+// Write `epoch` (system scope, after a system fence) to up to 16 flag words, which may live in
+// peer memory. Stream-ordered: everything enqueued before it on `stream` is visible first.
+cudaError_t signal_flags(const int64_t* ptrs, int n, int epoch, cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  if (n > kMaxPeers * 2) return cudaErrorInvalidValue;
+  FlagPtrs fp = {};
+  for (int i = 0; i < n; ++i) fp.p[i] = reinterpret_cast<int*>(ptrs[i]);
+  signal_flags_kernel<<<1, 32, 0, stream>>>(fp, n, epoch);
+  return cudaGetLastError();
+}
+
+// Block the stream until flags[0..n) >= epoch (bounded: records kTimeoutPeerFlag in *status
+// and returns after the wait budget instead of spinning forever).
+cudaError_t wait_flags(const int* flags, int n, int epoch, int* status, cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  if (n > 32) return cudaErrorInvalidValue;
+  wait_flags_kernel<<<1, 32, 0, stream>>>(flags, n, epoch, status);
+  return cudaGetLastError();
+}
 
 int gemm_pick_bn(int M, int N) {
   if (N <= 128) return 128;

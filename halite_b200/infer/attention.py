@@ -15,8 +15,12 @@ from torch import nn
 
 from halite_b200 import ops
 from halite_b200.models.initialize import init_weights
-from halite_b200.models.position import RotaryTable
+from halite_b200.models.position import RotaryTable, apply_rotary_emb
 from halite_b200.ops import paged_attention as pa
+
+
+def _is_plain_rope(fn):
+    return getattr(fn, "func", fn) is apply_rotary_emb
 
 
 class PagedAttention(nn.Module):
@@ -50,10 +54,16 @@ class PagedAttention(nn.Module):
             q = self.q_norm(q)
         if self.k_norm is not None:
             k = self.k_norm(k)
-        if self.apply_pos_emb_fn is not None and pos_embed is not None:
-            q, k = self.apply_pos_emb_fn(q, k, pos_embed)
         k_cache, v_cache = self.kv_pool.get_kv_buffer(self.layer_id)
-        pa.append_kv(k_cache, v_cache, k, v, forward_batch.out_cache_loc)
+        rope = self.apply_pos_emb_fn is not None and pos_embed is not None
+        if rope and isinstance(pos_embed, RotaryTable) and _is_plain_rope(self.apply_pos_emb_fn) \
+                and ops.use_sm100(q) and k_cache.dtype == torch.bfloat16:
+            # one kernel: rotate q in place, rotate k on its way into the pages, copy v
+            q = pa.rope_append(q, k, v, k_cache, v_cache, pos_embed, forward_batch.out_cache_loc)
+        else:
+            if rope:
+                q, k = self.apply_pos_emb_fn(q, k, pos_embed)
+            pa.append_kv(k_cache, v_cache, k, v, forward_batch.out_cache_loc)
         if forward_batch.mode.is_decode():
             out = pa.paged_decode_attention(q, k_cache, v_cache, forward_batch, self.normalize,
                                             self.softcap, self.window_size,

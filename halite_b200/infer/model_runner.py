@@ -43,9 +43,12 @@ class ModelRunner:
         self.page_size = server_config.page_size
         dtype = model_config.kv_cache_dtype
         if dtype == "auto":
-            dtype = getattr(model, "dtype", torch.float32)
-            if dtype is None or (self.device.type == "cuda" and dtype == torch.float32 and False):
-                dtype = torch.bfloat16
+            # the model is usually still on the meta device here: bf16 on a GPU, fp32 on CPU
+            first = next((p for p in model.parameters() if p.is_floating_point()), None)
+            if first is not None and not first.is_meta:
+                dtype = first.dtype
+            else:
+                dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
         self.kv_cache_dtype = get_torch_dtype(dtype)
         self.req_pool = None
         self.kv_pool = None

@@ -158,6 +158,20 @@ class GatedFeedForward(nn.Module):
     def fusable_linears(self):
         return {"proj_gate": ("linear_proj", "linear_gate")}
 
+    def pack_weights(self):
+        """Inference: copy [up | gate] into one matrix (the two parameters become views of it)
+        so both projections are a single GEMM."""
+        from torch import nn as _nn
+
+        ws = [self.linear_proj.weight, self.linear_gate.weight]
+        if self.linear_proj.bias is not None or self.linear_gate.bias is not None or ws[0].is_meta:
+            return
+        packed = torch.cat([w.detach() for w in ws], 0).contiguous()
+        n = ws[0].shape[0]
+        self.linear_proj.weight = _nn.Parameter(packed[:n], requires_grad=False)
+        self.linear_gate.weight = _nn.Parameter(packed[n:], requires_grad=False)
+        self._hb_fused = {"proj_gate": packed}
+
     def _act_kind(self):
         if isinstance(self.activation, nn.SiLU):
             return "silu"

@@ -18,7 +18,7 @@ import halite_b200.ops as ops
 
 
 def gemm(a, b, out=None, a_mn=False, b_mn=False, accumulate=False, out_dtype=None, block_n=0,
-         max_ctas=0):
+         max_ctas=0, gather=None, scatter=None):
     """out[M,N] (+)= op(a) @ op(b)^T on the sm_100a kernel.
 
     a: [M,K] (or [K,M] when a_mn); b: [N,K] (or [K,N] when b_mn); all bf16, row-major with
@@ -28,7 +28,8 @@ def gemm(a, b, out=None, a_mn=False, b_mn=False, accumulate=False, out_dtype=Non
     N = b.shape[1] if b_mn else b.shape[0]
     if out is None:
         out = torch.empty(M, N, device=a.device, dtype=out_dtype or torch.bfloat16)
-    ops.ext().gemm(a, b, out, a_mn, b_mn, accumulate, block_n, max_ctas, ops.status_word(a.device))
+    ops.ext().gemm(a, b, out, a_mn, b_mn, accumulate, block_n, max_ctas, ops.status_word(a.device),
+                   gather, scatter)
     return out
 
 

@@ -20,12 +20,29 @@ from halite_b200.ops.attention import attention_reference
 def append_kv(k_cache, v_cache, k, v, out_cache_loc):
     """Write new keys / values ([T, Hk, D]) to their flat slots (page * page_size + offset)."""
     if ops.use_sm100(k) and k_cache.dtype == torch.bfloat16:
-        ops.ext().kv_append(k_cache, v_cache, k, v, out_cache_loc)
+        kk = k if (k.stride(-1) == 1 and k.stride(-2) == k.shape[-1]) else k.contiguous()
+        vv = v if (v.stride(-1) == 1 and v.stride(-2) == v.shape[-1]) else v.contiguous()
+        ops.ext().kv_append(k_cache, v_cache, kk, vv, out_cache_loc)
         return
     kc = k_cache.view(-1, *k_cache.shape[2:])
     vc = v_cache.view(-1, *v_cache.shape[2:])
     kc[out_cache_loc] = k.to(kc.dtype)
     vc[out_cache_loc] = v.to(vc.dtype)
+
+
+def rope_append(q, k, v, k_cache, v_cache, table, out_cache_loc):
+    """Fused RoPE + append on the sm_100a path: q [T, Hq, D] is rotated in place (and returned),
+    k is rotated while it is written to its page slots, v is copied."""
+    def packed(t):
+        return t if (t.stride(-1) == 1 and t.stride(-2) == t.shape[-1]) else t.contiguous()
+
+    q, k, v = packed(q), packed(k), packed(v)
+    pos = table.positions.reshape(-1)
+    if pos.dtype != torch.int64:
+        pos = pos.long()
+    ops.ext().rope_append(q, k, v, k_cache, v_cache, table.cos, table.sin, pos.contiguous(),
+                          out_cache_loc, table.interleaved)
+    return q
 
 
 def gather_request_kv(k_cache, v_cache, page_table_row, seq_len, page_size):
@@ -60,7 +77,9 @@ def paged_prefill_attention(q, k_cache, v_cache, fb, scale=None, softcap=0.0, wi
     if ops.use_sm100(q) and k_cache.dtype == torch.bfloat16 and not softcap and window is None \
             and q.shape[-1] in (64, 128):
         scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
-        out = torch.empty_like(q)
+        if not (q.stride(-1) == 1 and q.stride(-2) == q.shape[-1]):
+            q = q.contiguous()
+        out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
         ops.ext().paged_prefill(q, k_cache, v_cache, out, fb.page_table, fb.req_slots, fb.qo_indptr,
                                 fb.seq_lens, fb.max_extend_len, float(scale))
         return out
@@ -71,7 +90,9 @@ def paged_decode_attention(q, k_cache, v_cache, fb, scale=None, softcap=0.0, win
     if ops.use_sm100(q) and k_cache.dtype == torch.bfloat16 and not softcap and window is None \
             and q.shape[-1] in (64, 128):
         scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
-        out = torch.empty_like(q)
+        if not (q.stride(-1) == 1 and q.stride(-2) == q.shape[-1]):
+            q = q.contiguous()
+        out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
         ops.ext().paged_decode(q, k_cache, v_cache, out, fb.page_table, fb.req_slots, fb.seq_lens,
                                workspace, float(scale))
         return out
