@@ -171,6 +171,30 @@ class _SelfAttentionBase(nn.Module):
         return ops.linear(out, self.out.weight, self.out.bias)
 
 
+def _tp_attention(module, input, pos_emb, qkv_weights):
+    """Tensor-parallel attention on a token shard: all-gather fused into the (first) projection,
+    attention over this rank's heads, output projection fused with the reduce-scatter."""
+    from halite_b200.parallel.tensor_parallel import ag_linear, linear_rs
+
+    tp = module._hb_tp
+    B, S = tp.batch_shape
+    a = module.attention
+    x = input.reshape(-1, input.shape[-1])
+    # separate q / k / v parameters that are not contiguous in memory are concatenated so the
+    # gathered input feeds one GEMM and its gradient flows back through one reduce-scatter
+    w = qkv_weights[0] if len(qkv_weights) == 1 else torch.cat(list(qkv_weights), 0)
+    qkv, _ = ag_linear(x, w, tp)
+    qkv = qkv.view(B, S, -1)
+    if pos_emb is not None and a.apply_pos_emb_fn is not None:
+        out = attn_ops.packed_qkv_attention(qkv, a.n_heads, a.kv_heads, a.head_dim, pos_emb.cos, pos_emb.sin,
+                                            pos_emb.positions, pos_emb.interleaved, a.is_causal, a.normalize)
+    else:
+        out = attn_ops.packed_qkv_attention(qkv, a.n_heads, a.kv_heads, a.head_dim, causal=a.is_causal,
+                                            scale=a.normalize)
+    out = linear_rs(out.reshape(B * S, -1), module.out.weight, tp)
+    return out.view(1, -1, out.shape[-1])
+
+
 class SelfAttention(_SelfAttentionBase):
     """Fused qkv projection. `qkv_split="llama"`: rows are [q | k | v]; `"megatron"`: rows are
     grouped per KV head as [q_group, k, v]."""
@@ -208,6 +232,8 @@ class SelfAttention(_SelfAttentionBase):
     def forward(self, input, attention_mask=None, attention_bias=None, pos_emb=None, cache=None,
                 use_cache=False, unpad_params=None):
         attention_mask, attention_bias, pos_emb = self._select_layer_type(attention_mask, attention_bias, pos_emb)
+        if getattr(self, "_hb_tp", None) is not None:
+            return _tp_attention(self, input, pos_emb, [self.qkv.weight]), None
         if self.qkv_split == "llama" and self._packed_ok(input, attention_mask, attention_bias, pos_emb,
                                                          cache, use_cache, unpad_params):
             return self._packed_forward(input, self.qkv.weight, self.qkv.bias, pos_emb), None
@@ -252,6 +278,9 @@ class SelfAttentionQKV(_SelfAttentionBase):
                 use_cache=False, unpad_params=None):
         attention_mask, attention_bias, pos_emb = self._select_layer_type(attention_mask, attention_bias, pos_emb)
         fused = getattr(self, "_hb_fused", {}).get("qkv")
+        if getattr(self, "_hb_tp", None) is not None:
+            ws = [fused] if fused is not None else [self.q.weight, self.k.weight, self.v.weight]
+            return _tp_attention(self, input, pos_emb, ws), None
         if fused is not None and self.q_norm is None and self.k_norm is None and \
                 self._packed_ok(input, attention_mask, attention_bias, pos_emb, cache, use_cache, unpad_params):
             return self._packed_forward(input, fused, None, pos_emb), None

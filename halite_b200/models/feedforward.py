@@ -125,6 +125,14 @@ class FeedForward(nn.Module):
         init_weights(self.linear2, self.linear2_init)
 
     def forward(self, input):
+        tp = getattr(self, "_hb_tp", None)
+        if tp is not None:
+            from halite_b200.parallel.tensor_parallel import ag_linear, linear_rs
+
+            x = input.reshape(-1, input.shape[-1])
+            h, _ = ag_linear(x, self.linear1.weight, tp)
+            out = linear_rs(self.activation(h), self.linear2.weight, tp)
+            return out.view(1, -1, out.shape[-1])
         out = ops.linear(input, self.linear1.weight, self.linear1.bias)
         out = self.activation(out)
         out = self.dropout(out)
@@ -182,6 +190,20 @@ class GatedFeedForward(nn.Module):
     def forward(self, input):
         kind = self._act_kind()
         fused = getattr(self, "_hb_fused", {}).get("proj_gate")
+        tp = getattr(self, "_hb_tp", None)
+        if tp is not None:
+            from halite_b200.parallel.tensor_parallel import ag_linear, linear_rs
+
+            x = input.reshape(-1, input.shape[-1])
+            w = fused if fused is not None else torch.cat([self.linear_proj.weight, self.linear_gate.weight], 0)
+            pg, _ = ag_linear(x, w, tp)
+            if kind is not None:
+                act = gated_act_packed(pg, kind, gate_first=False)
+            else:
+                proj, gate = pg.chunk(2, -1)
+                act = proj * self.activation(gate)
+            out = linear_rs(act, self.linear_out.weight, tp)
+            return out.view(1, -1, out.shape[-1])
         if fused is not None and kind is not None and ops.use_sm100(input):
             # one GEMM for [up | gate], one pass for act(gate) * up
             pg = ops.linear(input, fused)

@@ -11,6 +11,7 @@ from typing import Any
 import torch
 from torch import nn, utils
 
+from halite_b200.ops import linear as ops_linear
 from halite_b200.models.container import ModuleDict
 from halite_b200.models.model import ModelMixin
 from halite_b200.models.types import TransformerDecoderOutput
@@ -122,9 +123,54 @@ class TransformerDecoder(nn.Module, ModelMixin):
             blocked = attention_mask
         return blocked if extra is None else blocked | extra
 
+    def _forward_tp(self, tp, input_ids, position_ids, target):
+        """Tensor-parallel causal-LM forward: activations between blocks are token shards
+        [1, tokens / tp, dim]; the loss is computed vocabulary-parallel."""
+        from halite_b200.parallel import tensor_parallel as TP
+
+        B, S = input_ids.shape
+        tp.batch_shape = (B, S)
+        emb = self.embedding.get_input_embeddings()
+        out = TP.vocab_parallel_embedding(input_ids, emb.weight, tp)
+        mult = getattr(self.embedding, "multiplier", None)
+        if mult is not None:
+            out = out * mult
+        out = out.unsqueeze(0)
+        if self.use_position_ids and position_ids is None:
+            position_ids = torch.arange(S, device=out.device).unsqueeze(0)
+        pos_emb = None
+        if self.pos_embed is not None and not self.pos_embed_attention_bias:
+            pos_emb = self.pos_embed(position_ids, S, None, out.device, out.dtype)
+        hooks = self.block_hooks
+        residual = None
+        for key, block in self.blocks.items():
+            i = int(key)
+            if hooks is not None:
+                out = hooks[0](i, out)
+            out, residual, _, _ = block(out, residual, None, None, pos_emb=pos_emb, use_cache=False)
+            if hooks is not None:
+                out = hooks[1](i, out)
+        if self.post_blocks is not None:
+            out = self.post_blocks(out)
+        hidden = TP.gather_rows(out.reshape(-1, out.shape[-1]), tp)          # [B*S, dim]
+        if self.head is None:
+            return TransformerDecoderOutput(last_hidden_state=hidden.view(B, S, -1))
+        weight = self.head.weight
+        if target is not None:
+            losses = TP.vocab_parallel_cross_entropy(hidden, weight, target.reshape(-1), tp,
+                                                     getattr(self.head, "ignore_index", -100))
+            loss = losses.mean()
+            return TransformerDecoderOutput(loss=loss, loss_dict={"cross entropy": loss.detach()})
+        local = ops_linear(hidden, weight)                                   # [B*S, vocab / tp]
+        logits = TP.gather_cols(local, tp).view(B, S, -1)
+        return TransformerDecoderOutput(logits=logits)
+
     def forward(self, input_ids=None, attention_mask=None, position_ids=None, images=None, cache=None,
                 use_cache=False, output_hidden_states=False, bidirection_ids=None,
                 document_offsets=None, target=None, unpad_params=None):
+        tp = getattr(self, "_hb_tp", None)
+        if tp is not None:
+            return self._forward_tp(tp, input_ids, position_ids, target)
         emb_in = {}
         if input_ids is not None:
             emb_in["input_ids"] = input_ids

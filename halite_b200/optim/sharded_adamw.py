@@ -111,6 +111,20 @@ def clip_grad_norm_(model, max_norm, optimizer=None, norm_type=2.0):
     total = torch.zeros(1, dtype=torch.float32, device=dev)
     for u in fsdp.units:
         ops.grad_sumsq(u.grad_shard, total)
+    tp = getattr(model, "_hb_tp", None)
+    if tp is not None and tp.size > 1:
+        # parameters replicated over tensor-parallel ranks must count once, sharded ones on
+        # every rank: discount the replicated part before summing over the TP group
+        rep = torch.zeros(1, dtype=torch.float32, device=dev)
+        for u in fsdp.units:
+            for m, n, _, off, numel in u.entries:
+                if getattr(m._parameters[n], "_hb_tp_replicated", None) is None:
+                    continue
+                a, b = max(off, u.lo) - u.lo, min(off + numel, u.hi) - u.lo
+                if b > a:
+                    ops.grad_sumsq(u.grad_shard[a:b], rep)
+        total = total - rep * (1.0 - 1.0 / tp.size)
+        comm.all_reduce(total, tp.group)
     if fsdp.shard_group is not None:
         comm.all_reduce(total, fsdp.shard_group)
     out = torch.empty(2, dtype=torch.float32, device=dev)

@@ -105,6 +105,8 @@ class FlatUnit:
             new_p._hb_grad = self.full_grad[off:off + numel].view(p.shape)
             new_p._hb_grad_owner = self
             new_p._hb_unit_range = (off, numel)
+            if hasattr(p, "_hb_tp_replicated"):
+                new_p._hb_tp_replicated = p._hb_tp_replicated
             # keep initialiser-visible attributes
             m._parameters[n] = new_p
 
@@ -192,6 +194,12 @@ class FlatUnit:
             elif id(p) not in self._written:
                 p._hb_grad.zero_()
         self._written.clear()
+        # parameters replicated over tensor-parallel ranks saw only this rank's token shard
+        for m, n, _, off, numel in self.entries:
+            p = m._parameters[n]
+            tp = getattr(p, "_hb_tp_replicated", None)
+            if tp is not None and tp.size > 1:
+                dist.all_reduce(p._hb_grad, group=tp.group)
         self.start_reduce()
 
     def start_reduce(self):

@@ -66,8 +66,9 @@ class FusedAllGatherGemm:
             ops.ext().wait_flags(flags, self.last_epoch[b], ops.status_word(self.heap.device))
         return self.staging(b)[self.rank * self.rows:(self.rank + 1) * self.rows]
 
-    def __call__(self, weight, out=None, x_shard=None):
-        """weight: [N, K] bf16 (this rank's column shard). Returns [world * rows, N]."""
+    def __call__(self, weight, out=None, x_shard=None, b_mn=False):
+        """weight: [N, K] bf16 (this rank's column shard), or [K, N] with b_mn. Returns
+        [world * rows, N]."""
         b = self._buf()
         if x_shard is not None:
             self.input_slot().copy_(x_shard.reshape(self.rows, self.k))
@@ -90,7 +91,7 @@ class FusedAllGatherGemm:
                 ready_ptr=heap.flag_ptr(r, self.f_ready[b]), done_counter_ptr=self.counter.data_ptr(),
                 epoch=epoch, dep=1, dep_row_bytes=self.k * 2, dep_base_offset=0,
                 m_rot=r * self.rows // _TILE_ROWS, first_chunk=r)
-        y = gemm(staging, weight, out=out, gather=gather)
+        y = gemm(staging, weight, out=out, gather=gather, b_mn=b_mn)
         self.last_epoch[b] = epoch
         self.call += 1
         return y
@@ -112,16 +113,16 @@ class FusedGemmReduceScatter:
         self.counter = torch.zeros(1, dtype=torch.int32, device=dev)
         self.call = 0
 
-    def __call__(self, x, weight, out=None):
-        """x: [world * rows, K_local], weight: [N, K_local]. Returns this rank's reduced
-        [rows, N] shard of x @ weight^T summed over ranks."""
+    def __call__(self, x, weight, out=None, b_mn=False):
+        """x: [world * rows, K_local], weight: [N, K_local] (or [K_local, N] with b_mn). Returns
+        this rank's reduced [rows, N] shard of x @ weight^T summed over ranks."""
         heap, w, r = self.heap, self.world, self.rank
         b = self.call % self.n_buf
         epoch = heap.next_epoch()
         if out is None:
             out = torch.empty(self.rows, self.n, dtype=torch.bfloat16, device=x.device)
         if w == 1:
-            gemm(x, weight, out=out)
+            gemm(x, weight, out=out, b_mn=b_mn)
             self.call += 1
             return out
         off = self.recv_off[b]
@@ -133,6 +134,6 @@ class FusedGemmReduceScatter:
             my_flags_ptr=heap.flag_ptr(r, self.f_flags[b]), out_ptr=out.data_ptr(),
             cta_counter_ptr=self.counter.data_ptr(), rows_per_chunk=self.rows, rank=r, epoch=epoch)
         # the [M, N] `out` argument of the plain GEMM is unused in scatter mode: pass the partial
-        gemm(x, weight, out=self.partial, scatter=scatter)
+        gemm(x, weight, out=self.partial, scatter=scatter, b_mn=b_mn)
         self.call += 1
         return out
