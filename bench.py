@@ -82,7 +82,7 @@ def run_ours(args):
     from halite_b200.conf import instantiate, load_config
     from halite_b200.optim import build_optimizer, cycle_scheduler
     from halite_b200.parallel import ParallelDims, parallelize
-    from halite_b200.projects.common.train_fn import basic_train_step
+    from halite_b200.projects.common.train_fn import optimization_step
     from halite_b200.utils.timing import ClockSampler, DeviceTimer
     from functools import partial
 
@@ -109,7 +109,7 @@ def run_ours(args):
 
     def step(tokens_dev):
         batch = {"input": tokens_dev[:, :-1], "target": tokens_dev[:, 1:]}
-        return basic_train_step(model, batch, optimizer, scheduler, clip_grad_norm=1.0,
+        return optimization_step(model, batch, optimizer, scheduler, clip_grad_norm=1.0,
                                 calc_loss_in_model=True)
 
     # ---- warm-up (untimed)

@@ -111,10 +111,11 @@ void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& out, bool a_mn, 
   const int64_t N = b_mn ? b.size(1) : b.size(0);
   const int64_t Kb = b_mn ? b.size(0) : b.size(1);
   TORCH_CHECK(K == Kb, "gemm inner dimensions differ: ", K, " vs ", Kb);
-  if (scatter.has_value())
+  if (scatter.has_value()) {
     TORCH_CHECK(out.size(1) == N && out.is_contiguous(), "scatter mode wants a contiguous [rows, N] partial buffer");
-  else
+  } else {
     TORCH_CHECK(out.size(0) == M && out.size(1) == N, "gemm output shape mismatch");
+  }
   c10::cuda::CUDAGuard guard(a.device());
   hb::GemmArgs g;
   g.a = a.data_ptr(); g.b = b.data_ptr(); g.d = out.data_ptr();

@@ -76,7 +76,9 @@ class FlatUnit:
             if group is decay:
                 self.decay_end = off
         self.numel = off
-        chunk = self.ws * _ALIGN
+        # padding to a multiple of 8192 as well makes the flat length the same for every
+        # power-of-two shard count up to 64, so optimizer shards reshard without translation
+        chunk = math.lcm(self.ws * _ALIGN, 8192)
         self.padded = max(chunk, (off + chunk - 1) // chunk * chunk)
         self.shard_numel = self.padded // self.ws
         self.lo = self.rank * self.shard_numel

@@ -1,15 +1,41 @@
-"""One optimisation step (reference: projects/common/train_fn.py `basic_train_step`, and the hot
-loop of scripts/lm.py:56-143): forward, loss, backward, gradient clipping, scheduler and
-optimizer step. Returns device tensors only; the caller decides when to read them."""
+"""Step functions.
+
+`basic_train_step(data, model, criterion) -> (loss, loss_dict)` is the pluggable forward + loss
+that experiment configurations name as `train_step_fn` / `eval_step_fn`
+(reference: projects/common/train_fn.py:18-34).
+
+`optimization_step(...)` is a whole update (the hot loop of the reference's scripts/lm.py:56-143):
+forward, loss, backward, gradient clipping, scheduler and optimizer step. It returns device
+tensors only; the caller decides when to read them."""
 
 from __future__ import annotations
+
+from collections.abc import Mapping
 
 import torch
 
 from halite_b200.optim.sharded_adamw import clip_grad_norm_
 
 
-def basic_train_step(model, batch, optimizer, scheduler=None, criterion=None, clip_grad_norm=None,
+def get_fields(record, fields):
+    """{name: value} for one field name or several, from a mapping or an object."""
+    names = [fields] if isinstance(fields, str) else list(fields)
+    if isinstance(record, Mapping):
+        return {n: record[n] for n in names}
+    return {n: getattr(record, n) for n in names}
+
+
+_MODEL_INPUTS = (("input", "input_ids"), ("position_ids", "position_ids"),
+                 ("document_offsets", "document_offsets"))
+
+
+def basic_train_step(data, model, criterion):
+    kwargs = {dst: data[src] for src, dst in _MODEL_INPUTS if src in data}
+    out = model(**kwargs)
+    return criterion(out.logits, data["target"])
+
+
+def optimization_step(model, batch, optimizer, scheduler=None, criterion=None, clip_grad_norm=None,
                      calc_loss_in_model=False, grad_accum_steps=1, input_key="input", target_key="target",
                      aux_loss_weight=1.0):
     """`batch` maps `input_key` / `target_key` to [B, S] token tensors (already on the device).

@@ -54,7 +54,7 @@ def test_smoke_entry():
 
 def test_loss_decreases_on_fixed_batch(zoo):
     from halite_b200.optim import build_optimizer
-    from halite_b200.projects.common.train_fn import basic_train_step
+    from halite_b200.projects.common.train_fn import optimization_step
 
     dev = torch.device("cuda", 0)
     model = _build(zoo, dev)
@@ -62,7 +62,7 @@ def test_loss_decreases_on_fixed_batch(zoo):
     tokens = torch.randint(0, 1024, (4, 257), device=dev)
     losses = []
     for _ in range(8):
-        out = basic_train_step(model, {"input": tokens[:, :-1], "target": tokens[:, 1:]}, opt,
+        out = optimization_step(model, {"input": tokens[:, :-1], "target": tokens[:, 1:]}, opt,
                                clip_grad_norm=1.0, calc_loss_in_model=True)
         losses.append(out["loss"].item())
     assert losses[-1] < losses[0] - 0.5, losses
