@@ -295,10 +295,14 @@ def load_config(path: str, config_name: str | None = None, overrides=None, schem
 
 
 def load_arg_config(schema=None, args=None):
-    """CLI entry: `script.py CONF.py [config_name] [key=value ...]`."""
+    """CLI entry: `script.py [--conf] CONF.py [config_name] [key=value ...]`."""
     args = list(sys.argv[1:] if args is None else args)
+    if args and args[0] == "--conf":
+        args.pop(0)
+    elif args and args[0].startswith("--conf="):
+        args[0] = args[0][len("--conf="):]
     if not args:
-        raise SystemExit("usage: <script> CONFIG.py [config_name] [key=value ...]")
+        raise SystemExit("usage: <script> [--conf] CONFIG.py [config_name] [key=value ...]")
     path = args.pop(0)
     name = None
     if args and "=" not in args[0]:

@@ -36,11 +36,10 @@ class SymmetricHeap:
 
     def __init__(self, nbytes: int, group=None, device=None, backend: str = "auto"):
         self.group = group
-        self.world = dist.get_world_size(group) if (group is not None or dist.is_initialized()) and \
-            (group is not None) else 1
+        self.world = dist.get_world_size(group) if group is not None else 1
         self.rank = dist.get_rank(group) if group is not None else 0
-        self.device = torch.device(device if device is not None else
-                                   ("cuda", torch.cuda.current_device()))
+        self.device = torch.device(device) if device is not None else \
+            torch.device("cuda", torch.cuda.current_device())
         self.nbytes = (nbytes + 255) // 256 * 256
         total = _FLAG_BYTES + self.nbytes
         self.backend = None

@@ -207,6 +207,7 @@ class LMTrainer:
         for batch in batches:
             loss, loss_dict = _forward_loss(conf, model, self.criterion, batch, self.train_step_fn)
             loss.backward()
+            loss = loss.detach()
             if fsdp is not None:
                 fsdp.finish_backward()
             grad_norm = None
