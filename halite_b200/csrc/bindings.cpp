@@ -77,6 +77,7 @@ bool fill_scatter(const c10::optional<py::dict>& d, hb::ScatterParams& sp) {
   sp.rows_per_chunk = g["rows_per_chunk"].cast<int>();
   sp.rank = g["rank"].cast<int>();
   sp.epoch = g["epoch"].cast<int>();
+  sp.m_rot = g.contains("m_rot") ? g["m_rot"].cast<int>() : 0;
   return true;
 }
 

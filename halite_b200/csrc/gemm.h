@@ -54,6 +54,7 @@ struct ScatterParams {
   int n_chunks = 0;                 // 0 = scatter disabled
   int rank = 0;
   int epoch = 1;
+  int m_rot = 0;                    // first M tile to compute (start on a peer's rows so they travel early)
 };
 
 struct GemmArgs {

@@ -39,7 +39,8 @@ struct Cfg {
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // +1024 for alignment
+  static constexpr int kStagingBytes = 4 * 32 * 128;  // per epilogue warp: 32 rows x 128 bytes
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024;  // +1024: alignment
   static constexpr int kTmemCols = 2 * BN;
 };
 
@@ -288,6 +289,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
   const uint32_t tmem_base = tmem_slot;
 
   // With a fused gather the first `n_copy` CTAs only copy; the rest share the tiles.
+  const int m_rot = gp.m_rot + sp.m_rot;
   const int n_copy = gp.n_copy_ctas;
   const int first_tile = static_cast<int>(blockIdx.x) - n_copy;
   const int tile_step = static_cast<int>(gridDim.x) - n_copy;
@@ -302,7 +304,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
     for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
       int tm, tn;
       tile_coords(tile, tiles_m, tiles_n, tm, tn);
-      if (gp.m_rot) tm = (tm + gp.m_rot) % tiles_m;
+      if (m_rot) tm = (tm + m_rot) % tiles_m;
       const int m0 = tm * kBM, n0 = tn * BN;
       if (gp.dep == 1) ok = wait_rows(gp, m0, kBM, M, &abort_flag, status);
       if (gp.dep == 2) ok = wait_rows(gp, n0, BN, N, &abort_flag, status);
@@ -375,6 +377,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
   } else if (first_tile >= 0 && warp >= 4) {
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const bool staged_epilogue = (N % 8 == 0);
     const bool vec_ok = (ldd % (16 / (int)sizeof(OutT)) == 0) &&
                         ((reinterpret_cast<uintptr_t>(D) & 15) == 0);
     int local = 0;
@@ -382,7 +385,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
     for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++local) {
       int tm, tn;
       tile_coords(tile, tiles_m, tiles_n, tm, tn);
-      if (gp.m_rot) tm = (tm + gp.m_rot) % tiles_m;
+      if (m_rot) tm = (tm + m_rot) % tiles_m;
       const int m0 = tm * kBM, n0 = tn * BN;
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
@@ -392,6 +395,57 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+      if constexpr (sizeof(OutT) == 2) {
+        if (sp.n_chunks > 0 || (vec_ok && !accumulate && staged_epilogue)) {
+          // The warp's 32 x 64 sub-tile is transposed through shared memory (128B-swizzled,
+          // conflict-free both ways) and written 4 rows x 128 B per instruction: whole lines,
+          // which is what stores that cross NVLink need (reduce-scatter: the rows' owner
+          // receives this partial directly) and what keeps L2 write traffic to full sectors.
+          const uint32_t stage_base = smem_base + kStages * C::kStageBytes + q * (32 * 128);
+#pragma unroll 1
+          for (int c = 0; c < BN / 64; ++c) {
+#pragma unroll
+            for (int hlf = 0; hlf < 2; ++hlf) {
+              uint32_t v[32];
+              tmem_ld_32x32(taddr + c * 64 + hlf * 32, v);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const uint32_t chunk = static_cast<uint32_t>(hlf * 4 + j) ^ (lane & 7);
+                st_shared_v4(stage_base + lane * 128 + chunk * 16,
+                             pack_bf16x2(__uint_as_float(v[8 * j]), __uint_as_float(v[8 * j + 1])),
+                             pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3])),
+                             pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5])),
+                             pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7])));
+              }
+            }
+            __syncwarp();
+            const int col = n0 + c * 64 + (lane & 7) * 8;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int r = i * 4 + (lane >> 3);
+              const int grow = m0 + q * 32 + r;
+              const uint4 val = ld_shared_v4(stage_base + r * 128 + (((lane & 7) ^ (r & 7)) * 16));
+              if (grow < M && col < N) {
+                __nv_bfloat16* dst;
+                if (sp.n_chunks > 0) {
+                  const int owner = grow / sp.rows_per_chunk;
+                  dst = static_cast<__nv_bfloat16*>(sp.dst[owner]) +
+                        static_cast<size_t>(grow - owner * sp.rows_per_chunk) * ldd + col;
+                } else {
+                  dst = reinterpret_cast<__nv_bfloat16*>(D) + static_cast<size_t>(grow) * ldd + col;
+                }
+                *reinterpret_cast<uint4*>(dst) = val;
+              }
+            }
+            __syncwarp();
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[acc]));
+          continue;
+        }
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t v[32];
@@ -400,15 +454,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
         const int col = n0 + c * 32;
         if (row < M && col < N) {
           OutT* base = D + static_cast<size_t>(row) * ldd;
-          bool vok = vec_ok;
-          if (sp.n_chunks > 0) {
-            // reduce-scatter: the row's owner receives this partial directly
-            const int owner = row / sp.rows_per_chunk;
-            base = static_cast<OutT*>(sp.dst[owner]) +
-                   static_cast<size_t>(row - owner * sp.rows_per_chunk) * ldd;
-            vok = (ldd % (16 / (int)sizeof(OutT)) == 0) && ((reinterpret_cast<uintptr_t>(base) & 15) == 0);
-          }
-          store_chunk<OutT>(base + col, v, min(32, N - col), vok, accumulate != 0 && sp.n_chunks == 0);
+          store_chunk<OutT>(base + col, v, min(32, N - col), vec_ok, accumulate != 0);
         }
       }
       tc_fence_before();

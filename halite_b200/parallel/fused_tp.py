@@ -132,7 +132,10 @@ class FusedGemmReduceScatter:
             recv_ptrs=[0 if p == r else heap.data_ptr(r, off + p * self.slot_bytes) for p in range(w)],
             peer_flag_ptrs=[0 if c == r else heap.flag_ptr(c, self.f_flags[b] + r) for c in range(w)],
             my_flags_ptr=heap.flag_ptr(r, self.f_flags[b]), out_ptr=out.data_ptr(),
-            cta_counter_ptr=self.counter.data_ptr(), rows_per_chunk=self.rows, rank=r, epoch=epoch)
+            cta_counter_ptr=self.counter.data_ptr(), rows_per_chunk=self.rows, rank=r, epoch=epoch,
+            # start on the next rank's rows: what has to cross NVLink is computed first and the
+            # rank's own rows last
+            m_rot=((r + 1) % w) * self.rows // _TILE_ROWS if self.rows % _TILE_ROWS == 0 else 0)
         # the [M, N] `out` argument of the plain GEMM is unused in scatter mode: pass the partial
         gemm(x, weight, out=self.partial, scatter=scatter, b_mn=b_mn)
         self.call += 1
