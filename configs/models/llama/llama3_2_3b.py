@@ -2,11 +2,13 @@
 
 from functools import partial
 
-from halite_b200.conf import call, field
+from halite_b200.conf import call, field, function
+from halite_b200.data.tokenizers.llama3 import Llama3Tokenizer
 from halite_b200.models.position import Llama3RoPE, apply_rotary_emb
 from halite_b200.parallel.parallelize import parallelize
 
 from ..transformer import transformer, transformer_infer
+from .checkpoint import to_halite_postprocess, weight_maps
 
 conf = field()
 
@@ -41,3 +43,5 @@ conf.model_conf = field(
     intermediate_size=8192, context_len=context_len, rms_norm_epsilon=1e-5,
     use_complex_rope=use_complex_rope, qkv_split=qkv_split, dtype="bfloat16")
 conf.parallelize = partial(parallelize, param_dtype="bfloat16", reduce_dtype="float32")
+conf.tokenizer = Llama3Tokenizer()
+conf.policy = field(weight_maps=weight_maps, to_halite_postprocess=function(to_halite_postprocess))

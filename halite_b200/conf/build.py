@@ -21,8 +21,34 @@ def _resolve(path, node=None):
         obj = mod
         for p in qual.split("."):
             obj = getattr(obj, p)
-        return unwrap(obj)
+        return _runtime_function(mod, unwrap(obj))
     return unwrap(locate(path))
+
+
+_runtime_globals: dict = {}
+
+
+def _runtime_function(mod, fn):
+    """A plain function defined in a config file sees library imports as recording stand-ins.
+    When such a function is used at run time (a hook named with `function(...)`), re-bind its
+    code to a copy of the module's globals in which the stand-ins are the real objects, so
+    `torch.cat(...)` inside it computes instead of recording."""
+    import types
+
+    if not isinstance(fn, types.FunctionType) or getattr(fn, "__hb_config_fn__", False):
+        return fn
+    key = id(mod)
+    if key not in _runtime_globals:
+        real = {}
+        for k, v in mod.__dict__.items():
+            real[k] = unwrap(v) if isinstance(v, Lazy) else v
+        for k, v in list(real.items()):
+            if isinstance(v, types.FunctionType) and v.__globals__ is mod.__dict__ and \
+                    not getattr(v, "__hb_config_fn__", False):
+                real[k] = types.FunctionType(v.__code__, real, v.__name__, v.__defaults__, v.__closure__)
+                real[k].__kwdefaults__ = v.__kwdefaults__
+        _runtime_globals[key] = real
+    return _runtime_globals[key].get(fn.__name__, fn)
 
 
 def instantiate(node, *args, _tags_: dict | None = None, **kwargs):

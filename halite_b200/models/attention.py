@@ -108,8 +108,11 @@ class Attention(nn.Module):
             query, key = self.apply_pos_emb_fn(query, key, pos_embed)
         next_cache = None
         if cache is not None:
-            key = torch.cat((cache[0], key), 1)
-            value = torch.cat((cache[1], value), 1)
+            if hasattr(cache, "get"):           # cache objects append in their own way
+                key, value = cache.get(key, value)
+            else:
+                key = torch.cat((cache[0], key), 1)
+                value = torch.cat((cache[1], value), 1)
         if use_cache:
             next_cache = (key, value)
         out = self.core(query, key, value, attention_mask, attention_bias, unpad_params)

@@ -13,11 +13,12 @@ from torch import nn, utils
 
 from halite_b200.ops import linear as ops_linear
 from halite_b200.models.container import ModuleDict
+from halite_b200.models.generation import GenerationMixin
 from halite_b200.models.model import ModelMixin
 from halite_b200.models.types import TransformerDecoderOutput
 
 
-class TransformerDecoder(nn.Module, ModelMixin):
+class TransformerDecoder(nn.Module, ModelMixin, GenerationMixin):
     def __init__(self, embedding, post_embed=None, attention_mask=None, pos_embed=None, blocks=None,
                  post_blocks=None, head=None, tie_embeds=False, use_position_ids=False,
                  attention_processor="native", flex_attention_processor=None, config=None):
@@ -243,8 +244,13 @@ class TransformerDecoder(nn.Module, ModelMixin):
                 if hooks is not None:
                     out = hooks[1](index, out)
                 if use_cache:
-                    next_caches.append(next_cache)
+                    if hasattr(cache, "update"):      # a cache manager keeps its own per-layer state
+                        cache.update(index, next_cache)
+                    else:
+                        next_caches.append(next_cache)
                 aux_outputs.append(aux)
+            if use_cache and hasattr(cache, "update"):
+                next_caches = cache
 
         if self.post_blocks is not None:
             out = self.post_blocks(out, residual) if residual is not None else self.post_blocks(out)
