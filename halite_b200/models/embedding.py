@@ -69,32 +69,38 @@ class MultiModalEmbedding(nn.Module):
 
 
 class PatchEmbedding(nn.Module):
-    """Image -> patch tokens, by strided convolution or unfold + linear."""
+    """Image -> patch tokens, by strided convolution or reshape + linear, then an optional
+    position embedding (state-dict names `patch_embedding`, `position_embedding`)."""
 
-    def __init__(self, in_channels, dim, patch_size, use_conv=True, bias=True, proj_init=None):
+    def __init__(self, in_dim, out_dim, patch_size, position_embedding=None, use_conv=False, use_bias=False,
+                 patch_embedding_init=None):
         super().__init__()
         self.patch_size = patch_size
         self.use_conv = use_conv
-        self.proj_init = proj_init
+        self.patch_embedding_init = patch_embedding_init
         if use_conv:
-            self.proj = nn.Conv2d(in_channels, dim, patch_size, patch_size, bias=bias)
+            self.patch_embedding = nn.Conv2d(in_dim, out_dim, patch_size, patch_size, bias=use_bias)
         else:
-            self.proj = nn.Linear(in_channels * patch_size * patch_size, dim, bias=bias)
+            self.patch_embedding = nn.Linear(in_dim * patch_size * patch_size, out_dim, bias=use_bias)
+        self.position_embedding = position_embedding
 
     def init_weights(self):
-        w = self.proj.weight
-        if self.proj_init is not None:
-            self.proj_init(w.view(w.shape[0], -1) if w.dim() > 2 else w)
+        w = self.patch_embedding.weight
+        if self.patch_embedding_init is not None:
+            self.patch_embedding_init(w)
         else:
             nn.init.xavier_uniform_(w.view(w.shape[0], -1))
-        if self.proj.bias is not None:
-            nn.init.zeros_(self.proj.bias)
+        if self.patch_embedding.bias is not None:
+            nn.init.zeros_(self.patch_embedding.bias)
 
     def forward(self, images):
         if self.use_conv:
-            return self.proj(images).flatten(2).transpose(1, 2)
-        p = self.patch_size
-        B, C, H, W = images.shape
-        x = images.unfold(2, p, p).unfold(3, p, p)           # B,C,h,w,p,p
-        x = x.permute(0, 2, 3, 1, 4, 5).reshape(B, (H // p) * (W // p), C * p * p)
-        return self.proj(x)
+            out = self.patch_embedding(images).flatten(2).transpose(1, 2)
+        else:
+            p = self.patch_size
+            B, C, H, W = images.shape
+            x = images.reshape(B, C, H // p, p, W // p, p).permute(0, 2, 4, 1, 3, 5)
+            out = self.patch_embedding(x.reshape(B, (H // p) * (W // p), C * p * p))
+        if self.position_embedding is not None:
+            out = self.position_embedding(out)
+        return out

@@ -18,6 +18,8 @@ class BidirectionalMask:
 
     def __call__(self, bidirection_ids):
         inner = self.mask_mod_fn
+        if bidirection_ids is None:          # text-only batch: just the inner mask
+            return inner
         last = bidirection_ids.shape[1] - 1
 
         def bidirectional_mask_mod(b, h, q_idx, kv_idx):

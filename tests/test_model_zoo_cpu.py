@@ -1,0 +1,87 @@
+"""Model-zoo variants on CPU: a miniature Gemma-3-style multimodal decoder (vision tower, soft
+image tokens, alternating local / global layers with per-type RoPE and bidirectional image
+spans), Qwen3-style q/k norm with tied embeddings, SigLIP-style encoder, nGPT re-normalisation."""
+
+import os
+from functools import partial
+
+import torch
+from torch import nn
+
+from halite_b200.conf import instantiate
+from halite_b200.conf.loader import load_module
+from tests.helpers import ROOT
+
+zoo = load_module(os.path.join(ROOT, "configs/models/transformer.py"))
+init = partial(nn.init.normal_, std=0.05)
+
+
+def build(cfg):
+    torch.manual_seed(0)
+    m = instantiate(cfg)
+    m.init_weights()
+    return m.eval()
+
+
+def mini_gemma():
+    from halite_b200.conf import load_config
+
+    return load_config(os.path.join(ROOT, "tests/configs/mini_gemma3.py")).model
+
+
+def test_mini_gemma3_multimodal_forward_and_masks():
+    model = build(mini_gemma())
+    keys = set(model.state_dict())
+    assert "embedding.image_embedding.encoder.blocks.0.self_attention.module.q.bias" in keys
+    assert "blocks.0.self_attention.post_norm.weight" in keys and "blocks.2.ff.post_norm.weight" in keys
+    assert "embedding.text_embedding.multiplier" not in keys and not any(k.startswith("head.") for k in keys)
+    ids = torch.randint(0, 98, (2, 12))
+    ids[:, 3:7] = 99                               # one image = 4 soft tokens
+    bid = torch.zeros(2, 12, dtype=torch.long)
+    bid[:, 3:7] = 1
+    images = torch.randn(2, 3, 16, 16)
+    out = model(ids, images=images, bidirection_ids=bid)
+    assert out.logits.shape == (2, 12, 100) and torch.isfinite(out.logits).all()
+    # image tokens see each other both ways: changing the LAST image patch changes the logits at
+    # the FIRST image position; text before the image is untouched (causal)
+    images2 = images.clone()
+    images2[:, :, 8:, 8:] += 1.0
+    out2 = model(ids, images=images2, bidirection_ids=bid)
+    assert (out2.logits[:, 3] - out.logits[:, 3]).abs().max() > 1e-4
+    assert (out2.logits[:, :3] - out.logits[:, :3]).abs().max() < 1e-6
+    # the bidirectional span is what lets position 3 see positions 4..6: without the ids the
+    # logits there differ, while the last image position (which sees the whole span causally
+    # anyway, window permitting) is a weaker check and text before the image never changes
+    plain = model(ids, images=images)
+    assert (plain.logits[:, 3] - out.logits[:, 3]).abs().max() > 1e-4
+    assert (plain.logits[:, :3] - out.logits[:, :3]).abs().max() < 1e-6
+    out.logits.float().mean().backward()
+
+
+def test_qwen3_style_qk_norm_and_tied_head():
+    from halite_b200.models.position import RotaryEmbedding, apply_rotary_emb
+    from halite_b200.nn.normalization import RMSNorm
+
+    cfg = zoo.transformer(vocab_size=64, dim=32, n_heads=4, head_dim=16, n_layers=2, intermediate_size=64,
+                          context_len=32, n_key_value_heads=2, rms_norm_epsilon=1e-6,
+                          pos_embed=RotaryEmbedding(16, 32, base=1000000, use_rotate_half=True, pre_init=False),
+                          pos_embed_apply_fn=partial(apply_rotary_emb, use_complex=False), qkv_split=True,
+                          gated_ff_split=True, q_norm=RMSNorm(16, eps=1e-6), k_norm=RMSNorm(16, eps=1e-6),
+                          tie_embeds=True, init=init)
+    model = build(cfg)
+    sd = model.state_dict()
+    assert "blocks.1.self_attention.module.attention.k_norm.weight" in sd and "head.linear.weight" not in sd
+    x = torch.randint(0, 64, (2, 7))
+    logits = model(x).logits
+    assert logits.shape == (2, 7, 64)
+    hidden = model(x, output_hidden_states=True).hidden_states[-1]
+    torch.testing.assert_close(logits, hidden @ model.embedding.embed_weight.t(), rtol=1e-5, atol=1e-5)
+
+
+def test_ngpt_normalize_projects_to_unit_rows():
+    from halite_b200.models.optimizer import ngpt_normalize
+
+    lin = nn.ModuleDict({"q": nn.Linear(8, 16, bias=True), "out": nn.Linear(16, 8, bias=False)})
+    ngpt_normalize(lin)
+    torch.testing.assert_close(lin["q"].weight.norm(dim=1), torch.ones(16))
+    torch.testing.assert_close(lin["out"].weight.norm(dim=0), torch.ones(16))
