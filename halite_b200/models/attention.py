@@ -312,11 +312,13 @@ class DiffAttention(Attention):
     """Differential attention: two softmax maps from split heads, subtracted with a learned
     lambda, followed by a per-head norm scaled by (1 - lambda_init)."""
 
-    def __init__(self, n_heads, head_dim, layer_id, n_key_value_heads=None, is_causal=True,
-                 apply_pos_emb_fn=None, sub_norm=None, **kwargs):
+    def __init__(self, n_heads, head_dim, lambda_init=None, n_key_value_heads=None, is_causal=True,
+                 apply_pos_emb_fn=None, sub_norm=None, layer_id=None, **kwargs):
         super().__init__(n_heads, head_dim, n_key_value_heads, is_causal=is_causal,
                          apply_pos_emb_fn=apply_pos_emb_fn, **kwargs)
-        self.lambda_init = 0.8 - 0.6 * math.exp(-0.3 * layer_id)
+        if lambda_init is None:      # the schedule of the paper, by depth
+            lambda_init = 0.8 - 0.6 * math.exp(-0.3 * (layer_id or 0))
+        self.lambda_init = lambda_init
         self.lambda_q1 = nn.Parameter(torch.zeros(head_dim))
         self.lambda_k1 = nn.Parameter(torch.zeros(head_dim))
         self.lambda_q2 = nn.Parameter(torch.zeros(head_dim))

@@ -52,6 +52,14 @@ class FusedLinearCrossEntropy(nn.Module):
         return {"linear": "vocab_head"}
 
 
+def _project(module, x):
+    """A plain `nn.Linear` goes straight to the GEMM; a composite (e.g. a `LinearLayer` with a
+    learned scale behind the linear) is called as a module."""
+    if type(module) is nn.Linear:
+        return ops.linear(x, module.weight, module.bias)
+    return module(x)
+
+
 class VocabParallelLinear(nn.Module):
     def __init__(self, linear, linear_init=None, scale=None):
         super().__init__()
@@ -59,34 +67,38 @@ class VocabParallelLinear(nn.Module):
         self.linear_init = linear_init
         self.scale = None
         if scale:
-            self.scale = nn.Parameter(torch.ones(self.linear.out_features))
-        self.tie_weight_key = "linear.weight"
+            self.scale = nn.Parameter(torch.ones(self._lin().out_features))
+        self.tie_weight_key = "linear.weight" if type(linear) is nn.Linear else "linear.0.weight"
 
     def init_weights(self):
         init_weights(self.linear, self.linear_init)
         if self.scale is not None:
             nn.init.ones_(self.scale)
 
+    def _lin(self):
+        """The projection itself (the head may be a `LinearLayer` = linear + learned scale)."""
+        return self.linear if type(self.linear) is nn.Linear else self.linear[0]
+
     def forward(self, input):
-        out = ops.linear(input, self.linear.weight, self.linear.bias)
+        out = _project(self.linear, input)
         if self.scale is not None:
             out = out * self.scale
         return out
 
     def tie_weight(self, weight):
-        self.linear.weight = weight
+        self._lin().weight = weight
 
     @property
     def n_vocab(self):
-        return self.linear.weight.shape[0]
+        return self._lin().weight.shape[0]
 
     @property
     def weight(self):
-        return self.linear.weight
+        return self._lin().weight
 
     @property
     def bias(self):
-        return self.linear.bias
+        return self._lin().bias
 
     def tp_plan(self):
         return {"linear": "vocab_head"}
@@ -164,6 +176,8 @@ class GatedFeedForward(nn.Module):
         init_weights(self.linear_out, self.linear_out_init)
 
     def fusable_linears(self):
+        if not (isinstance(self.linear_proj, nn.Linear) and isinstance(self.linear_gate, nn.Linear)):
+            return {}
         return {"proj_gate": ("linear_proj", "linear_gate")}
 
     def pack_weights(self):
@@ -171,6 +185,8 @@ class GatedFeedForward(nn.Module):
         so both projections are a single GEMM."""
         from torch import nn as _nn
 
+        if not self.fusable_linears():
+            return
         ws = [self.linear_proj.weight, self.linear_gate.weight]
         if self.linear_proj.bias is not None or self.linear_gate.bias is not None or ws[0].is_meta:
             return
@@ -209,14 +225,14 @@ class GatedFeedForward(nn.Module):
             pg = ops.linear(input, fused)
             out = gated_act_packed(pg, kind, gate_first=False)
         else:
-            proj = ops.linear(input, self.linear_proj.weight, self.linear_proj.bias)
-            gate = ops.linear(input, self.linear_gate.weight, self.linear_gate.bias)
+            proj = _project(self.linear_proj, input)
+            gate = _project(self.linear_gate, input)
             if kind is not None:
                 out = gated_act(gate, proj, kind)
             else:
                 out = proj * self.activation(gate)
         out = self.dropout(out)
-        return ops.linear(out, self.linear_out.weight, self.linear_out.bias)
+        return _project(self.linear_out, out)
 
     def tp_plan(self):
         return {"linear_proj": "colwise", "linear_gate": "colwise", "linear_out": "rowwise"}

@@ -63,6 +63,13 @@ class FusedPostBlock(nn.Module):
 class LinearLayer(nn.Sequential):
     """Linear followed by extra modules; initialisers address the linear at index 0."""
 
+    def forward(self, input):
+        first, *rest = list(self)
+        out = ops.linear(input, first.weight, first.bias) if type(first) is nn.Linear else first(input)
+        for m in rest:
+            out = m(out)
+        return out
+
 
 class NormalizedEmbedding(nn.Embedding):
     def forward(self, input):
@@ -77,18 +84,23 @@ class NormalizedLinear(nn.Linear):
 
 
 class Scale(nn.Module):
-    """Learned per-channel scale stored at `init_scale` and applied as value * (init_value / init_scale)."""
+    """Learned per-channel scale for nGPT: the parameter is stored at magnitude `scale` and acts
+    as `weight * init / scale` (times `rescale`), optionally through abs()."""
 
-    def __init__(self, dim, init_value=1.0, init_scale=1.0):
+    def __init__(self, dim, init, scale, rescale=None, apply_abs=False):
         super().__init__()
-        self.init_value, self.init_scale = init_value, init_scale
-        self.scale = nn.Parameter(torch.full((dim,), float(init_scale)))
+        self.weight = nn.Parameter(torch.full((dim,), float(scale), dtype=torch.float32))
+        self.init, self.scale, self.rescale, self.apply_abs = init, scale, rescale, apply_abs
 
     def init_weights(self):
-        nn.init.constant_(self.scale, self.init_scale)
+        nn.init.constant_(self.weight, self.scale)
 
     def forward(self, input):
-        return input * (self.scale * (self.init_value / self.init_scale)).to(input.dtype)
+        factor = self.init / self.scale * (self.rescale if self.rescale is not None else 1.0)
+        scale = self.weight * factor
+        if self.apply_abs:
+            scale = scale.abs()
+        return input * scale.to(input.dtype)
 
 
 class L2Norm(nn.Module):

@@ -5,6 +5,7 @@ spans), Qwen3-style q/k norm with tied embeddings, SigLIP-style encoder, nGPT re
 import os
 from functools import partial
 
+import pytest
 import torch
 from torch import nn
 
@@ -85,3 +86,47 @@ def test_ngpt_normalize_projects_to_unit_rows():
     ngpt_normalize(lin)
     torch.testing.assert_close(lin["q"].weight.norm(dim=1), torch.ones(16))
     torch.testing.assert_close(lin["out"].weight.norm(dim=0), torch.ones(16))
+
+
+def _train_a_little(model, vocab, post_step=None, steps=10, lr=3e-3):
+    opt = torch.optim.AdamW(model.parameters(), lr=lr)
+    x = torch.randint(0, vocab, (4, 17))
+    losses = []
+    for _ in range(steps):
+        loss = torch.nn.functional.cross_entropy(model(x[:, :-1]).logits.flatten(0, 1).float(), x[:, 1:].flatten())
+        loss.backward()
+        opt.step()
+        opt.zero_grad()
+        if post_step is not None:
+            post_step(model)
+        losses.append(loss.item())
+    return losses
+
+
+def test_scaling_diff_transformer_and_ngpt_configs_train():
+    from halite_b200.models.optimizer import ngpt_normalize
+
+    torch.manual_seed(0)
+    base = load_module(os.path.join(ROOT, "configs/models/scaling/base.py"))
+    m = build(base.transformer(64, 32, 4, 8, 2, 48, 32, qkv_split=True, gated_ff_split=True, post_norm=True))
+    m.train()
+    losses = _train_a_little(m, 64)
+    assert losses[-1] < losses[0] - 0.2
+
+    diff = load_module(os.path.join(ROOT, "configs/models/diff_transformer.py"))
+    m = build(diff.diff_transformer(64, 32, 2, 2, 48, 32, qkv_split=True))
+    lam = [mod.lambda_init for mod in m.modules() if hasattr(mod, "lambda_init")]
+    assert len(lam) == 2 and lam[0] == pytest.approx(0.2) and lam[1] > lam[0]
+    m.train()
+    losses = _train_a_little(m, 64)
+    assert losses[-1] < losses[0] - 0.2
+
+    ng = load_module(os.path.join(ROOT, "configs/models/ngpt.py"))
+    m = build(ng.ngpt(64, 32, 4, 2, 48, 32))
+    ngpt_normalize(m)
+    m.train()
+    losses = _train_a_little(m, 64, post_step=ngpt_normalize, lr=1e-2)
+    assert losses[-1] < losses[0] - 0.1
+    w = m.blocks["0"].self_attention.module.q.weight
+    torch.testing.assert_close(w.norm(dim=1), torch.ones(32), rtol=1e-4, atol=1e-4)
+    assert "blocks.0.self_attention.scale.weight" in m.state_dict()
