@@ -29,24 +29,50 @@ _runtime_globals: dict = {}
 
 
 def _runtime_function(mod, fn):
-    """A plain function defined in a config file sees library imports as recording stand-ins.
-    When such a function is used at run time (a hook named with `function(...)`), re-bind its
-    code to a copy of the module's globals in which the stand-ins are the real objects, so
-    `torch.cat(...)` inside it computes instead of recording."""
+    """A plain function or class defined in a config file sees library imports as recording
+    stand-ins. When it is used at run time (a hook named with `function(...)`, a reward class
+    built with `external[...]`), re-bind its code to a copy of the module's globals in which the
+    stand-ins are the real objects, so `torch.cat(...)` inside it computes instead of
+    recording."""
     import types
 
-    if not isinstance(fn, types.FunctionType) or getattr(fn, "__hb_config_fn__", False):
+    is_fn = isinstance(fn, types.FunctionType) and not getattr(fn, "__hb_config_fn__", False)
+    is_cls = isinstance(fn, type) and getattr(fn, "__module__", None) == mod.__name__
+    if not (is_fn or is_cls):
         return fn
     key = id(mod)
     if key not in _runtime_globals:
         real = {}
         for k, v in mod.__dict__.items():
             real[k] = unwrap(v) if isinstance(v, Lazy) else v
+        lazy_import = mod.__dict__.get("__hb_import__")
+        if lazy_import is not None:
+            # imports written inside function bodies must also yield real objects at run time
+            real["__hb_import__"] = lambda *a: unwrap(lazy_import(*a))
+
+        def rebind(f):
+            g = types.FunctionType(f.__code__, real, f.__name__, f.__defaults__, f.__closure__)
+            g.__kwdefaults__ = f.__kwdefaults__
+            g.__qualname__ = f.__qualname__
+            g.__doc__ = f.__doc__
+            return g
+
         for k, v in list(real.items()):
             if isinstance(v, types.FunctionType) and v.__globals__ is mod.__dict__ and \
                     not getattr(v, "__hb_config_fn__", False):
-                real[k] = types.FunctionType(v.__code__, real, v.__name__, v.__defaults__, v.__closure__)
-                real[k].__kwdefaults__ = v.__kwdefaults__
+                real[k] = rebind(v)
+            elif isinstance(v, type) and getattr(v, "__module__", None) == mod.__name__:
+                body = {}
+                for name, attr in vars(v).items():
+                    if name in ("__dict__", "__weakref__"):
+                        continue
+                    if isinstance(attr, types.FunctionType) and attr.__globals__ is mod.__dict__:
+                        attr = rebind(attr)
+                    elif isinstance(attr, (staticmethod, classmethod)) and \
+                            getattr(attr.__func__, "__globals__", None) is mod.__dict__:
+                        attr = type(attr)(rebind(attr.__func__))
+                    body[name] = attr
+                real[k] = type(v)(v.__name__, v.__bases__, body)
         _runtime_globals[key] = real
     return _runtime_globals[key].get(fn.__name__, fn)
 

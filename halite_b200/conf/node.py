@@ -254,6 +254,9 @@ def record_call(obj, path, args, kwargs, partial=False) -> Field:
         dict.__setitem__(node, ARGS, [normalize(a) for a in leftover])
     for k, v in {**named, **kwargs}.items():
         node[k] = v
+    src = getattr(obj, "__hb_file__", None)      # defined inside a config file: remember where
+    if src:
+        dict.__setitem__(node, FILE, src)
     return node
 
 

@@ -17,23 +17,27 @@ from halite_b200.data.sources import FileInstruction, open_source
 
 
 def build_dataset_from_spec(spec, split="train", split_ratio=0):
-    """spec: {root, ratios: {name: w}, shards: {name: {file: n_records}}}. Each shard gives its
-    head to `train` and its tail (split_ratio of it, at least one record) to the other split."""
+    """spec: {root, ratios: {name: w}, shards: {name: {file: n_records}}}.
+
+    `train` reads the last `split_ratio` share of every shard (at least one record; the whole
+    shard when the ratio is 0), any other split reads the first `split_ratio` share (rounded up).
+    With train_ratio + eval_ratio <= 1 the two never overlap."""
+    get = spec.get if hasattr(spec, "get") else lambda k: getattr(spec, k)
     sources, ratios, names = [], [], []
-    for name, shards in spec["shards"].items():
+    for name, shards in get("shards").items():
         instructions = []
         for shard, size in shards.items():
-            path = os.path.join(spec["root"], name, shard)
+            path = os.path.join(get("root"), name, shard)
             if split == "train":
-                held = max(math.floor(size * split_ratio), 1) if split_ratio else 0
-                instructions.append(FileInstruction(path, 0, size - held, size))
+                take = max(math.floor(size * split_ratio), 1) if split_ratio else size
+                instructions.append(FileInstruction(path, size - take, take, size))
             else:
-                held = max(math.ceil(size * split_ratio), 1) if split_ratio else size
-                instructions.append(FileInstruction(path, size - held, held, size))
+                take = max(math.ceil(size * split_ratio), 1) if split_ratio else 0
+                instructions.append(FileInstruction(path, 0, take, size))
         if not instructions:
             continue
         sources.append(open_source(instructions))
-        ratios.append(spec["ratios"][name])
+        ratios.append(get("ratios")[name])
         names.append(name)
     return sources, ratios, names
 

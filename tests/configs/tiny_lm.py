@@ -30,7 +30,7 @@ _data_root = os.environ.get("HB_TEST_DATA", "/nonexistent")
 _spec = field(root=_data_root, ratios={"a": 0.8, "b": 0.2},
               shards={"a": {"s0.hbrec": 200}, "b": {"s0.hbrec": 50}})
 conf.data = field(
-    train=_spec, eval=_spec, train_ratio=0.1, eval_ratio=0.1,
+    train=_spec, eval=_spec, train_ratio=0.9, eval_ratio=0.1,
     preprocess=[preprocess.ParseFeatures(),
                 preprocess.Tokenize(ByteTokenizer(), bos=True, eos=True),
                 preprocess.SequencePacking(33),

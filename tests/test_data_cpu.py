@@ -49,10 +49,13 @@ def test_index_shuffle_is_a_permutation():
 
 def test_split_and_ratio_mixing(tmp_path):
     spec = make_spec(tmp_path)
-    train, ratios, names = build_dataset_from_spec(spec, "train", 0.1)
+    # train reads the tail share of each shard, eval the head share
+    train, ratios, names = build_dataset_from_spec(spec, "train", 0.9)
     evals, _, _ = build_dataset_from_spec(spec, "eval", 0.1)
     assert [len(s) for s in train] == [180, 45] and [len(s) for s in evals] == [20, 5]
-    assert json.loads(train[0][179])["idx"] == 179 and json.loads(evals[0][0])["idx"] == 180
+    assert json.loads(train[0][0])["idx"] == 20 and json.loads(train[0][179])["idx"] == 199
+    assert json.loads(evals[0][0])["idx"] == 0 and json.loads(evals[0][19])["idx"] == 19
+    assert len(build_dataset_from_spec(spec, "train", 0)[0][0]) == 200
     ds = WeightedIterableDataset(train, ratios, names, operations=[P.ParseFeatures()], seed=3)
     counts = {"a": 0, "b": 0}
     seen = set()
