@@ -28,7 +28,7 @@ def test_math_verify_and_format_rewards():
 
 def test_metric_fallback_and_timeout():
     assert _fallback_equal("\\frac{1}{2}", "\\boxed{0.5}", 6) and not _fallback_equal("2", "3", 6)
-    score, strings = math_metric()(["$7$"], ["\\boxed{7}"])
+    score, strings = math_metric()(["7"], ["the answer is 7"])
     assert score == 1.0 and strings is not None
 
     @timeout(0.3)
