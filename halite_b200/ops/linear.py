@@ -15,6 +15,7 @@ import torch
 import torch.nn.functional as F
 
 import halite_b200.ops as ops
+from halite_b200.utils import probe as _probe
 
 
 def gemm(a, b, out=None, a_mn=False, b_mn=False, accumulate=False, out_dtype=None, block_n=0,
@@ -86,8 +87,12 @@ class _LinearFn(torch.autograd.Function):
 
 def linear(x, weight, bias=None):
     if ops.use_sm100(x) and weight.dtype == torch.bfloat16:
-        return _LinearFn.apply(x, weight, bias)
-    return F.linear(x, weight, bias)
+        out = _LinearFn.apply(x, weight, bias)
+    else:
+        out = F.linear(x, weight, bias)
+    if _probe.active_probe() is not None:
+        _probe.active_probe().on_linear(x, weight, out)
+    return out
 
 
 def matmul_nt(a, b, out_dtype=None):

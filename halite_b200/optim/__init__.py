@@ -58,5 +58,6 @@ def build_optimizer(factory, model, weight_decay: float = 0.0):
     return factory(params)
 
 
+from .soap import SOAP  # noqa: E402
 from .lr_scheduler import PhaseScheduler, cycle_scheduler, exp_scheduler, lr_finder, step_scheduler  # noqa: E402
 from .sharded_adamw import ShardedAdamW  # noqa: E402

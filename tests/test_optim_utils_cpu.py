@@ -1,0 +1,100 @@
+"""SOAP optimizer and the linear-layer Probe."""
+
+import json
+import os
+from functools import partial
+
+import torch
+
+from halite_b200.conf import instantiate
+from halite_b200.conf.loader import load_module
+from halite_b200.optim.soap import SOAP, _merge_dims
+from halite_b200.utils.probe import QUANTILES, Probe, get_stats
+from tests.helpers import ROOT
+
+
+def test_soap_beats_adam_on_an_ill_conditioned_quadratic():
+    torch.manual_seed(0)
+    A = torch.randn(32, 32)
+    A = A @ A.t() / 32 + 0.01 * torch.eye(32)
+    B = torch.diag(torch.logspace(-2, 1, 16))
+    target = torch.randn(32, 16)
+
+    def loss_fn(w):
+        return ((A @ (w - target) @ B) ** 2).mean()
+
+    final = {}
+    for name in ("adam", "soap"):
+        w = torch.zeros(32, 16, requires_grad=True)
+        b = torch.zeros(16, requires_grad=True)
+        opt = torch.optim.Adam([w, b], lr=3e-2, betas=(0.95, 0.95)) if name == "adam" else \
+            SOAP([w, b], lr=3e-2, weight_decay=0, precondition_frequency=5)
+        for _ in range(300):
+            (loss_fn(w) + 0.1 * (b - 1).square().sum()).backward()
+            opt.step()
+            opt.zero_grad()
+        final[name] = loss_fn(w).item()
+        assert (b - 1).abs().max() < 0.2              # 1-D parameters fall back to plain Adam
+    assert final["soap"] < 0.5 * final["adam"]
+    assert _merge_dims((4, 8, 3, 3), 100) == (4, 72)
+    # 4-D conv weight with merged dims, bases stay orthonormal after refreshes
+    w = torch.randn(4, 3, 3, 3, requires_grad=True)
+    opt = SOAP([w], lr=1e-2, merge_dims=True, max_precond_dim=30, precondition_frequency=2)
+    for _ in range(6):
+        (w ** 2).sum().backward()
+        opt.step()
+        opt.zero_grad()
+    for q in opt.state[w]["basis"].Q:
+        if q is not None:
+            torch.testing.assert_close(q.t() @ q, torch.eye(q.shape[0]), rtol=1e-4, atol=1e-4)
+
+
+def test_probe_records_linear_statistics_and_gradients(tmp_path):
+    zoo = load_module(os.path.join(ROOT, "configs/models/transformer.py"))
+    cfg = zoo.transformer(vocab_size=64, dim=32, n_heads=4, head_dim=8, n_layers=2, intermediate_size=48,
+                          context_len=32, n_key_value_heads=2, qkv_split=True, gated_ff_split=True,
+                          init=partial(torch.nn.init.normal_, std=0.05))
+    torch.manual_seed(0)
+    model = instantiate(cfg)
+    model.init_weights()
+    out_file = tmp_path / "probe" / "stats.jsonl"
+    x = torch.randint(0, 64, (2, 9))
+    with Probe(model, str(out_file), save_tensors=True) as probe:
+        probe.metadata = {"it": 3}
+        loss = torch.nn.functional.cross_entropy(model(x[:, :-1]).logits.flatten(0, 1), x[:, 1:].flatten())
+        loss.backward()
+    rec = json.loads(out_file.read_text().splitlines()[0])
+    assert rec["meta"] == {"it": 3} and rec["quantiles"] == QUANTILES
+    data = rec["data"]
+    for suffix in ("in", "weight", "out", "in.g", "out.g", "w.g"):
+        assert f"blocks.1.ff.module.linear_out::{suffix}" in data, suffix
+    stat = data["blocks.0.self_attention.module.q::weight"]
+    assert stat["shape"] == [32, 32] and abs(stat["std"] - 0.05) < 0.01 and len(stat["quantiles"]) == 19
+    assert "head.linear::out" in data
+    assert (tmp_path / "probe" / "tensors" / "it0000000003").is_dir()
+    s = get_stats(torch.arange(10.0))
+    assert float(s["mean"]) == 4.5 and float(s["max"]) == 9.0 and get_stats(torch.arange(3)) == {}
+    # outside the context nothing is recorded
+    model(x)
+    assert not probe.store
+
+
+def test_stateless_process_group_objects_barrier_and_timeout():
+    from tests.helpers import free_port, run_ranks
+
+    outs = run_ranks(os.path.join(ROOT, "tests/ranks/stateless_pg.py"), 3, args=[free_port()], timeout=120)
+    assert "RESULT rank=0 timeout:" in outs[0] and "RESULT rank=1 timeout:" in outs[1], outs
+    assert "missing ranks" in "".join(outs) or "['2']" in "".join(outs)
+    assert "RESULT rank=2 absent" in outs[2]
+
+
+def test_nccl_library_binding_loads_and_reports_version():
+    from halite_b200.distributed.pynccl_wrapper import NCCLLibrary, ncclDataTypeEnum, ncclRedOpTypeEnum
+    from torch.distributed import ReduceOp
+
+    lib = NCCLLibrary()
+    major = int(lib.ncclGetVersion().split(".")[0])
+    assert major >= 2
+    assert ncclDataTypeEnum.from_torch(torch.bfloat16) == 9 and ncclRedOpTypeEnum.from_torch(ReduceOp.MAX) == 2
+    uid = lib.unique_id_from_bytes(bytes(range(128)))
+    assert bytes(uid.internal)[:4] == bytes([0, 1, 2, 3])
