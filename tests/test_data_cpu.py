@@ -112,3 +112,85 @@ def test_packing_meta_and_collator():
     assert len(batch["_meta_"]["samples_meta"]) == 3
     rows = batch.unbind(["input"])
     assert len(rows) == 3 and rows[1]["input"].shape == (9,)
+
+
+def test_sft_sample_masks_prompt_and_packing_pads_rows():
+    from halite_b200.projects.sft.preprocess import (SFTSample, SFTSequencePacking, collate_offsets,
+                                                     length_to_offsets)
+
+    tok = ByteTokenizer()
+    sample = SFTSample("q", "a", tok, prompt_tokenizer_kwargs={"bos": True}, response_tokenizer_kwargs={"eos": True})
+    rec = sample.process(Record(q="ab", a="xyz", _meta_={"dataset_id": 0, "sample_id": 5}))
+    assert rec["input"].tolist() == [tok.bos_id, 97, 98, 120, 121, 122, tok.eos_id]
+    # prompt positions ignored; position of the last prompt token predicts the first response token
+    assert rec["target"].tolist() == [-100, -100, 120, 121, 122, tok.eos_id, -100]
+
+    def recs(lengths):
+        for i, n in enumerate(lengths):
+            yield Record(input=torch.arange(n) + 100 * i, target=torch.arange(n) + 100 * i + 1,
+                         _meta_={"dataset_id": 0, "sample_id": i})
+
+    pack = SFTSequencePacking(8, use_position_ids=True, use_document_offsets=True)
+    rows = list(pack(recs([3, 4, 5, 8, 11, 2])))
+    assert all(len(r["input"]) == 8 and len(r["target"]) == 8 for r in rows)
+    assert rows[0]["input"].tolist() == [0, 1, 2, 100, 101, 102, 103, 0]          # 3 + 4, one pad
+    assert rows[0]["target"].tolist()[-1] == -100
+    assert rows[0]["document_offsets"].tolist() == [0, 3, 7, 8]
+    assert rows[0]["position_ids"].tolist() == [0, 1, 2, 0, 1, 2, 3, 0]
+    assert rows[0]["_meta_"]["sample_ids"] == [0, 1]
+    assert rows[1]["input"].tolist()[:5] == [200, 201, 202, 203, 204] and rows[2]["_meta_"]["sample_ids"] == [3]
+    assert rows[3]["input"].tolist() == list(range(400, 408))                      # long sample truncated
+    assert rows[4]["_meta_"]["sample_ids"] == [5] and len(rows) == 5
+    keep = SFTSequencePacking(8, use_rest_of_long_sequence=True)
+    rows2 = list(keep(recs([11])))
+    assert [r["input"].tolist()[:3] for r in rows2] == [[0, 1, 2], [8, 9, 10]]
+    assert length_to_offsets([2, 4, 3]).tolist() == [0, 2, 6, 9]
+    assert collate_offsets([torch.tensor([0, 3, 8]), torch.tensor([0, 8])], 4).tolist() == [[0, 3, 8, 8], [0, 8, 8, 8]]
+    # state round trip in the middle of a stream
+    a = SFTSequencePacking(8)
+    it = a(recs([3, 4, 5, 2, 6]))
+    first = next(it)
+    b = SFTSequencePacking(8)
+    b.load_state_dict(a.state_dict())
+    assert len(b.state_dict()["input_ids"]) == len(a._pending) and first["input"].shape == (8,)
+
+
+def test_tools_convert_gather_and_sanity(tmp_path, capsys):
+    import sys
+
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "scripts/tools"))
+    import convert_to_records
+    import gather_dataset
+    import sample_sanity
+
+    raw = tmp_path / "raw"
+    raw.mkdir()
+    for part in range(2):
+        with open(raw / f"p{part}.jsonl", "w") as f:
+            for i in range(25):
+                f.write(json.dumps({"text": f"doc {part}-{i} " + "lorem ipsum " * 8}) + "\n")
+    out = tmp_path / "corpus" / "web"
+    spec = convert_to_records.main(["--output", str(out), "--shard_size", "20", str(raw / "*.jsonl")])
+    assert sorted(spec.values()) == [10, 20, 20] and all(n.endswith("-of-3.hbrec") for n in spec)
+    rr = convert_to_records.main(["--output", str(tmp_path / "corpus" / "rr"), "--n_shards", "2", "--shuffle",
+                                  str(raw / "*.jsonl")])
+    assert sorted(rr.values()) == [25, 25]
+    gathered = gather_dataset.main(["--ext", "hbrec", str(tmp_path / "corpus")])
+    assert set(gathered["shards"]) == {"web", "rr"} and gathered["ratios"]["web"] == pytest.approx(0.5)
+    assert gathered["shards"]["web"] == spec
+    conf = tmp_path / "configs" / "exp.py"
+    conf.parent.mkdir()
+    conf.write_text(f'''
+from halite_b200.conf import field
+from halite_b200.data import preprocess
+from halite_b200.data.tokenizers import ByteTokenizer
+conf = field()
+conf.model = field(tokenizer=ByteTokenizer())
+conf.data = field(train={json.dumps(gathered)}, train_ratio=1.0,
+    preprocess=[preprocess.ParseFeatures(), preprocess.Tokenize(ByteTokenizer(), bos=True, eos=True),
+                preprocess.SequencePacking(33), preprocess.AutoregressiveSample()],
+    collate_fn=preprocess.Collator(keys=("input", "target")))
+''')
+    dumped = sample_sanity.main(["--conf", str(conf), "--n_batch", "2", "--output", str(tmp_path / "dump.json")])
+    assert len(dumped) == 2 and dumped[0]["input"]["shape"] == [2, 32] and "doc" in dumped[0]["input"]["text"][0] + dumped[1]["input"]["text"][0]
+    assert (tmp_path / "dump.json").exists()
