@@ -54,3 +54,52 @@ def test_ppo_script_runs_grpo_iterations_and_checkpoints(tmp_path):
     assert "actor/pg_loss" in logs and "critic/rewards_mean" in logs and "sample/response_len/mean" in logs
     assert "[reward]" in logs and "[output]" in logs
     assert sorted(os.listdir(out)) == ["step-2", "step-4"]
+
+
+def test_eval_task_script_on_a_saved_model_folder(tmp_path, monkeypatch):
+    """Save a tiny model folder (config.json + DCP weights + tokenizer config), then run the
+    evaluation entry point on a local task; generation is greedy so two runs agree."""
+    import sys
+
+    import torch
+    import torch.distributed.checkpoint as dcp
+
+    from halite_b200.conf import instantiate, load_config
+    from halite_b200.projects.common.config import Model
+
+    section = load_config(os.path.join(ROOT, "tests/configs/tiny_model.py"))
+    model_conf = Model(**section)
+    torch.manual_seed(0)
+    model = instantiate(model_conf.model)
+    model.init_weights()
+    folder = tmp_path / "model"
+    model_conf.save(str(folder))
+    dcp.save({"model": model.state_dict()}, checkpoint_id=str(folder))
+    assert (folder / "config.json").exists() and (folder / "halite_tokenizer_config.json").exists()
+
+    data = tmp_path / "qa.jsonl"
+    with open(data, "w") as f:
+        for i in range(6):
+            f.write(json.dumps({"problem": f"{i}+{i}", "solution": f"\\boxed{{{2 * i}}}"}) + "\n")
+    task = tmp_path / "configs" / "task.py"
+    task.parent.mkdir()
+    task.write_text(f'''
+from halite_b200.conf import field, function
+from halite_b200.conf.loader import load_module
+from halite_b200.data.preprocess import Map, SelectFeatures
+from halite_b200.projects.eval.dataset import jsonl_dataset
+_m = load_module("{ROOT}/configs/eval/tasks/minerva_math/eval.py")
+conf = field(tasks=[field(
+    name="toy_math", dataset=jsonl_dataset("{data}"), evaluate_fn=function(_m.evaluate),
+    preprocess=[SelectFeatures(keys=("problem", "solution")), Map(function(_m.record_to_input))],
+    sampling_params=field(max_new_tokens=8, top_k=1))])
+''')
+    sys.path.insert(0, os.path.join(ROOT, "scripts"))
+    import eval_task
+
+    monkeypatch.setenv("WORLD_SIZE", "1")
+    out = tmp_path / "result.json"
+    res = eval_task.main(["--model", str(folder), "--task", str(task), "--device", "cpu", "--output", str(out),
+                          "batch_size=4"])
+    assert res["toy_math"]["n_samples"] == 6 and 0.0 <= res["toy_math"]["exact_match"] <= 1.0
+    assert json.loads(out.read_text())["toy_math"]["n_samples"] == 6
