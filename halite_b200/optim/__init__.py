@@ -50,6 +50,9 @@ def build_optimizer(factory, model, weight_decay: float = 0.0):
         if fn in (torch.optim.AdamW, torch.optim.Adam, ShardedAdamW):
             kw.pop("fused", None)
             kw.pop("foreach", None)
+            if "weight_decay" in kw:      # the factory's own value wins only when none was passed
+                wd = kw.pop("weight_decay")
+                weight_decay = weight_decay if weight_decay else wd
             if fn is torch.optim.Adam:
                 weight_decay = 0.0
             return ShardedAdamW(model, weight_decay=weight_decay, **kw)

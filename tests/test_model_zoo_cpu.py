@@ -130,3 +130,44 @@ def test_scaling_diff_transformer_and_ngpt_configs_train():
     w = m.blocks["0"].self_attention.module.q.weight
     torch.testing.assert_close(w.norm(dim=1), torch.ones(32), rtol=1e-4, atol=1e-4)
     assert "blocks.0.self_attention.scale.weight" in m.state_dict()
+
+
+def test_jit_and_diffusion_objectives():
+    from halite_b200.projects.dit.diffusion import Diffusion, EquilibriumMatchingJiT
+
+    jit = load_module(os.path.join(ROOT, "configs/models/jit.py"))
+    model = build(jit.jit(image_size=16, patch_size=4, n_labels=10, dim=32, patch_dim=16, n_heads=2, head_dim=16,
+                          n_layers=3, intermediate_size=64, in_context_len=2, in_context_start=1, qk_norm=True))
+    x, lab = torch.randn(4, 3, 16, 16), torch.randint(0, 10, (4,))
+    out = model(x, torch.rand(4), lab)
+    assert out.shape == x.shape and out.abs().max() == 0          # adaLN-Zero: the head starts at zero
+    assert "in_context_rope.freqs_cos" in model.state_dict() and "post_embed.linear.weight" in model.state_dict()
+    d = Diffusion((3, 16, 16), 10, steps=4, guidance_scale=2.0, guidance_interval=(0.1, 1.0))
+
+    def fixed_loss():
+        torch.manual_seed(123)
+        model.eval()
+        v = sum(d.loss(model, x, lab).item() for _ in range(8)) / 8
+        model.train()
+        return v
+
+    before = fixed_loss()
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+    torch.manual_seed(1)
+    for _ in range(120):
+        d.loss(model, x, lab).backward()
+        torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+        opt.step()
+        opt.zero_grad()
+    assert fixed_loss() < 0.7 * before
+    model.eval()
+    a, b = d.generate(model, lab, seed=1), d.generate(model, lab, seed=1)
+    assert a.shape == x.shape and torch.equal(a, b) and torch.isfinite(a).all()
+    # label dropping only while training; the unconditional id is n_labels
+    d.train()
+    d.label_drop_p = 1.0
+    assert (d.drop_labels(lab) == 10).all()
+    e = EquilibriumMatchingJiT((3, 16, 16), 10, steps=3, method="euler")
+    t = torch.tensor([0.0, 0.8, 1.0]).view(-1, 1, 1, 1)
+    assert e.get_c_t(t).flatten().tolist() == pytest.approx([4.0, 4.0, 0.0], abs=1e-5)
+    assert torch.isfinite(e.loss(model, x, lab)) and e.generate(model, lab, seed=0).shape == x.shape

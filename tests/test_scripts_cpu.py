@@ -103,3 +103,19 @@ conf = field(tasks=[field(
                           "batch_size=4"])
     assert res["toy_math"]["n_samples"] == 6 and 0.0 <= res["toy_math"]["exact_match"] <= 1.0
     assert json.loads(out.read_text())["toy_math"]["n_samples"] == 6
+
+
+def test_dit_script_trains_samples_and_saves_ema(tmp_path):
+    out = str(tmp_path / "out")
+    logs = " ".join(run_ranks(os.path.join(ROOT, "scripts/dit.py"), 2,
+                              args=["--conf", os.path.join(ROOT, "tests/configs/tiny_jit.py")], timeout=900,
+                              env_extra={"HB_TEST_OUT": out})[0].split())
+    steps = [int(x) for x in re.findall(r"global (\d+); loss", logs)]
+    assert steps == [0, 2, 4, 6, 8], logs[-3000:]
+    files = sorted(os.listdir(os.path.join(out, "tiny")))
+    assert "ema-0000005.pt" in files and "ema-0000010.pt" in files, files
+    assert any(f.startswith("samples-0000005") for f in files)
+    import torch
+
+    ema = torch.load(os.path.join(out, "tiny", "ema-0000010.pt"))
+    assert "blocks.0.modulator.linear.weight" in ema and ema["head.linear.weight"].shape == (48, 32)
