@@ -19,6 +19,10 @@
 // Replaces the cuBLAS calls behind every nn.Linear of the reference
 // (configs/models/transformer.py:124-177,292).
 #include <stdio.h>
+#include <stdlib.h>
+
+#include <mutex>
+#include <vector>
 
 #include "gemm.h"
 #include "sm100.cuh"
@@ -238,13 +242,52 @@ __device__ __forceinline__ void gather_copy_cta(const GatherParams& gp, int cta,
   }
 }
 
+// Work schedule. Items [0, full) are whole tiles. When the last wave would leave most SMs idle,
+// its `tail` tiles are each cut into `parts` slices along K (items full .. full + tail * parts):
+// every slice leaves its fp32 partial tile in a workspace and bumps a per-tile counter; whichever
+// slice arrives last adds the partials in slice order (so the sum does not depend on timing) and
+// writes the tile.
+struct SplitParams {
+  int full = 0;        // number of whole-tile items
+  int parts = 1;       // K slices per tail tile
+  int kb_per = 0;      // k-blocks per slice
+  int items = 0;       // total number of work items
+  int prefetch = 0;    // k-blocks of L2 prefetch ahead of the shared-memory loads (0 = off)
+  float* workspace = nullptr;   // [tail][parts][4 quarters][BN/32][32 lanes][32] floats
+  int* counters = nullptr;      // [tail][4 quarters], zeroed by the launcher
+};
+
+struct WorkItem {
+  int tile, kb_begin, kb_end, part, tail_index;
+};
+
+__device__ __forceinline__ WorkItem decode_item(const SplitParams& kp, int w, int num_kb) {
+  WorkItem it;
+  if (w < kp.full || kp.parts <= 1) {
+    it.tile = w;
+    it.kb_begin = 0;
+    it.kb_end = num_kb;
+    it.part = -1;
+    it.tail_index = 0;
+  } else {
+    const int r = w - kp.full;
+    it.tail_index = r / kp.parts;
+    it.part = r - it.tail_index * kp.parts;
+    it.tile = kp.full + it.tail_index;
+    it.kb_begin = it.part * kp.kb_per;
+    it.kb_end = min(num_kb, it.kb_begin + kp.kb_per);
+  }
+  return it;
+}
+
 template <int BN, bool A_MN, bool B_MN, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
                  const __grid_constant__ CUtensorMap tma_b, OutT* __restrict__ D, int M, int N,
                  int K, int ldd, int accumulate, int* __restrict__ status,
                  const __grid_constant__ GatherParams gp,
-                 const __grid_constant__ ScatterParams sp) {
+                 const __grid_constant__ ScatterParams sp,
+                 const __grid_constant__ SplitParams kp) {
   using C = Cfg<BN>;
   constexpr int kStages = C::kStages;
 
@@ -290,6 +333,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
 
   // With a fused gather the first `n_copy` CTAs only copy; the rest share the tiles.
   const int m_rot = gp.m_rot + sp.m_rot;
+  const int n_items = kp.parts > 1 ? kp.items : num_tiles;
   const int n_copy = gp.n_copy_ctas;
   const int first_tile = static_cast<int>(blockIdx.x) - n_copy;
   const int tile_step = static_cast<int>(gridDim.x) - n_copy;
@@ -301,16 +345,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+    for (int w = first_tile; w < n_items && ok; w += tile_step) {
+      const WorkItem it = decode_item(kp, w, num_kb);
       int tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      tile_coords(it.tile, tiles_m, tiles_n, tm, tn);
       if (m_rot) tm = (tm + m_rot) % tiles_m;
       const int m0 = tm * kBM, n0 = tn * BN;
       if (gp.dep == 1) ok = wait_rows(gp, m0, kBM, M, &abort_flag, status);
       if (gp.dep == 2) ok = wait_rows(gp, n0, BN, N, &abort_flag, status);
       if (!ok) break;
       if (gp.dep) fence_proxy_async();  // copied data was written by generic stores; TMA reads it
-      for (int kb = 0; kb < num_kb; ++kb) {
+      for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
         ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1, &abort_flag, status, kTimeoutEmpty);
         if (!ok) break;
         const uint32_t full = smem_u32(&bar_full[stage]);
@@ -318,6 +363,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
         const uint32_t sb = sa + C::kABytes;
         mbar_expect_tx(full, C::kStageBytes);
         const int k0 = kb * kBK;
+        if (kp.prefetch > 0 && kb + kp.prefetch < it.kb_end) {
+          // warm L2 for a later k-block: the real loads then see L2 latency instead of DRAM's
+          const int kf = (kb + kp.prefetch) * kBK;
+          if (!A_MN) {
+            tma_prefetch_2d(&tma_a, kf, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < kBM / 64; ++c) tma_prefetch_2d(&tma_a, m0 + c * 64, kf);
+          }
+          if (!B_MN) {
+            tma_prefetch_2d(&tma_b, kf, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) tma_prefetch_2d(&tma_b, n0 + c * 64, kf);
+          }
+        }
         if (!A_MN) {
           tma_load_2d(sa, &tma_a, full, k0, m0);
         } else {
@@ -343,7 +404,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
     uint32_t phase = 0;
     int local = 0;
     bool ok = true;
-    for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++local) {
+    for (int w = first_tile; w < n_items && ok; w += tile_step, ++local) {
+      const WorkItem it = decode_item(kp, w, num_kb);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       ok = mbar_wait(smem_u32(&bar_tempty[acc]), acc_phase ^ 1, &abort_flag, status,
@@ -351,7 +413,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
       if (!ok) break;
       tc_fence_after();
       const uint32_t tmem_d = tmem_base + acc * BN;
-      for (int kb = 0; kb < num_kb; ++kb) {
+      for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
         ok = mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag, status, kTimeoutFull);
         if (!ok) break;
         tc_fence_after();
@@ -364,7 +426,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
                                    : make_smem_desc(sa + k * 32, 0, 1024);
           const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, 8192, 1024)
                                    : make_smem_desc(sb + k * 32, 0, 1024);
-          umma_bf16(tmem_d, da, db, idesc, (kb | k) != 0);
+          umma_bf16(tmem_d, da, db, idesc, ((kb - it.kb_begin) | k) != 0);
         }
         umma_commit(smem_u32(&bar_empty[stage]));  // frees the smem stage when the MMAs retire
         if (++stage == kStages) {
@@ -382,9 +444,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
                         ((reinterpret_cast<uintptr_t>(D) & 15) == 0);
     int local = 0;
     bool ok = true;
-    for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++local) {
+    for (int w = first_tile; w < n_items && ok; w += tile_step, ++local) {
+      const WorkItem it = decode_item(kp, w, num_kb);
       int tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      tile_coords(it.tile, tiles_m, tiles_n, tm, tn);
       if (m_rot) tm = (tm + m_rot) % tiles_m;
       const int m0 = tm * kBM, n0 = tn * BN;
       const int acc = local & 1;
@@ -395,6 +458,61 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+      if (it.part >= 0) {
+        // ---- K-slice of a tail tile: park the fp32 partial, last arriver reduces in slice order
+        constexpr int kQuarterFloats = (BN / 32) * 32 * 32;
+        float* slot0 = kp.workspace +
+                       (static_cast<size_t>(it.tail_index) * kp.parts * 4 + q) * kQuarterFloats;
+        float* mine = slot0 + static_cast<size_t>(it.part) * 4 * kQuarterFloats;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + c * 32, v);
+          tmem_ld_wait();
+          float4* dst = reinterpret_cast<float4*>(mine + (c * 32 + lane) * 32);
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            dst[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                 __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+        }
+        tc_fence_before();
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[acc]));
+        int prev = 0;
+        if (lane == 0) prev = atomicAdd(kp.counters + it.tail_index * 4 + q, 1);
+        prev = __shfl_sync(0xffffffffu, prev, 0);
+        if (prev == kp.parts - 1) {
+          __threadfence();
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            float f[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = 0.f;
+            for (int pp = 0; pp < kp.parts; ++pp) {
+              const float4* src = reinterpret_cast<const float4*>(
+                  slot0 + static_cast<size_t>(pp) * 4 * kQuarterFloats + (c * 32 + lane) * 32);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float4 x = __ldcg(src + i);
+                f[4 * i] += x.x;
+                f[4 * i + 1] += x.y;
+                f[4 * i + 2] += x.z;
+                f[4 * i + 3] += x.w;
+              }
+            }
+            uint32_t v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(f[j]);
+            const int col = n0 + c * 32;
+            if (row < M && col < N) {
+              OutT* base = D + static_cast<size_t>(row) * ldd;
+              store_chunk<OutT>(base + col, v, min(32, N - col), vec_ok, accumulate != 0);
+            }
+          }
+        }
+        continue;
+      }
       if constexpr (sizeof(OutT) == 2) {
         if (sp.n_chunks > 0 || (vec_ok && !accumulate && staged_epilogue)) {
           // The warp's 32 x 64 sub-tile is transposed through shared memory (128B-swizzled,
@@ -541,6 +659,66 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+constexpr int kDefaultL2Prefetch = 0;
+// k-blocks of L2 prefetch issued ahead of the pipeline (HB_GEMM_L2_PREFETCH overrides; 0 = off).
+int l2_prefetch_distance() {
+  static int dist = -1;
+  if (dist < 0) {
+    const char* env = getenv("HB_GEMM_L2_PREFETCH");
+    dist = env ? atoi(env) : kDefaultL2Prefetch;
+    if (dist < 0 || dist > 64) dist = 0;
+  }
+  return dist;
+}
+
+// Scratch for the split-K tail (partials + arrival counters), one fixed-size slot per
+// (device, stream) so GEMMs on different streams never share it. A slot is allocated the first
+// time a stream needs one, outside of stream capture; while a stream is being captured into a
+// CUDA graph and has no slot yet, the GEMM simply runs without the split.
+constexpr size_t kSplitWsBytes = size_t(20) << 20;   // >= 148 slices x 128 x 256 fp32
+constexpr int kSplitCounters = 1024;
+
+cudaError_t split_workspace(size_t bytes, int n_counters, cudaStream_t stream, float** ws, int** counters) {
+  struct Slot {
+    int dev;
+    cudaStream_t stream;
+    float* ws;
+    int* counters;
+  };
+  static std::vector<Slot> slots;
+  static std::mutex lock;
+  if (bytes > kSplitWsBytes || n_counters > kSplitCounters) return cudaErrorInvalidValue;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> hold(lock);
+  for (const Slot& s : slots) {
+    if (s.dev == dev && s.stream == stream) {
+      *ws = s.ws;
+      *counters = s.counters;
+      return cudaSuccess;
+    }
+  }
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+    (void)cudaGetLastError();
+    return cudaErrorStreamCaptureUnsupported;
+  }
+  if (slots.size() >= 32) return cudaErrorMemoryAllocation;   // bounded: 32 x 20 MB
+  Slot s{dev, stream, nullptr, nullptr};
+  e = cudaMalloc(&s.ws, kSplitWsBytes);
+  if (e != cudaSuccess) return e;
+  e = cudaMalloc(&s.counters, sizeof(int) * kSplitCounters);
+  if (e != cudaSuccess) {
+    cudaFree(s.ws);
+    return e;
+  }
+  slots.push_back(s);
+  *ws = s.ws;
+  *counters = s.counters;
+  return cudaSuccess;
+}
+
 EncodeTiledFn get_encode_fn() {
   static EncodeTiledFn fn = nullptr;
   if (fn) return fn;
@@ -635,6 +813,36 @@ cudaError_t launch(const GemmArgs& g) {
     grid = tiles < sm_count() ? tiles : sm_count();
     if (g.max_ctas > 0 && grid > g.max_ctas) grid = g.max_ctas;
   }
+  SplitParams kp;
+  kp.prefetch = l2_prefetch_distance();
+  if (!g.gather && !g.scatter) {
+    // cut the tiles of a mostly idle last wave along K (see SplitParams)
+    const int base = (g.max_ctas > 0 && g.max_ctas < sm_count()) ? g.max_ctas : sm_count();
+    const int num_kb = (g.K + kBK - 1) / kBK;
+    const int rem = tiles % base;
+    if (rem > 0 && rem * 2 <= base && num_kb >= 16) {
+      int parts = base / rem;
+      if (parts > 8) parts = 8;
+      while (parts > 1 && ((num_kb + parts - 1) / parts < 8 ||
+                           (parts - 1) * ((num_kb + parts - 1) / parts) >= num_kb))
+        --parts;   // every slice gets at least 8 k-blocks and none is empty
+      if (parts > 1) {
+        const size_t ws_bytes = static_cast<size_t>(rem) * parts * kBM * BN * sizeof(float);
+        float* ws = nullptr;
+        int* counters = nullptr;
+        if (split_workspace(ws_bytes, rem * 4, g.stream, &ws, &counters) == cudaSuccess) {
+          kp.full = tiles - rem;
+          kp.parts = parts;
+          kp.kb_per = (num_kb + parts - 1) / parts;
+          kp.items = kp.full + rem * parts;
+          kp.workspace = ws;
+          kp.counters = counters;
+          cudaMemsetAsync(counters, 0, sizeof(int) * rem * 4, g.stream);
+          grid = kp.items < base ? kp.items : base;
+        }
+      }
+    }
+  }
   ScatterParams sp;
   if (g.scatter) {
     sp = *g.scatter;
@@ -644,7 +852,7 @@ cudaError_t launch(const GemmArgs& g) {
     cudaMemsetAsync(sp.cta_counter, 0, sizeof(int), g.stream);
   }
   kern<<<grid, kThreads, C::kSmemBytes, g.stream>>>(ta, tb, static_cast<OutT*>(g.d), g.M, g.N, g.K,
-                                                    g.ldd, g.accumulate ? 1 : 0, g.status, gp, sp);
+                                                    g.ldd, g.accumulate ? 1 : 0, g.status, gp, sp, kp);
   return cudaGetLastError();
 }
 

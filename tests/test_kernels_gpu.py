@@ -68,6 +68,27 @@ def test_gemm_fp32_out_and_accumulate(C):
     assert rel_err(wide[:, 128:896], ref) < 6e-3 and wide[:, :128].abs().max() == 0
 
 
+@pytest.mark.parametrize("shape", [(5120, 3072, 2048), (640, 256, 8192), (3072, 8192, 1024)])
+def test_gemm_split_k_tail_is_exact_and_deterministic(C, shape):
+    """Shapes whose last wave is mostly idle take the K-sliced tail schedule: results must match
+    the plain schedule's accuracy, accumulate correctly into fp32, and repeat bit for bit."""
+    from halite_b200.ops import gemm
+
+    M, N, K = shape
+    torch.manual_seed(3)
+    A = torch.randn(K, M, device="cuda", dtype=torch.bfloat16)      # wgrad layout: both MN-major
+    B = torch.randn(K, N, device="cuda", dtype=torch.bfloat16)
+    ref = A.float().t() @ B.float()
+    out = gemm(A, B, a_mn=True, b_mn=True, out_dtype=torch.float32)
+    assert rel_err(out, ref) < 1e-5
+    again = gemm(A, B, a_mn=True, b_mn=True, out_dtype=torch.float32)
+    assert torch.equal(out, again)
+    gemm(A, B, out=out, a_mn=True, b_mn=True, accumulate=True)
+    assert rel_err(out, 2 * ref) < 1e-5
+    ob = gemm(A, B, a_mn=True, b_mn=True)
+    assert rel_err(ob, ref) < 6e-3
+
+
 def test_linear_autograd_matches_torch(C):
     from halite_b200 import ops
 
