@@ -145,6 +145,8 @@ void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& out, bool a_mn, 
 void register_elementwise(pybind11::module_& m);  // ops_bindings.cpp
 void register_infer(pybind11::module_& m);        // infer_bindings.cpp
 
+void register_runtime(py::module_& m);
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, "bf16 tcgen05 GEMM", py::arg("a"), py::arg("b"), py::arg("out"),
         py::arg("a_mn") = false, py::arg("b_mn") = false, py::arg("accumulate") = false,
@@ -157,4 +159,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("reset_launch_count", []() { hb::launch_counter().store(0); });
   register_elementwise(m);
   register_infer(m);
+  register_runtime(m);
 }

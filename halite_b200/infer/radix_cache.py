@@ -249,3 +249,78 @@ class RadixCache:
                     assert x is self.root or x.lock_ref >= c.lock_ref
                 stack.append(c)
         assert ev == self.evictable_pages and pr == self.protected_pages, (ev, pr, self.evictable_pages, self.protected_pages)
+
+
+class NativeRadixCache(RadixCache):
+    """Same contract as `RadixCache`, with the tree itself in C++ (`_C.RadixTree`): matching,
+    insertion, lock counting and LRU eviction run without touching Python objects per node. Node
+    handles are integers (0 = root)."""
+
+    def __init__(self, page_size: int, kv_pool, disable: bool = False):
+        from halite_b200.csrc import build
+
+        self._ext = build.load()
+        self.page_size = page_size
+        self.kv_pool = kv_pool
+        self.disable = disable
+        self.tree = self._ext.RadixTree(page_size)
+        self.root = 0
+
+    def reset(self):
+        self.tree.reset()
+
+    @property
+    def evictable_pages(self):
+        return self.tree.evictable_pages
+
+    @property
+    def protected_pages(self):
+        return self.tree.protected_pages
+
+    def match_prefix(self, tokens):
+        if self.disable:
+            return [], 0
+        return self.tree.match_prefix(list(tokens))
+
+    def insert(self, tokens, pages):
+        if self.disable:
+            return 0
+        return self.tree.insert(list(tokens), list(pages))
+
+    def inc_lock_ref(self, node):
+        if not self.disable and node:
+            self.tree.inc_lock_ref(node)
+
+    def dec_lock_ref(self, node):
+        if not self.disable and node:
+            self.tree.dec_lock_ref(node)
+
+    def evict(self, n_pages: int):
+        if self.disable or n_pages <= 0:
+            return 0
+        freed = self.tree.evict(n_pages)
+        self.kv_pool.free(freed)
+        return len(freed)
+
+    def total_pages(self):
+        return self.tree.total_pages()
+
+    def sanity_check(self):
+        self.tree.sanity_check()
+
+
+def make_radix_cache(page_size, kv_pool, disable=False, backend="auto"):
+    """`backend`: "native" (C++ tree), "python", or "auto" = native when the extension is
+    already built, else Python."""
+    if backend == "python":
+        return RadixCache(page_size, kv_pool, disable)
+    if backend == "native":
+        return NativeRadixCache(page_size, kv_pool, disable)
+    try:
+        from halite_b200.csrc import build
+
+        if build.is_current():
+            return NativeRadixCache(page_size, kv_pool, disable)
+    except Exception:  # noqa: BLE001
+        pass
+    return RadixCache(page_size, kv_pool, disable)

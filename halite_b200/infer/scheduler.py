@@ -14,7 +14,7 @@ import uuid
 import torch
 
 from halite_b200.infer.batch import Batch, ForwardMode, Request
-from halite_b200.infer.radix_cache import RadixCache
+from halite_b200.infer.radix_cache import RadixCache, make_radix_cache  # noqa: F401
 from halite_b200.infer.schedule_policy import PrefillAdder
 from halite_b200.infer.types import InferenceRequest, SamplingParams, ServerConfig
 from halite_b200.logging import logger
@@ -54,8 +54,9 @@ class Scheduler:
         self.req_pool = mr.req_pool
         self.kv_pool = mr.kv_pool
         self.device = mr.device
-        self.tree_cache = RadixCache(self.server_config.page_size, self.kv_pool,
-                                     disable=self.server_config.disable_radix_cache)
+        self.tree_cache = make_radix_cache(self.server_config.page_size, self.kv_pool,
+                                           disable=self.server_config.disable_radix_cache,
+                                           backend=self.server_config.radix_backend)
         self.max_running_requests = mr.max_running_requests
         self.waiting_queue: list[Request] = []
         self.running_batch: Batch | None = None

@@ -106,6 +106,7 @@ class ServerConfig:
     max_total_tokens: int | None = None      # overrides the memory-derived KV budget
     decode_steps_ahead: int = 8              # decode steps launched before the host reads tokens
     disable_radix_cache: bool = False
+    radix_backend: str = "auto"            # "native" (C++ tree), "python", or "auto"
     seed: int = 0
 
 

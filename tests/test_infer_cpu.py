@@ -160,9 +160,12 @@ def test_sampler_distribution_and_filters():
     assert ids.tolist() == [0, 0, 0, 0]
 
 
-def test_radix_cache_pages():
+@pytest.mark.parametrize("backend", ["python", "native"])
+def test_radix_cache_pages(backend):
+    from halite_b200.infer.radix_cache import make_radix_cache
+
     pool = PagedKVPool(64, 4, 1, 1, 8, torch.float32, "cpu")
-    tree = RadixCache(4, pool)
+    tree = make_radix_cache(4, pool, backend=backend)
     a = list(range(12))
     pa = pool.alloc(3)
     assert tree.insert(a, pa) == 0
@@ -185,3 +188,57 @@ def test_radix_cache_pages():
     tree.sanity_check()
     # partial page never matches
     assert tree.match_prefix([1, 2, 3])[0] == []
+
+
+def test_native_radix_tree_agrees_with_python_under_random_traffic():
+    """Random inserts / matches / locks / evictions against both trees: same matched pages,
+    same counters, invariants hold; plus the native page allocator."""
+    import random
+
+    from halite_b200.infer.radix_cache import NativeRadixCache
+
+    rng = random.Random(0)
+    ps = 4
+    pools = [PagedKVPool(4096, ps, 1, 1, 8, torch.float32, "cpu") for _ in range(2)]
+    trees = [RadixCache(ps, pools[0]), NativeRadixCache(ps, pools[1])]
+    stems = [[rng.randrange(50) for _ in range(ps * rng.randrange(1, 6))] for _ in range(8)]
+    locked = []
+    for step in range(400):
+        seq = list(rng.choice(stems)) + [rng.randrange(50) for _ in range(ps * rng.randrange(0, 4))]
+        op = rng.random()
+        if op < 0.5:
+            outs = []
+            for tree, pool in zip(trees, pools):
+                matched, _ = tree.match_prefix(seq)
+                fresh = pool.alloc(len(seq) // ps - len(matched))
+                shared = tree.insert(seq[: (len(seq) // ps) * ps], matched + fresh)
+                pool.free(fresh[: max(0, shared - len(matched))])
+                outs.append((len(matched), shared))
+            assert outs[0] == outs[1]
+        elif op < 0.7:
+            res = [tree.match_prefix(seq + [7]) for tree in trees]
+            assert len(res[0][0]) == len(res[1][0])
+            if res[0][0] and len(locked) < 6:
+                for tree, (_, node) in zip(trees, res):
+                    tree.inc_lock_ref(node)
+                locked.append([r[1] for r in res])
+        elif op < 0.8 and locked:
+            nodes = locked.pop(rng.randrange(len(locked)))
+            for tree, node in zip(trees, nodes):
+                tree.dec_lock_ref(node)
+        else:
+            n = rng.randrange(1, 12)
+            assert trees[0].evict(n) == trees[1].evict(n)
+        assert trees[0].evictable_pages == trees[1].evictable_pages
+        assert trees[0].protected_pages == trees[1].protected_pages
+        assert pools[0].available_pages() == pools[1].available_pages()
+        if step % 50 == 0:
+            for tree in trees:
+                tree.sanity_check()
+    assert trees[0].total_pages() == trees[1].total_pages() > 0
+    alloc = trees[1]._ext.PageAllocator(10)
+    first = alloc.alloc(3)
+    assert first == [3, 2, 1] or sorted(first) == [1, 2, 3]
+    assert alloc.alloc(8) is None and alloc.available() == 7
+    alloc.free(first)
+    assert alloc.available() == 10 and alloc.capacity() == 10
