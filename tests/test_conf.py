@@ -159,3 +159,25 @@ conf.hparams = field(a=1)
     assert "SGD" in text and "max_iter" in text
     with pytest.raises(Exception):
         Main(training={"max_iter": "x", "optimizer": {}})
+
+
+def test_shipped_experiment_configs_load_and_validate():
+    """Every pre-training experiment under configs/lm validates against the LM schema and its
+    model builds on the meta device with the expected parameter count."""
+    import os
+
+    import torch
+
+    from halite_b200.conf import instantiate, load_config
+    from halite_b200.projects.lm.config import LMConfig
+
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "configs", "lm")
+    expect = {"dense_662m.py": (0.55e9, 0.8e9), "dense_1.7b.py": (1.4e9, 2.0e9), "diff_transformer_383m.py": (0.3e9, 0.5e9),
+              "moe_383m.py": (1.5e9, 5e9), "ngpt_383m.py": (0.3e9, 0.5e9), "scale_383m_soap.py": (0.3e9, 0.5e9)}
+    for name, (lo, hi) in expect.items():
+        conf = load_config(os.path.join(root, name), schema=LMConfig)
+        assert conf.training.train_batch_size == 320 and conf.data.preprocess is not None
+        with torch.device("meta"):
+            model = instantiate(conf.model.model)
+        n = sum(p.numel() for p in model.parameters())
+        assert lo < n < hi, (name, n)
