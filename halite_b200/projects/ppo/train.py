@@ -69,8 +69,10 @@ def _get(conf, key, default=None):
 
 
 class PPOLoop:
-    def __init__(self, conf, device=None, server_config: ServerConfig | None = None, num_workers=4):
+    def __init__(self, conf, device=None, server_config=None, num_workers=4, engine="paged"):
+        """`engine`: "paged" = the in-process engine, "tokainfer" = the manager + worker engine."""
         self.conf = conf
+        self.engine_kind = engine
         t = conf.training
         self.pdims = ParallelDims(dp_replicate=t.data_parallel_replicate, dp_shard=t.data_parallel_shard,
                                   tp=t.tensor_parallel, pp=t.pipeline_parallel)
@@ -131,7 +133,10 @@ class PPOLoop:
         actor_infer.to_empty(device=self.device)
         self.tokenizer = instantiate(ppo.actor.tokenizer)
         mc = ppo.actor.model_conf
-        self.engine = InferenceEngine(
+        engine_cls = InferenceEngine
+        if self.engine_kind == "tokainfer":
+            from halite_b200.tokainfer import InferenceEngine as engine_cls
+        self.engine = engine_cls(
             actor_infer, self.tokenizer,
             ModelConfig(n_heads=_get(mc, "n_heads"), n_key_value_heads=_get(mc, "n_key_value_heads") or _get(mc, "n_heads"),
                         head_dim=_get(mc, "head_dim"), n_layers=_get(mc, "n_layers"), context_len=_get(mc, "context_len"),

@@ -1,0 +1,136 @@
+"""Model worker of engine B (reference: tokainfer/basic_worker.py:36-259, utils.py ModelRunner):
+executes `ModelInput`s — mixed prefill chunks and decode tokens in one flat forward — on the
+paged kernels and returns the sampled tokens. It owns the KV pages and the page table; the
+manager only ever names page ids and table rows. Decode entries whose token the manager has not
+seen yet (scheduling ahead) take their input from the worker's device-side last-token buffer, so
+no host round trip sits between consecutive decode steps.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from halite_b200.infer.batch import BatchSamplingParams, ForwardBatch, ForwardMode
+from halite_b200.infer.model_runner import ModelRunner
+from halite_b200.infer.types import ServerConfig as RunnerConfig
+from halite_b200.tokainfer.types import Command, ModelInput, ModelOutput
+
+
+class ModelWorker:
+    def __init__(self, model, model_config, server_config):
+        self.server_config = server_config
+        runner_conf = RunnerConfig(page_size=server_config.page_size, max_total_tokens=server_config.kv_cache_num_tokens,
+                                   max_running_requests=server_config.max_seqs_per_forward, seed=server_config.seed)
+        if server_config.kv_cache_num_tokens is None:
+            model_config.memory_fraction_static = server_config.memory_fraction
+        self.runner = ModelRunner(model, model_config, runner_conf)
+        self.device = self.runner.device
+        self._post_init()
+
+    def _post_init(self):
+        r = self.runner
+        self.page_size = r.page_size
+        self.num_blocks = r.kv_pool.num_pages
+        self.max_seqs = r.req_pool.size - 1
+        self.last_tokens = torch.zeros(r.req_pool.size, dtype=torch.int64, device=self.device)
+
+    # ------------------------------------------------------------------ lifecycle
+    def initialize(self):
+        if self.runner.kv_pool is None:
+            self.runner.initialize()
+            self._post_init()
+
+    def cleanup(self):
+        self.runner.cleanup()
+
+    def load_state_dict(self, state_dict, assign=True):
+        self.runner.load_state_dict(state_dict, assign=assign)
+
+    def handle(self, command: Command):
+        if command.kind == "cleanup":
+            self.cleanup()
+        elif command.kind == "initialize":
+            self.initialize()
+        elif command.kind == "load_state_dict":
+            self.load_state_dict(command.payload)
+        else:
+            raise ValueError(f"unknown command {command.kind}")
+
+    # ------------------------------------------------------------------ forward
+    @torch.no_grad()
+    def run(self, inp: ModelInput) -> ModelOutput:
+        r, ps, dev = self.runner, self.page_size, self.device
+        table = r.req_pool.req_to_pages
+        for row, start, pages in inp.page_updates:
+            # blocks are numbered from 0 by the manager; page 0 of the pool is the scratch page
+            table[row, start:start + len(pages)] = torch.tensor([p + 1 for p in pages], dtype=torch.int32).to(dev)
+        n_entries = len(inp.batch_indices)
+        if n_entries == 0:
+            return ModelOutput(inp.step_id, [], [], [])
+        lens = [1 if t is None else len(t) for t in inp.tokens]
+        indptr = [0]
+        for n in lens:
+            indptr.append(indptr[-1] + n)
+        total = indptr[-1]
+        ids = torch.zeros(total, dtype=torch.int64)
+        positions = torch.zeros(total, dtype=torch.int64)
+        from_device_rows, from_device_pos = [], []
+        for i, (toks, prefix, n) in enumerate(zip(inp.tokens, inp.prefix_lens, lens)):
+            s = indptr[i]
+            if toks is None:
+                from_device_rows.append(inp.batch_indices[i])
+                from_device_pos.append(s)
+            else:
+                ids[s:s + n] = torch.tensor(toks, dtype=torch.int64)
+            positions[s:s + n] = torch.arange(prefix, prefix + n)
+        ids, positions = ids.to(dev), positions.to(dev)
+        if from_device_rows:
+            ids[torch.tensor(from_device_pos, device=dev)] = self.last_tokens[torch.tensor(from_device_rows, device=dev)]
+        rows = torch.tensor(inp.batch_indices, dtype=torch.int64, device=dev)
+        entry_of_token = torch.repeat_interleave(torch.arange(n_entries, device=dev),
+                                                 torch.tensor(lens, device=dev))
+        page_of = table[rows[entry_of_token], (positions // ps)].to(torch.int64)
+        out_loc = page_of * ps + positions % ps
+        seq_lens = [p + n for p, n in zip(inp.prefix_lens, lens)]
+        i32 = lambda xs: torch.tensor(xs, dtype=torch.int32, device=dev)
+        fb = ForwardBatch(
+            mode=ForwardMode.EXTEND, input_ids=ids, positions=positions, out_cache_loc=out_loc,
+            req_slots=i32(inp.batch_indices), seq_lens=i32(seq_lens), extend_lens=i32(lens),
+            prefix_lens=i32(inp.prefix_lens), qo_indptr=i32(indptr), page_table=table, max_seq_len=max(seq_lens),
+            max_extend_len=max(lens), page_size=ps,
+            sample_indices=torch.tensor([x - 1 for x in indptr[1:]], dtype=torch.int64, device=dev),
+            seq_lens_cpu=seq_lens, extend_lens_cpu=lens)
+        logits = r.forward(fb)                                    # [entries, vocab]
+        f32 = lambda xs: torch.tensor(xs, dtype=torch.float32, device=dev)
+        sampling = BatchSamplingParams(
+            temperatures=f32(inp.temperatures).view(-1, 1), top_ps=f32(inp.top_ps),
+            top_ks=torch.tensor([min(k if k > 0 else 1 << 30, 1 << 30) for k in inp.top_ks], dtype=torch.int32, device=dev),
+            min_ps=f32(inp.min_ps), is_all_greedy=all(0 < k <= 1 for k in inp.top_ks),
+            need_min_p_sampling=any(p > 0 for p in inp.min_ps),
+            need_top_k_top_p=any(p < 1.0 for p in inp.top_ps) or any(1 < k < (1 << 29) for k in inp.top_ks))
+        tokens, logprobs = r.sampler(logits, sampling)
+        keep = [i for i, s in enumerate(inp.sample) if s]
+        if keep:
+            k = torch.tensor(keep, device=dev)
+            self.last_tokens[rows[k]] = tokens[k]
+        toks_cpu, lps_cpu = tokens.tolist(), logprobs.tolist()
+        return ModelOutput(inp.step_id, [inp.batch_indices[i] for i in keep], [toks_cpu[i] for i in keep],
+                           [lps_cpu[i] for i in keep])
+
+
+def worker_main(build_model, model_config, server_config, in_q, out_q):
+    """Entry point of the worker process: build the model, then serve inputs until shutdown."""
+    model = build_model()
+    worker = ModelWorker(model, model_config, server_config)
+    out_q.put(("ready", worker.num_blocks, worker.max_seqs))
+    while True:
+        msg = in_q.get()
+        if isinstance(msg, Command):
+            if msg.kind == "shutdown":
+                break
+            worker.handle(msg)
+            out_q.put(("done", msg.kind))
+            if msg.kind == "initialize":
+                out_q.put(("ready", worker.num_blocks, worker.max_seqs))
+            continue
+        out_q.put(worker.run(msg))

@@ -119,3 +119,17 @@ def test_dit_script_trains_samples_and_saves_ema(tmp_path):
 
     ema = torch.load(os.path.join(out, "tiny", "ema-0000010.pt"))
     assert "blocks.0.modulator.linear.weight" in ema and ema["head.linear.weight"].shape == (48, 32)
+
+
+def test_ppo_tokainfer_script_runs(tmp_path):
+    data, out = str(tmp_path / "data"), str(tmp_path / "out")
+    os.makedirs(os.path.join(data, "a"))
+    with RecordFileWriter(os.path.join(data, "a", "s0.hbrec")) as w:
+        for i in range(64):
+            w.write(json.dumps({"text": f"say a lot of a: {i % 7}"}))
+    logs = " ".join(run_ranks(os.path.join(ROOT, "scripts/ppo_tokainfer.py"), 1,
+                              args=["--conf", os.path.join(ROOT, "tests/configs/tiny_grpo.py"), "training.max_iter=2"],
+                              timeout=900, env_extra={"HB_TEST_DATA": data, "HB_TEST_OUT": out})[0].split())
+    steps = [int(x) for x in re.findall(r"global (\d+); actor/", logs)]
+    assert steps == [0, 1], logs[-3000:]
+    assert "critic/rewards_mean" in logs
