@@ -189,3 +189,46 @@ def test_engine_gpu_matches_dense(zoo, cudagraph):
     sch = eng.scheduler
     assert sch.kv_pool.available_pages() + sch.tree_cache.evictable_pages == sch.kv_pool.num_pages
     assert sch.stats["cached_tokens"] > 0
+
+
+def test_tokainfer_engine_gpu_matches_dense(zoo):
+    """Engine B on the device: mixed prefill + decode forwards scheduled ahead; generated tokens'
+    log-probs must agree with a dense bf16 evaluation of the same sequences."""
+    from halite_b200.conf import instantiate
+    from halite_b200.infer import InferenceRequest, ModelConfig
+    from halite_b200.tokainfer import InferenceEngine, ServerConfig
+
+    kw = dict(vocab_size=2048, dim=512, n_heads=8, head_dim=64, n_layers=3, intermediate_size=1024,
+              context_len=512, n_key_value_heads=2, rms_norm_epsilon=1e-5, qkv_split=True,
+              gated_ff_split=True, init=partial(torch.nn.init.normal_, std=0.05))
+    cfg = zoo.transformer(**kw)
+    torch.manual_seed(0)
+    model = instantiate(cfg)
+    model.init_weights()
+    model = model.cuda().bfloat16().eval()
+    with torch.device("meta"):
+        imodel = instantiate(instantiate(zoo.transformer_infer(**kw, infer="paged"))(cfg))
+    mc = ModelConfig(n_heads=8, n_key_value_heads=2, head_dim=64, n_layers=3, context_len=512, device="cuda")
+    eng = InferenceEngine(imodel, None, mc, ServerConfig(kv_cache_num_tokens=16384, scheduling_steps_ahead=4,
+                                                         max_tokens_per_forward=256))
+    eng.load_state_dict(model.state_dict())
+    g = torch.Generator().manual_seed(3)
+    shared = torch.randint(0, 2048, (48,), generator=g).tolist()
+    reqs = [InferenceRequest(i, (shared if i % 2 else []) + torch.randint(0, 2048, (5 + 9 * i,), generator=g).tolist(),
+                             {"max_new_tokens": 24, "top_k": 1}) for i in range(12)]
+    res = eng.infer_batch(reqs)
+    from halite_b200 import ops
+
+    ops.check_status()
+    worst = 0.0
+    for r in res:
+        n_in = len(r.input_ids)
+        seq = torch.tensor([r.input_ids + r.output_ids[0]], device="cuda")
+        with torch.no_grad():
+            lp = torch.log_softmax(model(seq).logits[0].float(), -1)[n_in - 1:-1]
+        out = torch.tensor(r.output_ids[0], device="cuda")
+        got = torch.tensor(r.output_logprobs[0], device="cuda")
+        worst = max(worst, (lp.gather(-1, out[:, None]).squeeze(-1) - got).abs().max().item())
+        assert len(r.output_ids[0]) == 24
+    assert worst < 0.15, worst
+    eng.manager.allocator.sanity_checks(set())
