@@ -11,6 +11,7 @@ reduces).
 from __future__ import annotations
 
 import pickle
+import threading
 import time
 from collections import deque
 from datetime import timedelta
@@ -35,6 +36,7 @@ class StatelessProcessGroup:
         self._bcast_recv = [0] * world_size
         self._barriers = 0
         self._entries: deque = deque()
+        self._lock = threading.Lock()      # several threads may send (each to its own peer)
 
     @classmethod
     def create(cls, host: str, port: int, rank: int, world_size: int, data_expiration_seconds: int = 3600,
@@ -45,9 +47,11 @@ class StatelessProcessGroup:
 
     # ------------------------------------------------------------------ bookkeeping
     def _put(self, key, obj):
-        self.expire_data()
-        self.store.set(key, pickle.dumps(obj))
-        self._entries.append((key, time.time()))
+        data = pickle.dumps(obj)
+        with self._lock:
+            self.expire_data()
+            self.store.set(key, data)
+            self._entries.append((key, time.time()))
 
     def expire_data(self):
         now = time.time()

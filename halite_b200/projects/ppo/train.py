@@ -110,6 +110,13 @@ class PPOLoop:
         return model
 
     def build(self):
+        self.build_training()
+        self.build_generation()
+        self.build_data()
+        self.build_optimizer()
+        return self
+
+    def build_training(self):
         conf, ppo = self.conf, self.conf.ppo
         self.actor = self.build_model(ppo.actor, "actor")
         self.ref = self.build_model(ppo.ref, "reference policy") if ppo.ref is not None else None
@@ -119,6 +126,8 @@ class PPOLoop:
         actor_train = instantiate(ppo.actor_wrapper)(self.actor) if ppo.actor_wrapper is not None else self.actor
         self.trainer = instantiate(ppo.trainer)(actor=actor_train, ref=self.ref, critic=self.critic, device=self.device)
 
+    def build_generation(self):
+        conf, ppo = self.conf, self.conf.ppo
         # generation side: the same architecture rewritten for the paged engine
         with torch.device("meta"):
             infer_conf = instantiate(ppo.actor.model_infer)
@@ -147,6 +156,8 @@ class PPOLoop:
         self.request_builder = instantiate(ppo.request_builder)
         self.rollout_generator = instantiate(ppo.rollout_generator)(self.engine)
 
+    def build_data(self):
+        conf = self.conf
         ops = [instantiate(op) for op in (conf.data.preprocess or [])]
         collate = instantiate(conf.data.collate_fn) if conf.data.collate_fn is not None else None
         dp, rank = self.pdims.dp, self.pdims.dp_rank
@@ -160,6 +171,9 @@ class PPOLoop:
             train = instantiate(spec)
         self.train_loader = DataLoader(train, batch_size=conf.training.train_batch_size // dp, collate_fn=collate,
                                        num_workers=self.num_workers, rank=rank, drop_last=True)
+
+    def build_optimizer(self):
+        conf, ppo = self.conf, self.conf.ppo
         t = conf.training
         self.optimizer = build_optimizer(instantiate(t.optimizer), self.actor, t.weight_decay)
         self.scheduler = instantiate(t.scheduler)(optimizer=self.optimizer)

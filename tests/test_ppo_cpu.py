@@ -193,3 +193,25 @@ def test_real_actor_wrapper_and_critic(zoo):
     loss.backward()
     assert head.linear.weight.grad is not None and torch.isfinite(loss)
     assert critic.score(batch).shape == (3,)
+
+
+def test_async_rollout_primitives():
+    import threading
+
+    from halite_b200.projects.common.rollout_async import ReplayBuffer, TensorSpec, chunk_list, get_peer_ranks
+
+    assert chunk_list(list(range(7)), 3) == [[0, 1, 2], [3, 4], [5, 6]]
+    assert get_peer_ranks(1, 2, 4) == [2, 3] and get_peer_ranks(3, 4, 2) == [] and get_peer_ranks(1, 4, 4) == [1]
+    assert get_peer_ranks(3, 4, 2, overlap_targets=True) == [1]
+    spec = TensorSpec.from_tensor("w", torch.zeros(2, 3, dtype=torch.bfloat16))
+    assert spec.empty("cpu").shape == (2, 3) and spec.dtype == torch.bfloat16
+    buf = ReplayBuffer(capacity=3, max_staleness=1)
+    for v in range(5):
+        buf.put(v, [f"r{v}"])
+    assert len(buf) == 3 and buf.dropped == 2                       # capacity
+    assert buf.get(current_version=4)[0] == 3 and buf.dropped == 3  # version 2 was too stale
+    assert buf.get(current_version=4)[0] == 4
+    with pytest.raises(TimeoutError):
+        buf.get(4, timeout=0.05)
+    threading.Timer(0.05, lambda: buf.put(9, ["late"])).start()
+    assert buf.get(9, timeout=5) == (9, ["late"])

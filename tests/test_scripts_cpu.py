@@ -133,3 +133,22 @@ def test_ppo_tokainfer_script_runs(tmp_path):
     steps = [int(x) for x in re.findall(r"global (\d+); actor/", logs)]
     assert steps == [0, 1], logs[-3000:]
     assert "critic/rewards_mean" in logs
+
+
+def test_ppo_async_script_two_trainers_one_generator(tmp_path):
+    data = str(tmp_path / "data")
+    os.makedirs(os.path.join(data, "a"))
+    with RecordFileWriter(os.path.join(data, "a", "s0.hbrec")) as w:
+        for i in range(64):
+            w.write(json.dumps({"text": f"say a lot of a: {i % 7}"}))
+    outs = run_ranks(os.path.join(ROOT, "scripts/ppo_async.py"), 3,
+                     args=["--conf", os.path.join(ROOT, "tests/configs/tiny_grpo.py"), "training.max_iter=3",
+                           "monarch.trainer_mesh_size=2", "monarch.generator_mesh_size=1", "output.save_step=100"],
+                     timeout=900, env_extra={"HB_TEST_DATA": data, "HB_TEST_OUT": str(tmp_path / "out")})
+    logs = " ".join(outs[0].split())
+    steps = [int(x) for x in re.findall(r"global (\d+); policy version of rollouts (-?\d+)", logs)
+             for x in [x[0]]]
+    assert steps == [0, 1, 2], logs[-3000:]
+    versions = [int(v) for _, v in re.findall(r"global (\d+); policy version of rollouts (-?\d+)", logs)]
+    assert versions[0] == 0 and all(0 <= s - v <= 1 for s, v in zip(steps, versions))
+    assert "actor/pg_loss" in logs and "replay buffer dropped" in logs
