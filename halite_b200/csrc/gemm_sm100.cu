@@ -674,9 +674,11 @@ int l2_prefetch_distance() {
 // Scratch for the split-K tail (partials + arrival counters), one fixed-size slot per
 // (device, stream) so GEMMs on different streams never share it. A slot is allocated the first
 // time a stream needs one, outside of stream capture; while a stream is being captured into a
-// CUDA graph and has no slot yet, the GEMM simply runs without the split.
+// CUDA graph it uses a slot set aside for graphs (see below).
 constexpr size_t kSplitWsBytes = size_t(20) << 20;   // >= 148 slices x 128 x 256 fp32
 constexpr int kSplitCounters = 1024;
+// pseudo stream handle that names the per-device slot used by captured graphs
+static const cudaStream_t kGraphSlot = reinterpret_cast<cudaStream_t>(static_cast<uintptr_t>(0x1));
 
 cudaError_t split_workspace(size_t bytes, int n_counters, cudaStream_t stream, float** ws, int** counters) {
   struct Slot {
@@ -699,12 +701,35 @@ cudaError_t split_workspace(size_t bytes, int n_counters, cudaStream_t stream, f
       return cudaSuccess;
     }
   }
+  // A stream that is being captured cannot allocate. It uses the device's graph slot, which is
+  // created together with the first ordinary slot (so: run one GEMM eagerly before capturing).
+  // All captured graphs of a device share that slot: replay them on one stream at a time.
   cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
   if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
     (void)cudaGetLastError();
+    for (const Slot& s : slots) {
+      if (s.dev == dev && s.stream == kGraphSlot) {
+        *ws = s.ws;
+        *counters = s.counters;
+        return cudaSuccess;
+      }
+    }
     return cudaErrorStreamCaptureUnsupported;
   }
   if (slots.size() >= 32) return cudaErrorMemoryAllocation;   // bounded: 32 x 20 MB
+  bool have_graph_slot = false;
+  for (const Slot& s : slots) have_graph_slot |= (s.dev == dev && s.stream == kGraphSlot);
+  if (!have_graph_slot) {
+    Slot gs{dev, kGraphSlot, nullptr, nullptr};
+    if (cudaMalloc(&gs.ws, kSplitWsBytes) == cudaSuccess) {
+      if (cudaMalloc(&gs.counters, sizeof(int) * kSplitCounters) == cudaSuccess) {
+        slots.push_back(gs);
+      } else {
+        cudaFree(gs.ws);
+      }
+    }
+    (void)cudaGetLastError();
+  }
   Slot s{dev, stream, nullptr, nullptr};
   e = cudaMalloc(&s.ws, kSplitWsBytes);
   if (e != cudaSuccess) return e;
@@ -820,7 +845,9 @@ cudaError_t launch(const GemmArgs& g) {
     const int base = (g.max_ctas > 0 && g.max_ctas < sm_count()) ? g.max_ctas : sm_count();
     const int num_kb = (g.K + kBK - 1) / kBK;
     const int rem = tiles % base;
-    if (rem > 0 && rem * 2 <= base && num_kb >= 16) {
+    // only for the tail of a multi-wave launch: slicing a launch that does not even fill the
+    // GPU once costs more (fixed per-CTA set-up, partials through memory) than it recovers
+    if (tiles > base && rem > 0 && rem * 2 <= base && num_kb >= 16) {
       int parts = base / rem;
       if (parts > 8) parts = 8;
       while (parts > 1 && ((num_kb + parts - 1) / parts < 8 ||

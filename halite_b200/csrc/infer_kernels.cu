@@ -95,19 +95,55 @@ __global__ void rope_append_kernel(__nv_bfloat16* __restrict__ q, const __nv_bfl
 // ------------------------------------------------------------------ decode attention
 // grid (batch, kv_heads, splits), 128 threads. A CTA covers tokens [split * chunk, ...) of one
 // request for one KV head and all G = hq / hk query heads of its group, in tiles of 64 tokens.
+// K and V tiles stream through a three-stage shared-memory ring filled by cp.async, so the loads
+// of tiles i+1 and i+2 are in flight while tile i is consumed (decode is bandwidth-bound: what matters is
+// bytes in flight, not arithmetic). Rows are padded by 16 bytes so that a warp's 16-byte reads of
+// 32 consecutive rows hit distinct banks.
+__device__ __forceinline__ void cp_async_16_zfill(uint32_t dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;       // src-size 0: the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group_n() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <int D>
+struct DecodeSmem {
+  static constexpr int kTile = 64;
+  static constexpr int kRow = D + 8;                       // padded row, elements
+  static constexpr int kStages = 3;                        // two tiles in flight while one is consumed
+  static constexpr int kStageElems = 2 * kTile * kRow;     // K tile then V tile
+  static constexpr int kBytes = kStages * kStageElems * 2; // bf16
+};
+
+constexpr int kDecodeThreads = 256;
+
 template <int D, int G>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kDecodeThreads)
 paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                     const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ page_table,
                     const int* __restrict__ req_slots, const int* __restrict__ seq_lens,
                     float* __restrict__ ws, __nv_bfloat16* __restrict__ out, int hq, int hk,
                     int max_pages, int splits, long q_stride, float scale_log2, long num_pages) {
-  constexpr int TILE = 64;
+  using S = DecodeSmem<D>;
+  constexpr int TILE = S::kTile;
+  constexpr int ROW = S::kRow;
+  extern __shared__ __align__(16) unsigned char decode_smem_raw[];
+  __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(decode_smem_raw);
+  constexpr int NT = kDecodeThreads;
+  constexpr int NPART = NT / TILE;          // threads per token in the score phase
+  constexpr int NTG = NT / 16;              // token groups in the PV phase
+  constexpr int TPG = TILE / NTG;           // tokens per group
   __shared__ float s_scores[G][TILE];
+  __shared__ float s_part[NPART][G][TILE];
   __shared__ __align__(16) float s_q[G][D];
   __shared__ float s_alpha[G];
-  __shared__ float s_red[8][G][D + 1];
-  __shared__ int s_pages[TILE / kPage];
+  __shared__ float s_m[G], s_l[G];       // running max / sum when there are more heads than warps
+  // the cross-thread reduction at the end reuses the ring (no tile is live by then)
+  float (*s_red)[G][D + 1] = reinterpret_cast<float (*)[G][D + 1]>(decode_smem_raw);
+  static_assert(sizeof(float) * NTG * G * (D + 1) <= S::kBytes, "reduction scratch must fit in the ring");
 
   const int b = blockIdx.x, kh = blockIdx.y, sp = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -117,13 +153,38 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const int end = min(seq, start + chunk);
   const int* pt = page_table + static_cast<long>(req_slots[b]) * max_pages;
 
-  // QK mapping: thread -> (token = tid / 2, half of the head dim)
-  const int tok = tid >> 1, part = tid & 1;
-  constexpr int HD = D / 2;
   // queries of the group, pre-scaled, in shared memory (read as broadcasts in the dot loop)
-  for (int i = tid; i < G * D; i += 128)
+  for (int i = tid; i < G * D; i += NT)
     s_q[i / D][i % D] = __bfloat162float(q[b * q_stride + (kh * G + i / D) * D + i % D]) * scale_log2;
-  // PV mapping: thread -> (token group = tid / 16 (8 tokens), dim group = tid % 16 (D/16 dims))
+
+  // fill one stage: 64 rows x D elements of K and of V, 16 bytes per copy
+  auto load_tile = [&](int stage, int t0) {
+    __nv_bfloat16* sk = ring + stage * S::kStageElems;
+    __nv_bfloat16* sv = sk + TILE * ROW;
+    constexpr int CH = D / 8;                               // 16-byte chunks per row
+    for (int i = tid; i < TILE * CH; i += NT) {
+      const int row = i / CH, ch = i - row * CH;
+      const int t = t0 + row;
+      const bool valid = t < end;
+      long slot = 0;
+      if (valid) {
+        const int pi = t >> 4;
+        int pg = pi < max_pages ? pt[pi] : 0;
+        if (pg < 0 || pg >= num_pages) pg = 0;
+        slot = static_cast<long>(pg) * kPage + (t & 15);
+      }
+      const long off = (slot * hk + kh) * D + ch * 8;
+      cp_async_16_zfill(static_cast<uint32_t>(__cvta_generic_to_shared(sk + row * ROW + ch * 8)), k_cache + off, valid);
+      cp_async_16_zfill(static_cast<uint32_t>(__cvta_generic_to_shared(sv + row * ROW + ch * 8)), v_cache + off, valid);
+    }
+    cp_async_commit_group();
+  };
+
+  // QK mapping: thread -> (token = tid % 64, slice of the head dim = tid / 64): a warp reads 32
+  // consecutive padded rows at the same offset
+  const int tok = tid & 63, part = tid >> 6;
+  constexpr int HD = D / NPART;
+  // PV mapping: thread -> (token group = tid / 16 (TPG tokens), dim group = tid % 16 (D/16 dims))
   constexpr int DG = D / 16;
   const int tg = tid >> 4, dg = tid & 15;
   float acc[G][DG];
@@ -132,63 +193,74 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 #pragma unroll
     for (int i = 0; i < DG; ++i) acc[g][i] = 0.f;
   float m_run = -INFINITY, l_run = 0.f;  // maintained by warp g (lane-uniform) for head g
-  if (G > 4 && tid < G) {
-    // with more heads than warps the running statistics live in the spare column of s_red
-    s_red[0][tid][D] = -INFINITY;
-    s_red[1][tid][D] = 0.f;
+  if (G > NT / 32 && tid < G) {
+    s_m[tid] = -INFINITY;
+    s_l[tid] = 0.f;
   }
 
-  for (int t0 = start; t0 < end; t0 += TILE) {
-    if (tid < TILE / kPage) {
-      const int pi = (t0 >> 4) + tid;
-      int pg = (t0 + tid * kPage < end && pi < max_pages) ? pt[pi] : 0;
-      if (pg < 0 || pg >= num_pages) pg = 0;
-      s_pages[tid] = pg;
+  // prologue: two tiles in flight. Every iteration commits exactly one group (possibly empty),
+  // so "all but the two newest groups are complete" always means "this iteration's tile landed".
+  if (start < end) load_tile(0, start); else cp_async_commit_group();
+  if (start + TILE < end) load_tile(1, start + TILE); else cp_async_commit_group();
+  int stage = 0;
+  for (int t0 = start; t0 < end; t0 += TILE, stage = (stage + 1 == S::kStages) ? 0 : stage + 1) {
+    if (t0 + 2 * TILE < end) {
+      load_tile((stage + 2) % S::kStages, t0 + 2 * TILE);
+    } else {
+      cp_async_commit_group();
     }
+    cp_async_wait_group_n<2>();
     __syncthreads();
-    // ---- scores
+    const __nv_bfloat16* sk = ring + stage * S::kStageElems;
+    const __nv_bfloat16* sv = sk + TILE * ROW;
+    // ---- scores: NPART threads per token, each over a slice of the head dim
     {
       const int t = t0 + tok;
       float dot[G];
 #pragma unroll
       for (int g = 0; g < G; ++g) dot[g] = 0.f;
-      if (t < end) {
-        const long slot = static_cast<long>(s_pages[tok >> 4]) * kPage + (t & 15);
-        const uint4* kp = reinterpret_cast<const uint4*>(k_cache + (slot * hk + kh) * D + part * HD);
+      const uint4* kp = reinterpret_cast<const uint4*>(sk + tok * ROW + part * HD);
 #pragma unroll
-        for (int c = 0; c < HD / 8; ++c) {
-          const uint4 raw = kp[c];
-          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-          float kf[8];
+      for (int c = 0; c < HD / 8; ++c) {
+        const uint4 raw = kp[c];
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        float kf[8];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 kv = __bfloat1622float2(h2[j]);
-            kf[2 * j] = kv.x;
-            kf[2 * j + 1] = kv.y;
-          }
+        for (int j = 0; j < 4; ++j) {
+          const float2 kv = __bfloat1622float2(h2[j]);
+          kf[2 * j] = kv.x;
+          kf[2 * j + 1] = kv.y;
+        }
 #pragma unroll
-          for (int g = 0; g < G; ++g) {
-            const float4 qa = *reinterpret_cast<const float4*>(&s_q[g][part * HD + c * 8]);
-            const float4 qb = *reinterpret_cast<const float4*>(&s_q[g][part * HD + c * 8 + 4]);
-            dot[g] += qa.x * kf[0] + qa.y * kf[1] + qa.z * kf[2] + qa.w * kf[3] + qb.x * kf[4] +
-                      qb.y * kf[5] + qb.z * kf[6] + qb.w * kf[7];
-          }
+        for (int g = 0; g < G; ++g) {
+          const float4 qa = *reinterpret_cast<const float4*>(&s_q[g][part * HD + c * 8]);
+          const float4 qb = *reinterpret_cast<const float4*>(&s_q[g][part * HD + c * 8 + 4]);
+          dot[g] += qa.x * kf[0] + qa.y * kf[1] + qa.z * kf[2] + qa.w * kf[3] + qb.x * kf[4] +
+                    qb.y * kf[5] + qb.z * kf[6] + qb.w * kf[7];
         }
       }
+      // the slices of a token sit 64 threads apart: combine through shared memory
 #pragma unroll
-      for (int g = 0; g < G; ++g) {
-        dot[g] += __shfl_xor_sync(0xffffffffu, dot[g], 1);
-        if (part == 0) s_scores[g][tok] = (t < end) ? dot[g] : -INFINITY;
+      for (int g = 0; g < G; ++g) s_part[part][g][tok] = dot[g];
+      __syncthreads();
+      if (part == 0) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          float sum = 0.f;
+#pragma unroll
+          for (int pp = 0; pp < NPART; ++pp) sum += s_part[pp][g][tok];
+          s_scores[g][tok] = (t < end) ? sum : -INFINITY;
+        }
       }
     }
     __syncthreads();
     // ---- online softmax statistics: warp g owns head g (G <= 4 warps; loop otherwise)
-    for (int g = warp; g < G; g += 4) {
+    for (int g = warp; g < G; g += NT / 32) {
       const float a0 = s_scores[g][lane], a1 = s_scores[g][lane + 32];
       const float tmax = warp_max_f(fmaxf(a0, a1));
       // m_run / l_run live in registers of warp (g % 4); with G > 4 they are kept in smem below
-      float m_old = (G <= 4) ? m_run : s_red[0][g][D];
-      float l_old = (G <= 4) ? l_run : s_red[1][g][D];
+      float m_old = (G <= NT / 32) ? m_run : s_m[g];
+      float l_old = (G <= NT / 32) ? l_run : s_l[g];
       const float m_new = fmaxf(m_old, tmax);
       const float alpha = (m_old == -INFINITY) ? 0.f : exp2f(m_old - m_new);
       const float p0 = (a0 == -INFINITY) ? 0.f : exp2f(a0 - m_new);
@@ -196,7 +268,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       s_scores[g][lane] = p0;
       s_scores[g][lane + 32] = p1;
       const float l_new = l_old * alpha + warp_sum_f(p0 + p1);
-      if (G <= 4) { m_run = m_new; l_run = l_new; } else if (lane == 0) { s_red[0][g][D] = m_new; s_red[1][g][D] = l_new; }
+      if (G <= NT / 32) { m_run = m_new; l_run = l_new; } else if (lane == 0) { s_m[g] = m_new; s_l[g] = l_new; }
       if (lane == 0) s_alpha[g] = alpha;
     }
     __syncthreads();
@@ -208,12 +280,10 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       for (int i = 0; i < DG; ++i) acc[g][i] *= al;
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int tl = tg * 8 + j;
-      const int t = t0 + tl;
-      if (t < end) {
-        const long slot = static_cast<long>(s_pages[tl >> 4]) * kPage + (t & 15);
-        const __nv_bfloat16* vp = v_cache + (slot * hk + kh) * D + dg * DG;
+    for (int j = 0; j < TPG; ++j) {
+      const int tl = tg * TPG + j;
+      if (t0 + tl < end) {
+        const __nv_bfloat16* vp = sv + tl * ROW + dg * DG;
         float vv[DG];
         if (DG == 8) {
           const uint4 raw = *reinterpret_cast<const uint4*>(vp);
@@ -242,26 +312,28 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
         }
       }
     }
-    __syncthreads();
+    __syncthreads();   // everyone is done with this stage before the next iteration refills it
   }
 
   // ---- reduce the 8 token groups, write the split's partial result
+  cp_async_wait_group_n<0>();
+  __syncthreads();
 #pragma unroll
   for (int g = 0; g < G; ++g)
 #pragma unroll
     for (int i = 0; i < DG; ++i) s_red[tg][g][dg * DG + i] = acc[g][i];
-  if (G <= 4 && warp < G && lane == 0) {
+  if (G <= NT / 32 && warp < G && lane == 0) {
     s_scores[warp][0] = m_run;
     s_scores[warp][1] = l_run;
   }
   __syncthreads();
-  for (int idx = tid; idx < G * D; idx += 128) {
+  for (int idx = tid; idx < G * D; idx += NT) {
     const int g = idx / D, d = idx - g * D;
     float o = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) o += s_red[j][g][d];
-    const float m = (G <= 4) ? s_scores[g][0] : s_red[0][g][D];
-    const float l = (G <= 4) ? s_scores[g][1] : s_red[1][g][D];
+    for (int j = 0; j < NTG; ++j) o += s_red[j][g][d];
+    const float m = (G <= NT / 32) ? s_scores[g][0] : s_m[g];
+    const float l = (G <= NT / 32) ? s_scores[g][1] : s_l[g];
     const int h = kh * G + g;
     if (splits == 1) {
       out[(static_cast<long>(b) * hq + h) * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
@@ -618,7 +690,14 @@ int paged_decode_splits(int batch, int hk, int sm_count) {
 template <int D, int G>
 static cudaError_t launch_decode(const PagedDecodeArgs& a, cudaStream_t stream) {
   dim3 grid(a.batch, a.hk, a.splits);
-  paged_decode_kernel<D, G><<<grid, 128, 0, stream>>>(
+  constexpr int smem = DecodeSmem<D>::kBytes;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(paged_decode_kernel<D, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  paged_decode_kernel<D, G><<<grid, kDecodeThreads, smem, stream>>>(
       static_cast<const __nv_bfloat16*>(a.q), static_cast<const __nv_bfloat16*>(a.k_cache),
       static_cast<const __nv_bfloat16*>(a.v_cache), a.page_table, a.req_slots, a.seq_lens, a.workspace,
       static_cast<__nv_bfloat16*>(a.out), a.hq, a.hk, a.max_pages, a.splits, a.q_stride,
