@@ -39,7 +39,7 @@ constexpr int kGroupM = 16;  // raster: kGroupM row-tiles share the same column 
 
 template <int BN>
 struct Cfg {
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128) ? 6 : 8;
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
@@ -936,10 +936,16 @@ cudaError_t wait_flags(const int* flags, int n, int epoch, int* status, cudaStre
 }
 
 int gemm_pick_bn(int M, int N) {
-  if (N <= 128) return 128;
-  const int t256 = ((M + kBM - 1) / kBM) * ((N + 255) / 256);
+  if (N <= 64) return 64;
+  const int tm = (M + kBM - 1) / kBM;
+  const int t256 = tm * ((N + 255) / 256);
   // prefer the wide tile once it still fills the machine
-  return (t256 >= sm_count()) ? 256 : 128;
+  if (t256 >= sm_count()) return 256;
+  // skinny problems (decode: one row of tiles) are bound by how many SMs pull weights at once:
+  // narrower tiles put more CTAs on the job
+  const int t128 = tm * ((N + 127) / 128);
+  if (N > 128 && 2 * t128 > sm_count()) return 128;
+  return 64;
 }
 
 cudaError_t gemm_bf16(const GemmArgs& g) {
@@ -951,6 +957,9 @@ cudaError_t gemm_bf16(const GemmArgs& g) {
   const int bn = g.block_n > 0 ? g.block_n : gemm_pick_bn(g.M, g.N);
   if (bn == 256) {
     return g.out_f32 ? dispatch_layout<256, float>(g) : dispatch_layout<256, __nv_bfloat16>(g);
+  }
+  if (bn == 64) {
+    return g.out_f32 ? dispatch_layout<64, float>(g) : dispatch_layout<64, __nv_bfloat16>(g);
   }
   return g.out_f32 ? dispatch_layout<128, float>(g) : dispatch_layout<128, __nv_bfloat16>(g);
 }
