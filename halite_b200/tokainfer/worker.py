@@ -67,6 +67,8 @@ class ModelWorker:
         n_entries = len(inp.batch_indices)
         if n_entries == 0:
             return ModelOutput(inp.step_id, [], [], [])
+        if all(t is None for t in inp.tokens):
+            return self._run_decode(inp)
         lens = [1 if t is None else len(t) for t in inp.tokens]
         indptr = [0]
         for n in lens:
@@ -101,6 +103,10 @@ class ModelWorker:
             sample_indices=torch.tensor([x - 1 for x in indptr[1:]], dtype=torch.int64, device=dev),
             seq_lens_cpu=seq_lens, extend_lens_cpu=lens)
         logits = r.forward(fb)                                    # [entries, vocab]
+        return self._sample(inp, logits, rows)
+
+    def _sample(self, inp, logits, rows):
+        r, dev = self.runner, self.device
         f32 = lambda xs: torch.tensor(xs, dtype=torch.float32, device=dev)
         sampling = BatchSamplingParams(
             temperatures=f32(inp.temperatures).view(-1, 1), top_ps=f32(inp.top_ps),
@@ -110,12 +116,64 @@ class ModelWorker:
             need_top_k_top_p=any(p < 1.0 for p in inp.top_ps) or any(1 < k < (1 << 29) for k in inp.top_ks))
         tokens, logprobs = r.sampler(logits, sampling)
         keep = [i for i, s in enumerate(inp.sample) if s]
-        if keep:
-            k = torch.tensor(keep, device=dev)
-            self.last_tokens[rows[k]] = tokens[k]
-        toks_cpu, lps_cpu = tokens.tolist(), logprobs.tolist()
-        return ModelOutput(inp.step_id, [inp.batch_indices[i] for i in keep], [toks_cpu[i] for i in keep],
-                           [lps_cpu[i] for i in keep])
+        if not keep:
+            return ModelOutput(inp.step_id, [], [], [])
+        k = torch.tensor(keep, device=dev)
+        kept_tokens, kept_lps = tokens[k], logprobs[k].float()
+        self.last_tokens[rows[k]] = kept_tokens
+        return LazyModelOutput(inp.step_id, [inp.batch_indices[i] for i in keep], kept_tokens, kept_lps)
+
+    @torch.no_grad()
+    def _run_decode(self, inp: ModelInput):
+        """Every entry is one decode token fed from the device-side buffer: the split-KV decode
+        kernel path, no host-built token tensor."""
+        r, ps, dev = self.runner, self.page_size, self.device
+        table = r.req_pool.req_to_pages
+        rows = torch.tensor(inp.batch_indices, dtype=torch.int64, device=dev)
+        positions = torch.tensor(inp.prefix_lens, dtype=torch.int64, device=dev)
+        page_of = table[rows, positions // ps].to(torch.int64)
+        seq_lens = [p + 1 for p in inp.prefix_lens]
+        fb = ForwardBatch(
+            mode=ForwardMode.DECODE, input_ids=self.last_tokens[rows], positions=positions,
+            out_cache_loc=page_of * ps + positions % ps,
+            req_slots=torch.tensor(inp.batch_indices, dtype=torch.int32, device=dev),
+            seq_lens=torch.tensor(seq_lens, dtype=torch.int32, device=dev), page_table=table,
+            max_seq_len=max(seq_lens), max_extend_len=1, page_size=ps, seq_lens_cpu=seq_lens)
+        return self._sample(inp, r.forward(fb), rows)
+
+
+class LazyModelOutput:
+    """Result of a forward whose sampled tokens are still on their way to the host: the copy
+    into pinned memory is enqueued behind the forward and only waited for when the manager reads
+    the tokens, by which time later forwards are already queued on the device."""
+
+    def __init__(self, step_id, batch_indices, tokens_dev, logprobs_dev):
+        self.step_id, self.batch_indices = step_id, batch_indices
+        pin = tokens_dev.is_cuda
+        self._tok = torch.empty(tokens_dev.shape, dtype=tokens_dev.dtype, pin_memory=pin)
+        self._lp = torch.empty(logprobs_dev.shape, dtype=logprobs_dev.dtype, pin_memory=pin)
+        self._tok.copy_(tokens_dev, non_blocking=True)
+        self._lp.copy_(logprobs_dev, non_blocking=True)
+        self._event = None
+        if pin:
+            self._event = torch.cuda.Event()
+            self._event.record()
+        self._done = None
+
+    def materialize(self):
+        if self._done is None:
+            if self._event is not None:
+                self._event.synchronize()
+            self._done = ModelOutput(self.step_id, self.batch_indices, self._tok.tolist(), self._lp.tolist())
+        return self._done
+
+    @property
+    def tokens(self):
+        return self.materialize().tokens
+
+    @property
+    def logprobs(self):
+        return self.materialize().logprobs
 
 
 def worker_main(build_model, model_config, server_config, in_q, out_q):
@@ -133,4 +191,5 @@ def worker_main(build_model, model_config, server_config, in_q, out_q):
             if msg.kind == "initialize":
                 out_q.put(("ready", worker.num_blocks, worker.max_seqs))
             continue
-        out_q.put(worker.run(msg))
+        out = worker.run(msg)
+        out_q.put(out.materialize() if hasattr(out, "materialize") else out)
