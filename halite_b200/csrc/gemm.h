@@ -8,6 +8,7 @@
 namespace hb {
 
 constexpr int kMaxPeers = 8;
+constexpr int kPairBlockN = 512;   // GemmArgs::block_n value that forces the CTA-pair (cta_group::2) kernel
 
 // Side job that a GEMM launch can carry: a few CTAs copy `n_chunks` equal chunks (each from a
 // peer GPU's memory, or from local memory) into one contiguous local destination while the
@@ -67,7 +68,7 @@ struct GemmArgs {
   bool b_mn_major = false;        // false: B is [N, K] row-major; true: B is [K, N] row-major
   bool out_f32 = false;
   bool accumulate = false;  // D += A*B instead of D = A*B
-  int block_n = 0;          // 0 = choose, else 128 or 256
+  int block_n = 0;          // 0 = choose, else 64, 128 or 256 (one CTA per tile) or kPairBlockN
   int max_ctas = 0;         // 0 = one per SM; >0 caps the grid (leaves SMs for a concurrent copy)
   int* status = nullptr;    // device int: set to a WaitCode when a bounded wait gave up
   const GatherParams* gather = nullptr;  // optional fused gather (see above)

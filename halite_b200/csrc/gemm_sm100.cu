@@ -280,6 +280,140 @@ __device__ __forceinline__ WorkItem decode_item(const SplitParams& kp, int w, in
   return it;
 }
 
+// Epilogue of one warp for one accumulator: TMEM lanes [32 q, 32 q + 32) x BN columns, i.e. rows
+// m0 + 32 q .. of the output tile whose first column is n0. `release()` is called (by the whole
+// warp) as soon as the accumulator has been read out of TMEM. `part` >= 0 marks a K-slice of a
+// split tile; `split_slot` then names its workspace / counter slot. `staging` is the CTA's
+// 4 x 4 KB shared-memory staging area.
+template <int BN, typename OutT, typename Release>
+__device__ __forceinline__ void drain_quarter(uint32_t taddr, uint32_t staging, OutT* __restrict__ D, int M,
+                                              int N, int ldd, bool accumulate, bool vec_ok,
+                                              bool staged_epilogue, int m0, int n0, int q, int lane,
+                                              const ScatterParams& sp, const SplitParams& kp, int part,
+                                              int split_slot, Release release) {
+  const int row = m0 + q * 32 + lane;
+  if (part >= 0) {
+    // ---- K-slice of a tail tile: park the fp32 partial, last arriver reduces in slice order
+    constexpr int kQuarterFloats = (BN / 32) * 32 * 32;
+    float* slot0 = kp.workspace +
+                   (static_cast<size_t>(split_slot) * kp.parts * 4 + q) * kQuarterFloats;
+    float* mine = slot0 + static_cast<size_t>(part) * 4 * kQuarterFloats;
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      uint32_t v[32];
+      tmem_ld_32x32(taddr + c * 32, v);
+      tmem_ld_wait();
+      float4* dst = reinterpret_cast<float4*>(mine + (c * 32 + lane) * 32);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        dst[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                             __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+    }
+    tc_fence_before();
+    __threadfence();
+    __syncwarp();
+    release();
+    int prev = 0;
+    if (lane == 0) prev = atomicAdd(kp.counters + split_slot * 4 + q, 1);
+    prev = __shfl_sync(0xffffffffu, prev, 0);
+    if (prev == kp.parts - 1) {
+      __threadfence();
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        float f[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) f[j] = 0.f;
+        for (int pp = 0; pp < kp.parts; ++pp) {
+          const float4* src = reinterpret_cast<const float4*>(
+              slot0 + static_cast<size_t>(pp) * 4 * kQuarterFloats + (c * 32 + lane) * 32);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 x = __ldcg(src + i);
+            f[4 * i] += x.x;
+            f[4 * i + 1] += x.y;
+            f[4 * i + 2] += x.z;
+            f[4 * i + 3] += x.w;
+          }
+        }
+        uint32_t v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(f[j]);
+        const int col = n0 + c * 32;
+        if (row < M && col < N) {
+          OutT* base = D + static_cast<size_t>(row) * ldd;
+          store_chunk<OutT>(base + col, v, min(32, N - col), vec_ok, accumulate);
+        }
+      }
+    }
+    return;
+  }
+  if constexpr (sizeof(OutT) == 2) {
+    if (sp.n_chunks > 0 || (vec_ok && !accumulate && staged_epilogue)) {
+      // The warp's 32 x 64 sub-tile is transposed through shared memory (128B-swizzled,
+      // conflict-free both ways) and written 4 rows x 128 B per instruction: whole lines,
+      // which is what stores that cross NVLink need (reduce-scatter: the rows' owner
+      // receives this partial directly) and what keeps L2 write traffic to full sectors.
+      const uint32_t stage_base = staging + q * (32 * 128);
+#pragma unroll 1
+      for (int c = 0; c < BN / 64; ++c) {
+#pragma unroll
+        for (int hlf = 0; hlf < 2; ++hlf) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + c * 64 + hlf * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t chunk = static_cast<uint32_t>(hlf * 4 + j) ^ (lane & 7);
+            st_shared_v4(stage_base + lane * 128 + chunk * 16,
+                         pack_bf16x2(__uint_as_float(v[8 * j]), __uint_as_float(v[8 * j + 1])),
+                         pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3])),
+                         pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5])),
+                         pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7])));
+          }
+        }
+        __syncwarp();
+        const int col = n0 + c * 64 + (lane & 7) * 8;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int r = i * 4 + (lane >> 3);
+          const int grow = m0 + q * 32 + r;
+          const uint4 val = ld_shared_v4(stage_base + r * 128 + (((lane & 7) ^ (r & 7)) * 16));
+          if (grow < M && col < N) {
+            __nv_bfloat16* dst;
+            if (sp.n_chunks > 0) {
+              const int owner = grow / sp.rows_per_chunk;
+              dst = static_cast<__nv_bfloat16*>(sp.dst[owner]) +
+                    static_cast<size_t>(grow - owner * sp.rows_per_chunk) * ldd + col;
+            } else {
+              dst = reinterpret_cast<__nv_bfloat16*>(D) + static_cast<size_t>(grow) * ldd + col;
+            }
+            *reinterpret_cast<uint4*>(dst) = val;
+          }
+        }
+        __syncwarp();
+      }
+      tc_fence_before();
+      __syncwarp();
+      release();
+      return;
+    }
+  }
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    uint32_t v[32];
+    tmem_ld_32x32(taddr + c * 32, v);
+    tmem_ld_wait();
+    const int col = n0 + c * 32;
+    if (row < M && col < N) {
+      OutT* base = D + static_cast<size_t>(row) * ldd;
+      store_chunk<OutT>(base + col, v, min(32, N - col), vec_ok, accumulate);
+    }
+  }
+  tc_fence_before();
+  __syncwarp();
+  release();
+}
+
 template <int BN, bool A_MN, bool B_MN, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
@@ -456,128 +590,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const int row = m0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
-      if (it.part >= 0) {
-        // ---- K-slice of a tail tile: park the fp32 partial, last arriver reduces in slice order
-        constexpr int kQuarterFloats = (BN / 32) * 32 * 32;
-        float* slot0 = kp.workspace +
-                       (static_cast<size_t>(it.tail_index) * kp.parts * 4 + q) * kQuarterFloats;
-        float* mine = slot0 + static_cast<size_t>(it.part) * 4 * kQuarterFloats;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(taddr + c * 32, v);
-          tmem_ld_wait();
-          float4* dst = reinterpret_cast<float4*>(mine + (c * 32 + lane) * 32);
-#pragma unroll
-          for (int i = 0; i < 8; ++i)
-            dst[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
-                                 __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
-        }
-        tc_fence_before();
-        __threadfence();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[acc]));
-        int prev = 0;
-        if (lane == 0) prev = atomicAdd(kp.counters + it.tail_index * 4 + q, 1);
-        prev = __shfl_sync(0xffffffffu, prev, 0);
-        if (prev == kp.parts - 1) {
-          __threadfence();
-#pragma unroll 1
-          for (int c = 0; c < BN / 32; ++c) {
-            float f[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) f[j] = 0.f;
-            for (int pp = 0; pp < kp.parts; ++pp) {
-              const float4* src = reinterpret_cast<const float4*>(
-                  slot0 + static_cast<size_t>(pp) * 4 * kQuarterFloats + (c * 32 + lane) * 32);
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const float4 x = __ldcg(src + i);
-                f[4 * i] += x.x;
-                f[4 * i + 1] += x.y;
-                f[4 * i + 2] += x.z;
-                f[4 * i + 3] += x.w;
-              }
-            }
-            uint32_t v[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(f[j]);
-            const int col = n0 + c * 32;
-            if (row < M && col < N) {
-              OutT* base = D + static_cast<size_t>(row) * ldd;
-              store_chunk<OutT>(base + col, v, min(32, N - col), vec_ok, accumulate != 0);
-            }
-          }
-        }
-        continue;
-      }
-      if constexpr (sizeof(OutT) == 2) {
-        if (sp.n_chunks > 0 || (vec_ok && !accumulate && staged_epilogue)) {
-          // The warp's 32 x 64 sub-tile is transposed through shared memory (128B-swizzled,
-          // conflict-free both ways) and written 4 rows x 128 B per instruction: whole lines,
-          // which is what stores that cross NVLink need (reduce-scatter: the rows' owner
-          // receives this partial directly) and what keeps L2 write traffic to full sectors.
-          const uint32_t stage_base = smem_base + kStages * C::kStageBytes + q * (32 * 128);
-#pragma unroll 1
-          for (int c = 0; c < BN / 64; ++c) {
-#pragma unroll
-            for (int hlf = 0; hlf < 2; ++hlf) {
-              uint32_t v[32];
-              tmem_ld_32x32(taddr + c * 64 + hlf * 32, v);
-              tmem_ld_wait();
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const uint32_t chunk = static_cast<uint32_t>(hlf * 4 + j) ^ (lane & 7);
-                st_shared_v4(stage_base + lane * 128 + chunk * 16,
-                             pack_bf16x2(__uint_as_float(v[8 * j]), __uint_as_float(v[8 * j + 1])),
-                             pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3])),
-                             pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5])),
-                             pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7])));
-              }
-            }
-            __syncwarp();
-            const int col = n0 + c * 64 + (lane & 7) * 8;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int r = i * 4 + (lane >> 3);
-              const int grow = m0 + q * 32 + r;
-              const uint4 val = ld_shared_v4(stage_base + r * 128 + (((lane & 7) ^ (r & 7)) * 16));
-              if (grow < M && col < N) {
-                __nv_bfloat16* dst;
-                if (sp.n_chunks > 0) {
-                  const int owner = grow / sp.rows_per_chunk;
-                  dst = static_cast<__nv_bfloat16*>(sp.dst[owner]) +
-                        static_cast<size_t>(grow - owner * sp.rows_per_chunk) * ldd + col;
-                } else {
-                  dst = reinterpret_cast<__nv_bfloat16*>(D) + static_cast<size_t>(grow) * ldd + col;
-                }
-                *reinterpret_cast<uint4*>(dst) = val;
-              }
-            }
-            __syncwarp();
-          }
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[acc]));
-          continue;
-        }
-      }
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(taddr + c * 32, v);
-        tmem_ld_wait();
-        const int col = n0 + c * 32;
-        if (row < M && col < N) {
-          OutT* base = D + static_cast<size_t>(row) * ldd;
-          store_chunk<OutT>(base + col, v, min(32, N - col), vec_ok, accumulate != 0);
-        }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[acc]));
+      const uint32_t tempty = smem_u32(&bar_tempty[acc]);
+      drain_quarter<BN, OutT>(taddr, smem_base + kStages * C::kStageBytes, D, M, N, ldd, accumulate != 0, vec_ok,
+                              staged_epilogue, m0, n0, q, lane, sp, kp, it.part, it.tail_index, [&]() {
+                                if (lane == 0) mbar_arrive(tempty);
+                              });
     }
   }
 
@@ -649,6 +667,226 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
   if (warp == 2) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------ CTA-pair kernel
+// Same roles as above, but two CTAs of a cluster (one per SM of a TPC) share each 256 x 256
+// output tile through `tcgen05.mma.cta_group::2`: each CTA loads its own 128 rows of A and its
+// own 128 columns of B (32 KB per k-block instead of 48 KB, which is what the single-CTA kernel
+// is bound by) and owns 128 x 256 of the accumulator in its own TMEM. The even CTA issues the
+// MMAs for both. Barrier traffic between the two:
+//   full[s]    lives in the even CTA; both CTAs' TMA loads count their bytes on it
+//   empty[s]   one in each CTA, released together by a commit addressed to both
+//   tfull[a]   one in each CTA (both epilogues wait locally), same commit form
+//   tempty[a]  lives in the even CTA; the eight epilogue warps of the pair arrive on it
+struct PairCfg {
+  static constexpr int kBN = 256;                       // columns of the pair's tile
+  static constexpr int kHalfN = 128;                    // columns of B held by one CTA
+  static constexpr int kStages = 6;
+  static constexpr int kABytes = kBM * kBK * 2;         // 16 KB
+  static constexpr int kBBytes = kHalfN * kBK * 2;      // 16 KB
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStagingBytes = 4 * 32 * 128;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024;
+  static constexpr int kTmemCols = 2 * kBN;
+  static constexpr int kGroupM = 8;                     // raster group, in 256-row tiles
+};
+
+__device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int per_group = PairCfg::kGroupM * tiles_n;
+  const int g = tile / per_group;
+  const int first_m = g * PairCfg::kGroupM;
+  const int gsz = min(PairCfg::kGroupM, tiles_m - first_m);
+  const int r = tile - g * per_group;
+  tm = first_m + r % gsz;
+  tn = r / gsz;
+}
+
+template <bool A_MN, bool B_MN, typename OutT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
+                      const __grid_constant__ CUtensorMap tma_b, OutT* __restrict__ D, int M, int N,
+                      int K, int ldd, int accumulate, int* __restrict__ status,
+                      const __grid_constant__ SplitParams kp) {
+  using C = PairCfg;
+  constexpr int kStages = C::kStages;
+  constexpr int BN = C::kBN;
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kStages];
+  __shared__ __align__(8) uint64_t bar_empty[kStages];
+  __shared__ __align__(8) uint64_t bar_tfull[2];
+  __shared__ __align__(8) uint64_t bar_tempty[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();   // 0: issues the MMAs, 1: its partner
+  const bool leader = rank == 0;
+
+  const int tiles_m = (M + 2 * kBM - 1) / (2 * kBM);
+  const int tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);    // the even CTA's producer; bytes from both CTAs
+      mbar_init(smem_u32(&bar_empty[s]), 1);   // one commit
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&bar_tfull[s]), 1);   // one commit
+      mbar_init(smem_u32(&bar_tempty[s]), 8);  // four epilogue warps in each CTA
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 2) {
+    tmem_alloc_pair(smem_u32(&tmem_slot), C::kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  // both CTAs' barriers exist before either sends the other a signal
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  const int n_items = kp.parts > 1 ? kp.items : num_tiles;
+  const int first_tile = static_cast<int>(cluster_id_x());
+  const int tile_step = static_cast<int>(num_clusters_x());
+
+  if (warp == 0 && lane == 0) {
+    // ------------------------------------------------------------ producer (one per CTA)
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int w = first_tile; w < n_items && ok; w += tile_step) {
+      const WorkItem it = decode_item(kp, w, num_kb);
+      int tm, tn;
+      pair_tile_coords(it.tile, tiles_m, tiles_n, tm, tn);
+      const int m0 = tm * 2 * kBM + static_cast<int>(rank) * kBM;
+      const int n0 = tn * BN + static_cast<int>(rank) * C::kHalfN;
+      for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
+        ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1, &abort_flag, status, kTimeoutEmpty);
+        if (!ok) break;
+        const uint32_t full_local = smem_u32(&bar_full[stage]);
+        const uint32_t full = mapa_shared(full_local, 0);
+        const uint32_t sa = smem_base + stage * C::kStageBytes;
+        const uint32_t sb = sa + C::kABytes;
+        if (leader) mbar_expect_tx(full_local, 2 * C::kStageBytes);
+        const int k0 = kb * kBK;
+        if (!A_MN) {
+          tma_load_2d_pair(sa, &tma_a, full, k0, m0);
+        } else {
+#pragma unroll
+          for (int c = 0; c < kBM / 64; ++c) tma_load_2d_pair(sa + c * 8192, &tma_a, full, m0 + c * 64, k0);
+        }
+        if (!B_MN) {
+          tma_load_2d_pair(sb, &tma_b, full, k0, n0);
+        } else {
+#pragma unroll
+          for (int c = 0; c < C::kHalfN / 64; ++c)
+            tma_load_2d_pair(sb + c * 8192, &tma_b, full, n0 + c * 64, k0);
+        }
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+    // The stage releases come from the even CTA's commits: wait until every one addressed to
+    // this CTA has landed, so that none arrives after the CTA has left.
+    for (int s = 0; s < kStages && ok; ++s) {
+      ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1, &abort_flag, status, kTimeoutEmpty);
+      if (++stage == kStages) {
+        stage = 0;
+        phase ^= 1;
+      }
+    }
+  } else if (leader && warp == 1 && lane == 0) {
+    // ------------------------------------------------------------ MMA issuer (even CTA only)
+    constexpr uint32_t idesc = make_idesc_bf16(2 * kBM, BN, A_MN, B_MN);
+    int stage = 0;
+    uint32_t phase = 0;
+    int local = 0;
+    bool ok = true;
+    for (int w = first_tile; w < n_items && ok; w += tile_step, ++local) {
+      const WorkItem it = decode_item(kp, w, num_kb);
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      ok = mbar_wait_cluster(smem_u32(&bar_tempty[acc]), acc_phase ^ 1, &abort_flag, status,
+                             kTimeoutTmemEmpty);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t tmem_d = tmem_base + acc * BN;
+      for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
+        ok = mbar_wait_cluster(smem_u32(&bar_full[stage]), phase, &abort_flag, status, kTimeoutFull);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t sa = smem_base + stage * C::kStageBytes;
+        const uint32_t sb = sa + C::kABytes;
+#pragma unroll
+        for (int k = 0; k < kBK / kUK; ++k) {
+          const uint64_t da = A_MN ? make_smem_desc(sa + k * 2048, 8192, 1024)
+                                   : make_smem_desc(sa + k * 32, 0, 1024);
+          const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, 8192, 1024)
+                                   : make_smem_desc(sb + k * 32, 0, 1024);
+          umma_bf16_pair(tmem_d, da, db, idesc, ((kb - it.kb_begin) | k) != 0);
+        }
+        umma_commit_pair(smem_u32(&bar_empty[stage]), 3);  // frees the stage in both CTAs
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (ok) umma_commit_pair(smem_u32(&bar_tfull[acc]), 3);  // both epilogues may read
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------ epilogue (both CTAs)
+    const int q = warp & 3;
+    const bool staged_epilogue = (N % 8 == 0);
+    const bool vec_ok = (ldd % (16 / (int)sizeof(OutT)) == 0) &&
+                        ((reinterpret_cast<uintptr_t>(D) & 15) == 0);
+    const ScatterParams no_scatter;
+    int local = 0;
+    bool ok = true;
+    for (int w = first_tile; w < n_items && ok; w += tile_step, ++local) {
+      const WorkItem it = decode_item(kp, w, num_kb);
+      int tm, tn;
+      pair_tile_coords(it.tile, tiles_m, tiles_n, tm, tn);
+      const int m0 = tm * 2 * kBM + static_cast<int>(rank) * kBM;
+      const int n0 = tn * BN;
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      ok = mbar_wait_cluster(smem_u32(&bar_tfull[acc]), acc_phase, &abort_flag, status, kTimeoutTmemFull);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+      const uint32_t tempty = mapa_shared(smem_u32(&bar_tempty[acc]), 0);
+      drain_quarter<BN, OutT>(taddr, smem_base + kStages * C::kStageBytes, D, M, N, ldd, accumulate != 0, vec_ok,
+                              staged_epilogue, m0, n0, q, lane, no_scatter, kp, it.part,
+                              it.tail_index * 2 + static_cast<int>(rank), [&]() {
+                                if (lane == 0) mbar_arrive_cluster(tempty);
+                              });
+    }
+  }
+
+  if (abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  // neither CTA leaves (or frees tensor memory) while its partner may still signal its
+  // barriers or read its shared memory
+  cluster_sync_all();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, C::kTmemCols);
   }
 }
 
@@ -891,6 +1129,105 @@ cudaError_t dispatch_layout(const GemmArgs& g) {
   return launch<BN, true, false, OutT>(g);
 }
 
+int max_pair_clusters(const void* kern, int smem_bytes) {
+  // how many 2-CTA clusters of this kernel the device can hold at once
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(sm_count(), 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem_bytes;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+    (void)cudaGetLastError();
+    n = sm_count() / 2;
+  }
+  return n < sm_count() / 2 ? n : sm_count() / 2;
+}
+
+template <bool A_MN, bool B_MN, typename OutT>
+cudaError_t launch_pair(const GemmArgs& g) {
+  using C = PairCfg;
+  CUtensorMap ta, tb;
+  bool ok;
+  if (!A_MN) ok = make_tmap_bf16_2d(&ta, g.a, g.M, g.K, g.lda, kBM, kBK);
+  else       ok = make_tmap_bf16_2d(&ta, g.a, g.K, g.M, g.lda, kBK, 64);
+  if (!ok) return cudaErrorInvalidPitchValue;
+  if (!B_MN) ok = make_tmap_bf16_2d(&tb, g.b, g.N, g.K, g.ldb, C::kHalfN, kBK);
+  else       ok = make_tmap_bf16_2d(&tb, g.b, g.K, g.N, g.ldb, kBK, 64);
+  if (!ok) return cudaErrorInvalidPitchValue;
+
+  auto kern = gemm_bf16_pair_kernel<A_MN, B_MN, OutT>;
+  static int clusters_max = 0;
+  if (clusters_max == 0) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (e != cudaSuccess) {
+      fprintf(stderr, "halite_b200: cudaFuncSetAttribute (pair kernel) failed: %s\n", cudaGetErrorString(e));
+      return e;
+    }
+    clusters_max = max_pair_clusters(reinterpret_cast<const void*>(kern), C::kSmemBytes);
+  }
+  (void)cudaGetLastError();
+  const int tiles = ((g.M + 2 * kBM - 1) / (2 * kBM)) * ((g.N + C::kBN - 1) / C::kBN);
+  int clusters = tiles < clusters_max ? tiles : clusters_max;
+  SplitParams kp;
+  {
+    // same tail treatment as the single-CTA kernel, counted in clusters
+    const int base = clusters_max;
+    const int num_kb = (g.K + kBK - 1) / kBK;
+    const int rem = tiles % base;
+    if (tiles > base && rem > 0 && rem * 2 <= base && num_kb >= 16) {
+      int parts = base / rem;
+      if (parts > 8) parts = 8;
+      while (parts > 1 && ((num_kb + parts - 1) / parts < 8 ||
+                           (parts - 1) * ((num_kb + parts - 1) / parts) >= num_kb))
+        --parts;
+      if (parts > 1) {
+        const size_t ws_bytes = static_cast<size_t>(rem) * parts * 2 * kBM * C::kBN * sizeof(float);
+        float* ws = nullptr;
+        int* counters = nullptr;
+        if (split_workspace(ws_bytes, rem * 8, g.stream, &ws, &counters) == cudaSuccess) {
+          kp.full = tiles - rem;
+          kp.parts = parts;
+          kp.kb_per = (num_kb + parts - 1) / parts;
+          kp.items = kp.full + rem * parts;
+          kp.workspace = ws;
+          kp.counters = counters;
+          cudaMemsetAsync(counters, 0, sizeof(int) * rem * 8, g.stream);
+          clusters = kp.items < base ? kp.items : base;
+        }
+      }
+    }
+  }
+  kern<<<2 * clusters, kThreads, C::kSmemBytes, g.stream>>>(ta, tb, static_cast<OutT*>(g.d), g.M, g.N, g.K,
+                                                            g.ldd, g.accumulate ? 1 : 0, g.status, kp);
+  return cudaGetLastError();
+}
+
+template <typename OutT>
+cudaError_t dispatch_pair(const GemmArgs& g) {
+  if (!g.a_mn_major && !g.b_mn_major) return launch_pair<false, false, OutT>(g);
+  if (!g.a_mn_major && g.b_mn_major) return launch_pair<false, true, OutT>(g);
+  if (g.a_mn_major && g.b_mn_major) return launch_pair<true, true, OutT>(g);
+  return launch_pair<true, false, OutT>(g);
+}
+
+// The pair kernel is chosen for plain GEMMs that give every SM pair at least one 256 x 256 tile.
+// HB_GEMM_PAIR=0 turns it off.
+bool pair_kernel_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* env = getenv("HB_GEMM_PAIR");
+    on = (env && env[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
+
 }  // namespace
 
 namespace {
@@ -954,6 +1291,14 @@ cudaError_t gemm_bf16(const GemmArgs& g) {
   if ((reinterpret_cast<uintptr_t>(g.a) & 15) || (reinterpret_cast<uintptr_t>(g.b) & 15) ||
       (g.lda % 8) || (g.ldb % 8))
     return cudaErrorInvalidValue;
+  const bool plain = !g.gather && !g.scatter && g.max_ctas == 0;
+  if (g.block_n == kPairBlockN && !plain) return cudaErrorInvalidValue;
+  bool pair = g.block_n == kPairBlockN;
+  if (g.block_n == 0 && plain && pair_kernel_enabled()) {
+    const long pair_tiles = static_cast<long>((g.M + 255) / 256) * ((g.N + 255) / 256);
+    pair = pair_tiles >= sm_count() / 2;
+  }
+  if (pair) return g.out_f32 ? dispatch_pair<float>(g) : dispatch_pair<__nv_bfloat16>(g);
   const int bn = g.block_n > 0 ? g.block_n : gemm_pick_bn(g.M, g.N);
   if (bn == 256) {
     return g.out_f32 ? dispatch_layout<256, float>(g) : dispatch_layout<256, __nv_bfloat16>(g);

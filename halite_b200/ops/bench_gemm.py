@@ -42,10 +42,13 @@ def main():
     ap.add_argument("--layers", default="", help="comma list of layer names to run (default: all)")
     ap.add_argument("--cases", default="", help="comma list among fwd,dgrad,wgrad_f32 (default: all)")
     ap.add_argument("--no-cublas", action="store_true", help="time only this package's kernel")
+    ap.add_argument("--block-n", type=int, default=0,
+                    help="force a tile: 64 / 128 / 256 (one CTA per tile) or 512 (CTA pair, 256 x 256); 0 = choose")
     args = ap.parse_args()
     dev = "cuda"
     flush = torch.zeros(192 << 20, dtype=torch.uint8, device=dev)       # > 126 MB of L2
     T = args.tokens
+    bn = args.block_n
     layers = [("qkv", args.dim, args.qkv), ("attn_out", args.dim, args.dim), ("up_gate", args.dim, 2 * args.ff),
               ("down", args.ff, args.dim)]
     if args.vocab:
@@ -63,9 +66,9 @@ def main():
         dw = torch.empty(n, k, device=dev, dtype=torch.float32)
         dwb = torch.empty(n, k, device=dev, dtype=torch.bfloat16)
         cases = {
-            "fwd": (lambda: gemm(x, w, out=y), lambda: torch.matmul(x, w.t(), out=y)),
-            "dgrad": (lambda: gemm(dy, w, out=dx, b_mn=True), lambda: torch.matmul(dy, w, out=dx)),
-            "wgrad_f32": (lambda: gemm(dy, x, out=dw, a_mn=True, b_mn=True),
+            "fwd": (lambda: gemm(x, w, out=y, block_n=bn), lambda: torch.matmul(x, w.t(), out=y)),
+            "dgrad": (lambda: gemm(dy, w, out=dx, b_mn=True, block_n=bn), lambda: torch.matmul(dy, w, out=dx)),
+            "wgrad_f32": (lambda: gemm(dy, x, out=dw, a_mn=True, b_mn=True, block_n=bn),
                           lambda: torch.matmul(dy.t(), x, out=dwb)),
         }
         flops = 2.0 * T * k * n
@@ -75,7 +78,7 @@ def main():
             t_ours = _time(ours, args.iters, flush)
             t_lib = float("nan") if args.no_cublas else _time(lib, args.iters, flush)
             print(json.dumps({"layer": name, "case": case, "M_N_K": [T, n, k] if case == "fwd" else None,
-                              "ours_ms": round(t_ours, 4), "cublas_ms": round(t_lib, 4),
+                              "block_n": bn, "ours_ms": round(t_ours, 4), "cublas_ms": round(t_lib, 4),
                               "ours_tflops": round(flops / t_ours / 1e9, 1),
                               "cublas_tflops": round(flops / t_lib / 1e9, 1),
                               "ratio": round(t_lib / t_ours, 3)}), flush=True)

@@ -142,3 +142,32 @@ class ValueModel(ModelWrapper):
         v = self._values(batch)
         last = batch.attention_mask.shape[1] - 1 - torch.flip(batch.attention_mask, [1]).argmax(1)
         return v.gather(1, last.unsqueeze(1)).squeeze(1)
+
+
+class RewardModelScorer:
+    """Reward handler backed by a `ValueModel`: called with the `input_ids` and `output_ids`
+    columns of a list of rollouts, returns token rewards [n, longest response] that are zero
+    except for the model's scalar score at each response's last token."""
+
+    def __init__(self, reward_model: ValueModel, batch_size: int = 16, device=None):
+        self.reward_model = reward_model
+        self.batch_size = batch_size
+        self.device = device
+
+    @torch.no_grad()
+    def __call__(self, input_ids, output_ids):
+        from halite_b200.projects.common.rollout import Rollout
+        from halite_b200.projects.ppo.trainer import build_batch_from_rollouts
+
+        n = len(input_ids)
+        longest = max(len(o) for o in output_ids)
+        rewards = torch.zeros(n, longest, dtype=torch.float32)
+        for lo in range(0, n, self.batch_size):
+            hi = min(n, lo + self.batch_size)
+            rows = [Rollout(id=str(i), input_ids=input_ids[i], output_ids=output_ids[i], rewards=[0.0])
+                    for i in range(lo, hi)]
+            batch = build_batch_from_rollouts(rows, device=self.device)
+            scores = self.reward_model.score(batch).float().cpu()
+            for j, i in enumerate(range(lo, hi)):
+                rewards[i, len(output_ids[i]) - 1] = scores[j]
+        return rewards

@@ -29,7 +29,7 @@ def rel_err(a, b):
 
 @pytest.mark.parametrize("layout", ["tn", "nn", "tt", "nt_a_mn"])
 @pytest.mark.parametrize("shape", [(128, 128, 64), (512, 768, 1024), (1000, 520, 264), (2048, 1024, 3072), (77, 3072, 4096)])
-@pytest.mark.parametrize("bn", [64, 128, 256])
+@pytest.mark.parametrize("bn", [64, 128, 256, 512])   # 512: the CTA-pair kernel (256 x 256 per two SMs)
 def test_gemm_layouts(C, layout, shape, bn):
     from halite_b200.ops import gemm
 
@@ -87,6 +87,29 @@ def test_gemm_split_k_tail_is_exact_and_deterministic(C, shape):
     assert rel_err(out, 2 * ref) < 3e-5
     ob = gemm(A, B, a_mn=True, b_mn=True)
     assert rel_err(ob, ref) < 6e-3
+
+
+@pytest.mark.parametrize("shape", [(5120, 3072, 2048), (4096, 5120, 512), (2560, 8192, 1024), (300, 1000, 4096)])
+def test_gemm_pair_kernel_waves_and_split_tail(C, shape):
+    """The CTA-pair kernel over several waves of 256 x 256 tiles, with and without a K-sliced last
+    wave, in the forward and weight-gradient layouts; results repeat bit for bit."""
+    from halite_b200.ops import gemm
+
+    M, N, K = shape
+    torch.manual_seed(4)
+    A = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    B = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    ref = A.float() @ B.float().t()
+    out = gemm(A, B, block_n=512)
+    assert rel_err(out, ref) < 6e-3
+    At, Bt = A.t().contiguous(), B.t().contiguous()
+    acc = gemm(At, Bt, a_mn=True, b_mn=True, out_dtype=torch.float32, block_n=512)
+    assert rel_err(acc, ref) < 3e-5
+    assert torch.equal(acc, gemm(At, Bt, a_mn=True, b_mn=True, out_dtype=torch.float32, block_n=512))
+    gemm(At, Bt, out=acc, a_mn=True, b_mn=True, accumulate=True, block_n=512)
+    assert rel_err(acc, 2 * ref) < 3e-5
+    dgrad = gemm(A, Bt, b_mn=True, block_n=512)
+    assert rel_err(dgrad, ref) < 6e-3
 
 
 def test_linear_autograd_matches_torch(C):

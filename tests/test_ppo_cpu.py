@@ -215,3 +215,17 @@ def test_async_rollout_primitives():
         buf.get(4, timeout=0.05)
     threading.Timer(0.05, lambda: buf.put(9, ["late"])).start()
     assert buf.get(9, timeout=5) == (9, ["late"])
+
+
+def test_ppo_iteration_benchmark_runs_four_models():
+    """Actor, critic, reference and reward model through one timed iteration (tiny widths)."""
+    import os
+
+    from halite_b200.projects.ppo import bench_iter
+
+    conf = os.path.join(os.path.dirname(os.path.abspath(__file__)), "configs/tiny_ppo_models.py")
+    out = bench_iter.main(["--conf", conf, "--prompts", "8", "--prompt-len", "12", "--new-tokens", "10",
+                           "--microbatch", "2", "--iters", "1", "--warmup", "0", "--device", "cpu"])
+    assert out["sampled_tokens_per_iteration_per_rank"] == 80 and out["value"] > 0
+    assert set(out["phases_s_per_iteration"]) == {"weight_sync", "rollout_and_reward_model",
+                                                  "logprobs_values_gae", "update"}
