@@ -253,6 +253,7 @@ struct SplitParams {
   int kb_per = 0;      // k-blocks per slice
   int items = 0;       // total number of work items
   int prefetch = 0;    // k-blocks of L2 prefetch ahead of the shared-memory loads (0 = off)
+  int group_m = 0;     // pair kernel: row tiles that share one column sweep (0 = default)
   float* workspace = nullptr;   // [tail][parts][4 quarters][BN/32][32 lanes][32] floats
   int* counters = nullptr;      // [tail][4 quarters], zeroed by the launcher
 };
@@ -693,11 +694,12 @@ struct PairCfg {
   static constexpr int kGroupM = 8;                     // raster group, in 256-row tiles
 };
 
-__device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
-  const int per_group = PairCfg::kGroupM * tiles_n;
+__device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int group_m, int& tm,
+                                                 int& tn) {
+  const int per_group = group_m * tiles_n;
   const int g = tile / per_group;
-  const int first_m = g * PairCfg::kGroupM;
-  const int gsz = min(PairCfg::kGroupM, tiles_m - first_m);
+  const int first_m = g * group_m;
+  const int gsz = min(group_m, tiles_m - first_m);
   const int r = tile - g * per_group;
   tm = first_m + r % gsz;
   tn = r / gsz;
@@ -757,6 +759,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
   const uint32_t tmem_base = tmem_slot;
 
   const int n_items = kp.parts > 1 ? kp.items : num_tiles;
+  const int group_m = kp.group_m > 0 ? kp.group_m : C::kGroupM;
   const int first_tile = static_cast<int>(cluster_id_x());
   const int tile_step = static_cast<int>(num_clusters_x());
 
@@ -768,7 +771,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
     for (int w = first_tile; w < n_items && ok; w += tile_step) {
       const WorkItem it = decode_item(kp, w, num_kb);
       int tm, tn;
-      pair_tile_coords(it.tile, tiles_m, tiles_n, tm, tn);
+      pair_tile_coords(it.tile, tiles_m, tiles_n, group_m, tm, tn);
       const int m0 = tm * 2 * kBM + static_cast<int>(rank) * kBM;
       const int n0 = tn * BN + static_cast<int>(rank) * C::kHalfN;
       for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
@@ -858,7 +861,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
     for (int w = first_tile; w < n_items && ok; w += tile_step, ++local) {
       const WorkItem it = decode_item(kp, w, num_kb);
       int tm, tn;
-      pair_tile_coords(it.tile, tiles_m, tiles_n, tm, tn);
+      pair_tile_coords(it.tile, tiles_m, tiles_n, group_m, tm, tn);
       const int m0 = tm * 2 * kBM + static_cast<int>(rank) * kBM;
       const int n0 = tn * BN;
       const int acc = local & 1;

@@ -42,13 +42,14 @@ def main():
     ap.add_argument("--layers", default="", help="comma list of layer names to run (default: all)")
     ap.add_argument("--cases", default="", help="comma list among fwd,dgrad,wgrad_f32 (default: all)")
     ap.add_argument("--no-cublas", action="store_true", help="time only this package's kernel")
-    ap.add_argument("--block-n", type=int, default=0,
-                    help="force a tile: 64 / 128 / 256 (one CTA per tile) or 512 (CTA pair, 256 x 256); 0 = choose")
+    ap.add_argument("--block-n", default="0",
+                    help="comma list of tiles to time: 64 / 128 / 256 (one CTA per tile), 512 (CTA pair, 256 x 256), "
+                         "0 = the launcher's choice")
     args = ap.parse_args()
     dev = "cuda"
     flush = torch.zeros(192 << 20, dtype=torch.uint8, device=dev)       # > 126 MB of L2
     T = args.tokens
-    bn = args.block_n
+    block_ns = [int(b) for b in args.block_n.split(",")]
     layers = [("qkv", args.dim, args.qkv), ("attn_out", args.dim, args.dim), ("up_gate", args.dim, 2 * args.ff),
               ("down", args.ff, args.dim)]
     if args.vocab:
@@ -65,23 +66,30 @@ def main():
         dx = torch.empty(T, k, device=dev, dtype=torch.bfloat16)
         dw = torch.empty(n, k, device=dev, dtype=torch.float32)
         dwb = torch.empty(n, k, device=dev, dtype=torch.bfloat16)
-        cases = {
-            "fwd": (lambda: gemm(x, w, out=y, block_n=bn), lambda: torch.matmul(x, w.t(), out=y)),
-            "dgrad": (lambda: gemm(dy, w, out=dx, b_mn=True, block_n=bn), lambda: torch.matmul(dy, w, out=dx)),
-            "wgrad_f32": (lambda: gemm(dy, x, out=dw, a_mn=True, b_mn=True, block_n=bn),
-                          lambda: torch.matmul(dy.t(), x, out=dwb)),
+        def cases_for(bn):
+            return {
+                "fwd": lambda: gemm(x, w, out=y, block_n=bn),
+                "dgrad": lambda: gemm(dy, w, out=dx, b_mn=True, block_n=bn),
+                "wgrad_f32": lambda: gemm(dy, x, out=dw, a_mn=True, b_mn=True, block_n=bn),
+            }
+
+        lib_cases = {
+            "fwd": lambda: torch.matmul(x, w.t(), out=y),
+            "dgrad": lambda: torch.matmul(dy, w, out=dx),
+            "wgrad_f32": lambda: torch.matmul(dy.t(), x, out=dwb),
         }
         flops = 2.0 * T * k * n
-        for case, (ours, lib) in cases.items():
+        for case, lib in lib_cases.items():
             if want_cases and case not in want_cases:
                 continue
-            t_ours = _time(ours, args.iters, flush)
             t_lib = float("nan") if args.no_cublas else _time(lib, args.iters, flush)
-            print(json.dumps({"layer": name, "case": case, "M_N_K": [T, n, k] if case == "fwd" else None,
-                              "block_n": bn, "ours_ms": round(t_ours, 4), "cublas_ms": round(t_lib, 4),
-                              "ours_tflops": round(flops / t_ours / 1e9, 1),
-                              "cublas_tflops": round(flops / t_lib / 1e9, 1),
-                              "ratio": round(t_lib / t_ours, 3)}), flush=True)
+            for bn in block_ns:
+                t_ours = _time(cases_for(bn)[case], args.iters, flush)
+                print(json.dumps({"layer": name, "case": case, "M_N_K": [T, n, k] if case == "fwd" else None,
+                                  "block_n": bn, "ours_ms": round(t_ours, 4), "cublas_ms": round(t_lib, 4),
+                                  "ours_tflops": round(flops / t_ours / 1e9, 1),
+                                  "cublas_tflops": round(flops / t_lib / 1e9, 1),
+                                  "ratio": round(t_lib / t_ours, 3)}), flush=True)
 
 
 if __name__ == "__main__":
