@@ -1,5 +1,6 @@
 """Benchmark variant of Llama-3.2-3B: N(0, 0.02) initialisation, Llama-3 RoPE scaling factor 32,
-and the head replaced by the fused linear + cross-entropy module (loss computed in the model)."""
+the head replaced by the fused linear + cross-entropy module (loss computed in the model), and
+blocks that fold every residual add into the following RMSNorm kernel."""
 
 from functools import partial
 
@@ -7,7 +8,7 @@ from halite_b200.conf import call, field
 from halite_b200.models.position import Llama3RoPE, apply_rotary_emb
 from torch import nn
 
-from ..transformer import transformer, use_fused_linear_cross_entropy
+from ..transformer import transformer, use_fused_linear_cross_entropy, use_fused_residual
 
 conf = field()
 
@@ -15,7 +16,7 @@ dim = 3072
 n_heads = 24
 head_dim = dim // n_heads
 
-conf.model = use_fused_linear_cross_entropy(
+conf.model = use_fused_residual(use_fused_linear_cross_entropy(
     call[transformer](
         vocab_size=128256,
         dim=dim,
@@ -32,4 +33,4 @@ conf.model = use_fused_linear_cross_entropy(
         gated_ff_split=True,
         init=partial(nn.init.normal_, std=0.02),
     )
-)
+))

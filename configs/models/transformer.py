@@ -14,7 +14,7 @@ from torch import nn
 from halite_b200.nn.activation import GEGLU, SwiGLU
 from halite_b200.nn.normalization import RMSNorm
 from halite_b200.models.attention import Attention, SelfAttention, SelfAttentionQKV
-from halite_b200.models.block import ResidualBlock, TransformerEncoderBlock
+from halite_b200.models.block import FusedTransformerEncoderBlock, ResidualBlock, TransformerEncoderBlock
 from halite_b200.models.embedding import TextEmbedding
 from halite_b200.models.feedforward import (FeedForward, FusedLinearCrossEntropy, GatedFeedForward,
                                             SequenceParallelWrapper, VocabParallelLinear)
@@ -197,6 +197,14 @@ def use_flex_attention(model_conf):
 @config_fn
 def use_flash_attention(model_conf):
     return select(model_conf).instance(Attention).update_dict(dict(processor="flash_attn"))
+
+
+@config_fn
+def use_fused_residual(model_conf):
+    """Pre-norm blocks that hand the un-normalised residual stream to the next norm, so every
+    residual add runs inside the following RMSNorm kernel (forward and backward)."""
+    return select(model_conf).instance(TransformerEncoderBlock).map(
+        lambda x: FusedTransformerEncoderBlock(x.self_attention, x.ff))
 
 
 @config_fn

@@ -174,6 +174,138 @@ rmsnorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16*
   }
 }
 
+// Row-in-registers variants: one 128-thread CTA per row, each thread holding VPT 16-byte vectors
+// of the row (and of its companion operand) packed in registers between the reduction and the
+// output pass; all loads of a row are issued before the first use, and the many small CTAs per
+// SM overlap one another's load, reduce and store phases. Covers dim <= 128 * 8 * VPT.
+constexpr int kRowThreads = 128;
+
+__device__ __forceinline__ float row_sum(float v, float* red) {
+  v = warp_sum(v);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  return red[0] + red[1] + red[2] + red[3];
+}
+
+template <int VPT, bool HAS_RES, bool WRITE_H>
+__global__ void __launch_bounds__(kRowThreads)
+rmsnorm_fwd_row_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                       const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                       __nv_bfloat16* __restrict__ h_out, float* __restrict__ rstd_out, int dim, float eps,
+                       float w_offset) {
+  __shared__ float red[4];
+  const long row = blockIdx.x;
+  const int nvec = dim >> 3;
+  const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * dim);
+  const bf16x8* rr = HAS_RES ? reinterpret_cast<const bf16x8*>(res + row * dim) : nullptr;
+  const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
+  bf16x8 xv[VPT], rv[HAS_RES ? VPT : 1];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * kRowThreads;
+    if (v < nvec) {
+      xv[i] = xr[v];
+      if (HAS_RES) rv[i] = rr[v];
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * kRowThreads;
+    if (v < nvec) {
+      float h[8];
+      unpack8(xv[i], h);
+      if (HAS_RES) {
+        float r[8];
+        unpack8(rv[i], r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) h[j] += r[j];
+        xv[i] = pack8(h);          // the normalisation sees the rounded residual stream
+        unpack8(xv[i], h);
+        if (WRITE_H) reinterpret_cast<bf16x8*>(h_out + row * dim)[v] = xv[i];
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += h[j] * h[j];
+    }
+  }
+  ss = row_sum(ss, red);
+  const float rstd = rsqrtf(ss / dim + eps);
+  if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+  bf16x8* yr = reinterpret_cast<bf16x8*>(y + row * dim);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * kRowThreads;
+    if (v < nvec) {
+      float h[8], wv[8], o[8];
+      unpack8(xv[i], h);
+      unpack8(wr[v], wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = h[j] * rstd * (wv[j] + w_offset);
+      yr[v] = pack8(o);
+    }
+  }
+}
+
+template <int VPT, bool HAS_DRES>
+__global__ void __launch_bounds__(kRowThreads)
+rmsnorm_bwd_dx_row_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
+                          const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                          const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx, int dim,
+                          float w_offset) {
+  __shared__ float red[4];
+  const long row = blockIdx.x;
+  const int nvec = dim >> 3;
+  const bf16x8* dyr = reinterpret_cast<const bf16x8*>(dy + row * dim);
+  const bf16x8* hr = reinterpret_cast<const bf16x8*>(h + row * dim);
+  const bf16x8* drr = HAS_DRES ? reinterpret_cast<const bf16x8*>(dres + row * dim) : nullptr;
+  const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
+  bf16x8 gv[VPT], hv[VPT], rv[HAS_DRES ? VPT : 1];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * kRowThreads;
+    if (v < nvec) {
+      gv[i] = dyr[v];
+      hv[i] = hr[v];
+      if (HAS_DRES) rv[i] = drr[v];
+    }
+  }
+  const float rs = rstd[row];
+  float dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * kRowThreads;
+    if (v < nvec) {
+      float d[8], hh[8], wv[8];
+      unpack8(gv[i], d);
+      unpack8(hv[i], hh);
+      unpack8(wr[v], wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dot += d[j] * (wv[j] + w_offset) * hh[j];
+    }
+  }
+  dot = row_sum(dot, red) * rs / dim;  // mean(g * xhat)
+  bf16x8* dxr = reinterpret_cast<bf16x8*>(dx + row * dim);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * kRowThreads;
+    if (v < nvec) {
+      float d[8], hh[8], wv[8], o[8];
+      unpack8(gv[i], d);
+      unpack8(hv[i], hh);
+      unpack8(wr[v], wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = rs * (d[j] * (wv[j] + w_offset) - hh[j] * rs * dot);
+      if (HAS_DRES) {
+        float r[8];
+        unpack8(rv[i], r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += r[j];
+      }
+      dxr[v] = pack8(o);
+    }
+  }
+}
+
 // (2) dw partials: CTA (x, y) sums dy * h * rstd over its row slice for 256 columns.
 __global__ void __launch_bounds__(256)
 rmsnorm_bwd_dw_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
@@ -265,6 +397,69 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restri
       float2 b = __bfloat1622float2(*hi);
       *lo = __floats2bfloat162_rn(a.x * c.x - b.x * s.x, a.y * c.y - b.y * s.y);
       *hi = __floats2bfloat162_rn(b.x * c.x + a.x * s.x, b.y * c.y + a.y * s.y);
+    }
+  }
+}
+
+// 16-byte variant, optionally out of place (src and dst may have different token strides, e.g.
+// a contiguous gradient rotated into its slot of a packed qkv gradient). One thread per
+// (token, head, 8 elements); elements past rot_dim are copied when src != dst.
+template <typename PosT, bool INTERLEAVED>
+__global__ void rope_vec_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst,
+                                const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                const PosT* __restrict__ pos, int tokens, int heads, int head_dim,
+                                int rot_dim, long src_stride, long dst_stride, float sign, bool in_place) {
+  const int half = rot_dim >> 1;
+  const int vph = head_dim >> 3;
+  const long total = static_cast<long>(tokens) * heads * vph;
+  for (long idx = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long>(gridDim.x) * blockDim.x) {
+    const int j = idx % vph;
+    const long th = idx / vph;
+    const int hd = th % heads;
+    const long t = th / heads;
+    const __nv_bfloat16* s = src + t * src_stride + static_cast<long>(hd) * head_dim;
+    __nv_bfloat16* d = dst + t * dst_stride + static_cast<long>(hd) * head_dim;
+    if (INTERLEAVED) {
+      if (8 * j < rot_dim) {
+        const long p = static_cast<long>(pos[t]);
+        const float4 c = *reinterpret_cast<const float4*>(cos_t + p * half + 4 * j);
+        const float4 sn = *reinterpret_cast<const float4*>(sin_t + p * half + 4 * j);
+        float f[8], o[8];
+        unpack8(*reinterpret_cast<const bf16x8*>(s + 8 * j), f);
+        const float cc[4] = {c.x, c.y, c.z, c.w};
+        const float ss[4] = {sn.x * sign, sn.y * sign, sn.z * sign, sn.w * sign};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          o[2 * k] = f[2 * k] * cc[k] - f[2 * k + 1] * ss[k];
+          o[2 * k + 1] = f[2 * k] * ss[k] + f[2 * k + 1] * cc[k];
+        }
+        *reinterpret_cast<bf16x8*>(d + 8 * j) = pack8(o);
+      } else if (!in_place) {
+        *reinterpret_cast<bf16x8*>(d + 8 * j) = *reinterpret_cast<const bf16x8*>(s + 8 * j);
+      }
+    } else {
+      const int hv = half >> 3;
+      if (j < hv) {
+        const long p = static_cast<long>(pos[t]);
+        float cc[8], ss[8], lo[8], hi[8], olo[8], ohi[8];
+        *reinterpret_cast<float4*>(cc) = *reinterpret_cast<const float4*>(cos_t + p * half + 8 * j);
+        *reinterpret_cast<float4*>(cc + 4) = *reinterpret_cast<const float4*>(cos_t + p * half + 8 * j + 4);
+        *reinterpret_cast<float4*>(ss) = *reinterpret_cast<const float4*>(sin_t + p * half + 8 * j);
+        *reinterpret_cast<float4*>(ss + 4) = *reinterpret_cast<const float4*>(sin_t + p * half + 8 * j + 4);
+        unpack8(*reinterpret_cast<const bf16x8*>(s + 8 * j), lo);
+        unpack8(*reinterpret_cast<const bf16x8*>(s + half + 8 * j), hi);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float sk = ss[k] * sign;
+          olo[k] = lo[k] * cc[k] - hi[k] * sk;
+          ohi[k] = hi[k] * cc[k] + lo[k] * sk;
+        }
+        *reinterpret_cast<bf16x8*>(d + 8 * j) = pack8(olo);
+        *reinterpret_cast<bf16x8*>(d + half + 8 * j) = pack8(ohi);
+      } else if (8 * j >= rot_dim && !in_place) {
+        *reinterpret_cast<bf16x8*>(d + 8 * j) = *reinterpret_cast<const bf16x8*>(s + 8 * j);
+      }
     }
   }
 }
@@ -696,6 +891,26 @@ cudaError_t rmsnorm_fwd(const void* x, const void* residual, const void* w, void
   auto W = static_cast<const __nv_bfloat16*>(w);
   auto Y = static_cast<__nv_bfloat16*>(y);
   auto H = static_cast<__nv_bfloat16*>(h_out);
+  const int vpt = (dim / 8 + kRowThreads - 1) / kRowThreads;
+  if (vpt <= 8) {
+#define HB_NORM_FWD(V)                                                                                        \
+  do {                                                                                                        \
+    if (R && H)                                                                                               \
+      rmsnorm_fwd_row_kernel<V, true, true><<<rows, kRowThreads, 0, stream>>>(X, R, W, Y, H, rstd, dim, eps, w_offset);  \
+    else if (R)                                                                                               \
+      rmsnorm_fwd_row_kernel<V, true, false><<<rows, kRowThreads, 0, stream>>>(X, R, W, Y, H, rstd, dim, eps, w_offset); \
+    else                                                                                                      \
+      rmsnorm_fwd_row_kernel<V, false, false><<<rows, kRowThreads, 0, stream>>>(X, R, W, Y, H, rstd, dim, eps, w_offset); \
+  } while (0)
+    if (vpt <= 1) HB_NORM_FWD(1);
+    else if (vpt <= 2) HB_NORM_FWD(2);
+    else if (vpt <= 3) HB_NORM_FWD(3);
+    else if (vpt <= 4) HB_NORM_FWD(4);
+    else if (vpt <= 6) HB_NORM_FWD(6);
+    else HB_NORM_FWD(8);
+#undef HB_NORM_FWD
+    return cudaGetLastError();
+  }
   if (R && H)
     rmsnorm_fwd_kernel<true, true><<<rows, kNormThreads, 0, stream>>>(X, R, W, Y, H, rstd, dim, eps, w_offset);
   else if (R)
@@ -717,10 +932,25 @@ cudaError_t rmsnorm_bwd(const void* dy, const void* h, const void* w, const floa
   auto DR = static_cast<const __nv_bfloat16*>(dres);
   auto DX = static_cast<__nv_bfloat16*>(dx);
   const int grid_dx = (rows + 7) / 8;
-  if (DR)
+  const int vpt = (dim / 8 + kRowThreads - 1) / kRowThreads;
+#define HB_NORM_BWD(V)                                                                                          \
+  do {                                                                                                          \
+    if (DR)                                                                                                     \
+      rmsnorm_bwd_dx_row_kernel<V, true><<<rows, kRowThreads, 0, stream>>>(DY, H, W, rstd, DR, DX, dim, w_offset);  \
+    else                                                                                                        \
+      rmsnorm_bwd_dx_row_kernel<V, false><<<rows, kRowThreads, 0, stream>>>(DY, H, W, rstd, DR, DX, dim, w_offset); \
+  } while (0)
+  if (vpt <= 1) HB_NORM_BWD(1);
+  else if (vpt <= 2) HB_NORM_BWD(2);
+  else if (vpt <= 3) HB_NORM_BWD(3);
+  else if (vpt <= 4) HB_NORM_BWD(4);
+  else if (vpt <= 6) HB_NORM_BWD(6);
+  else if (vpt <= 8) HB_NORM_BWD(8);
+  else if (DR)
     rmsnorm_bwd_dx_kernel<true><<<grid_dx, 256, 0, stream>>>(DY, H, W, rstd, DR, DX, rows, dim, w_offset);
   else
     rmsnorm_bwd_dx_kernel<false><<<grid_dx, 256, 0, stream>>>(DY, H, W, rstd, DR, DX, rows, dim, w_offset);
+#undef HB_NORM_BWD
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   // every one of the `partial_rows` rows is written (row slices may be empty -> zeros)
@@ -735,21 +965,52 @@ cudaError_t colsum_f32(const float* partial, int prows, int dim, void* out, bool
   return cudaGetLastError();
 }
 
-cudaError_t rope_inplace(void* x, const float* cos, const float* sin, const void* positions,
-                         bool pos_is_i64, int tokens, int heads, int head_dim, int rot_dim,
-                         long token_stride, bool interleaved, bool conjugate, cudaStream_t stream) {
-  if (tokens == 0) return cudaSuccess;
-  if (rot_dim % 4 != 0 || rot_dim > head_dim || head_dim % 4 != 0 || token_stride % 4 != 0)
+cudaError_t rope_apply(const void* src, void* dst, const float* cos, const float* sin, const void* positions,
+                       bool pos_is_i64, int tokens, int heads, int head_dim, int rot_dim, long src_stride,
+                       long dst_stride, bool interleaved, bool conjugate, cudaStream_t stream) {
+  if (tokens == 0 || heads == 0) return cudaSuccess;
+  const bool in_place = src == dst && src_stride == dst_stride;
+  if (rot_dim > head_dim) return cudaErrorInvalidValue;
+  const float sign = conjugate ? -1.f : 1.f;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst) |
+                         reinterpret_cast<uintptr_t>(cos) | reinterpret_cast<uintptr_t>(sin)) & 15) == 0;
+  const bool vec_ok = aligned && head_dim % 8 == 0 && src_stride % 8 == 0 && dst_stride % 8 == 0 &&
+                      rot_dim % (interleaved ? 8 : 16) == 0;
+  auto S = static_cast<const __nv_bfloat16*>(src);
+  auto D = static_cast<__nv_bfloat16*>(dst);
+  if (vec_ok) {
+    const long total = static_cast<long>(tokens) * heads * (head_dim / 8);
+    const int grid = grid_for(total, 256);
+#define HB_ROPE_VEC(PT, IL)                                                                              \
+  rope_vec_kernel<PT, IL><<<grid, 256, 0, stream>>>(S, D, cos, sin, static_cast<const PT*>(positions), tokens, \
+                                                    heads, head_dim, rot_dim, src_stride, dst_stride, sign, in_place)
+    if (pos_is_i64) {
+      if (interleaved) HB_ROPE_VEC(int64_t, true);
+      else HB_ROPE_VEC(int64_t, false);
+    } else {
+      if (interleaved) HB_ROPE_VEC(int32_t, true);
+      else HB_ROPE_VEC(int32_t, false);
+    }
+#undef HB_ROPE_VEC
+    return cudaGetLastError();
+  }
+  // narrow fallback: in place only
+  if (!in_place || rot_dim % 4 != 0 || head_dim % 4 != 0 || src_stride % 4 != 0 || rot_dim == 0)
     return cudaErrorInvalidValue;
   const long total = static_cast<long>(tokens) * heads * (rot_dim / 4);
   const int grid = grid_for(total, 256);
-  const float sign = conjugate ? -1.f : 1.f;
-  auto X = static_cast<__nv_bfloat16*>(x);
   if (pos_is_i64)
-    rope_kernel<int64_t><<<grid, 256, 0, stream>>>(X, cos, sin, static_cast<const int64_t*>(positions), tokens, heads, head_dim, rot_dim, token_stride, interleaved, sign);
+    rope_kernel<int64_t><<<grid, 256, 0, stream>>>(D, cos, sin, static_cast<const int64_t*>(positions), tokens, heads, head_dim, rot_dim, dst_stride, interleaved, sign);
   else
-    rope_kernel<int32_t><<<grid, 256, 0, stream>>>(X, cos, sin, static_cast<const int32_t*>(positions), tokens, heads, head_dim, rot_dim, token_stride, interleaved, sign);
+    rope_kernel<int32_t><<<grid, 256, 0, stream>>>(D, cos, sin, static_cast<const int32_t*>(positions), tokens, heads, head_dim, rot_dim, dst_stride, interleaved, sign);
   return cudaGetLastError();
+}
+
+cudaError_t rope_inplace(void* x, const float* cos, const float* sin, const void* positions,
+                         bool pos_is_i64, int tokens, int heads, int head_dim, int rot_dim,
+                         long token_stride, bool interleaved, bool conjugate, cudaStream_t stream) {
+  return rope_apply(x, x, cos, sin, positions, pos_is_i64, tokens, heads, head_dim, rot_dim, token_stride,
+                    token_stride, interleaved, conjugate, stream);
 }
 
 cudaError_t gated_act_fwd(const void* gate, const void* up, void* out, long n, long row, long gate_ld,

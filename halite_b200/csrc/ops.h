@@ -27,6 +27,12 @@ cudaError_t rope_inplace(void* x, const float* cos, const float* sin, const void
                          bool pos_is_i64, int tokens, int heads, int head_dim, int rot_dim,
                          long token_stride, bool interleaved, bool conjugate, cudaStream_t stream);
 
+// Out-of-place form: dst[token, head, :] = rotate(src[token, head, :]) with independent token strides
+// (elements past rot_dim are copied; rot_dim = 0 is a strided copy). src == dst is the in-place case.
+cudaError_t rope_apply(const void* src, void* dst, const float* cos, const float* sin, const void* positions,
+                       bool pos_is_i64, int tokens, int heads, int head_dim, int rot_dim, long src_stride,
+                       long dst_stride, bool interleaved, bool conjugate, cudaStream_t stream);
+
 // ---- gated activations: out = act(gate) * up ; kind 0 = SiLU (SwiGLU), 1 = GELU tanh (GEGLU)
 cudaError_t gated_act_fwd(const void* gate, const void* up, void* out, long n, long row, long gate_ld,
                           long up_ld, int kind, cudaStream_t stream);

@@ -102,6 +102,48 @@ void rope_(at::Tensor& x, const at::Tensor& cos, const at::Tensor& sin, const at
                               interleaved, conjugate, cur_stream()));
 }
 
+static int64_t collapsed_token_stride(const at::Tensor& x, const char* name) {
+  const int64_t head_dim = x.size(-1);
+  TORCH_CHECK(x.dim() >= 3 && x.stride(-1) == 1 && x.stride(-2) == head_dim, name, ": heads must be packed");
+  for (int d = x.dim() - 4; d >= 0; --d)
+    TORCH_CHECK(x.size(d) == 1 || x.stride(d) == x.stride(d + 1) * x.size(d + 1), name,
+                ": token dims must be collapsible");
+  return x.stride(-3);
+}
+
+// dst[..., heads, head_dim] = rotate(src[..., heads, head_dim]); both may be strided views (slices
+// of packed qkv tensors). Without tables (rot_dim = 0) this is a strided copy.
+void rope_copy(const at::Tensor& src, at::Tensor& dst, const c10::optional<at::Tensor>& cos,
+               const c10::optional<at::Tensor>& sin, const c10::optional<at::Tensor>& positions, int64_t rot_dim,
+               bool interleaved, bool conjugate) {
+  TORCH_CHECK(src.is_cuda() && src.scalar_type() == at::kBFloat16 && dst.is_cuda() &&
+                  dst.scalar_type() == at::kBFloat16, "src/dst must be CUDA bf16");
+  TORCH_CHECK(src.sizes() == dst.sizes(), "src/dst shapes differ");
+  const int64_t head_dim = src.size(-1), heads = src.size(-2);
+  const int64_t tokens = src.numel() / (heads * head_dim);
+  const int64_t ss = collapsed_token_stride(src, "src"), ds = collapsed_token_stride(dst, "dst");
+  const float* c = nullptr;
+  const float* s = nullptr;
+  const void* p = nullptr;
+  bool i64 = false;
+  if (rot_dim > 0) {
+    TORCH_CHECK(cos.has_value() && sin.has_value() && positions.has_value(), "rotation needs cos, sin and positions");
+    check_f32(*cos, "cos");
+    check_f32(*sin, "sin");
+    TORCH_CHECK(positions->is_cuda() && positions->is_contiguous() && positions->numel() == tokens &&
+                    (positions->scalar_type() == at::kLong || positions->scalar_type() == at::kInt),
+                "positions must be contiguous CUDA int32/int64, one per token");
+    TORCH_CHECK(cos->size(-1) * 2 == rot_dim, "cos/sin tables must be [max_pos, rot_dim/2]");
+    c = cos->data_ptr<float>();
+    s = sin->data_ptr<float>();
+    p = positions->data_ptr();
+    i64 = positions->scalar_type() == at::kLong;
+  }
+  c10::cuda::CUDAGuard guard(src.device());
+  HB_CUDA_OK(hb::rope_apply(src.data_ptr(), dst.data_ptr(), c, s, p, i64, (int)tokens, (int)heads, (int)head_dim,
+                            (int)rot_dim, ss, ds, interleaved, conjugate, cur_stream()));
+}
+
 at::Tensor gated_act_fwd(const at::Tensor& gate, const at::Tensor& up, int64_t kind) {
   TORCH_CHECK(gate.is_cuda() && gate.scalar_type() == at::kBFloat16 && gate.stride(-1) == 1);
   TORCH_CHECK(up.is_cuda() && up.scalar_type() == at::kBFloat16 && up.stride(-1) == 1);
@@ -327,6 +369,8 @@ void register_elementwise(pybind11::module_& m) {
         py::arg("dres"), py::arg("w_offset") = 0.0);
   m.def("rope_", &rope_, py::arg("x"), py::arg("cos"), py::arg("sin"), py::arg("positions"),
         py::arg("rot_dim"), py::arg("interleaved"), py::arg("conjugate") = false);
+  m.def("rope_copy", &rope_copy, py::arg("src"), py::arg("dst"), py::arg("cos"), py::arg("sin"),
+        py::arg("positions"), py::arg("rot_dim"), py::arg("interleaved"), py::arg("conjugate") = false);
   m.def("gated_act_fwd", &gated_act_fwd, py::arg("gate"), py::arg("up"), py::arg("kind") = 0);
   m.def("gated_act_bwd", &gated_act_bwd, py::arg("gate"), py::arg("up"), py::arg("dout"),
         py::arg("kind") = 0, py::arg("dgate_out") = py::none(), py::arg("dup_out") = py::none());

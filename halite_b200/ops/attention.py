@@ -114,8 +114,9 @@ class _PackedQKVAttention(torch.autograd.Function):
         if cos is not None:
             pos = positions.expand(B, S).reshape(-1).contiguous()
             rot = cos.shape[-1] * 2
-            C.rope_(q, cos, sin, pos, rot, interleaved, False)
-            C.rope_(k, cos, sin, pos, rot, interleaved, False)
+            # q and k heads are neighbours in the packed row: one launch rotates both
+            C.rope_(qkv[..., :qd + kd].unflatten(-1, (n_heads + n_kv, head_dim)), cos, sin, pos, rot,
+                    interleaved, False)
         if not ctx.needs_input_grad[0]:
             return _sdpa(q, k, v, causal and S > 1, scale).reshape(B, S, qd)
         with torch.enable_grad():
@@ -138,14 +139,13 @@ class _PackedQKVAttention(torch.autograd.Function):
         gq = dqkv[..., :qd].unflatten(-1, (H, D))
         gk = dqkv[..., qd:qd + kd].unflatten(-1, (Hk, D))
         gv = dqkv[..., qd + kd:].unflatten(-1, (Hk, D))
-        gq.copy_(dq)
-        gk.copy_(dk)
-        gv.copy_(dv)
         cos, sin, pos, interleaved = ctx.rope
-        if cos is not None:
-            rot = cos.shape[-1] * 2
-            C.rope_(gq, cos, sin, pos, rot, interleaved, True)
-            C.rope_(gk, cos, sin, pos, rot, interleaved, True)
+        rot = cos.shape[-1] * 2 if cos is not None else 0
+        # each gradient is read once and lands, un-rotated, in its slot of the packed gradient
+        for src, dst, r in ((dq, gq, rot), (dk, gk, rot), (dv, gv, 0)):
+            if src.stride(-1) != 1 or src.stride(-2) != D:
+                src = src.contiguous()
+            C.rope_copy(src, dst, cos if r else None, sin if r else None, pos if r else None, r, interleaved, True)
         return dqkv, None, None, None, None, None, None, None, None, None
 
 

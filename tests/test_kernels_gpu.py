@@ -131,7 +131,7 @@ def test_linear_autograd_matches_torch(C):
     assert rel_err(b.grad, br.grad) < 1e-2
 
 
-@pytest.mark.parametrize("dim", [256, 3072, 4096, 8192])
+@pytest.mark.parametrize("dim", [256, 1000, 2048, 3072, 4096, 8192])
 @pytest.mark.parametrize("residual", [False, True])
 def test_rmsnorm(C, dim, residual):
     from halite_b200 import ops
