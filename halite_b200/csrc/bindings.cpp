@@ -152,6 +152,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("a_mn") = false, py::arg("b_mn") = false, py::arg("accumulate") = false,
         py::arg("block_n") = 0, py::arg("max_ctas") = 0, py::arg("status") = py::none(),
         py::arg("gather") = py::none(), py::arg("scatter") = py::none());
+  m.def("gemm_set_dynamic_schedule", [](bool on, bool force) { hb::gemm_set_dynamic_schedule(on, force); },
+        "CTA-pair GEMM: hand work items out through a counter (true) or in fixed shares (false)",
+        py::arg("on"), py::arg("force") = false);
   m.def("signal_flags", &signal_flags, "write epoch to flag words (possibly in peer memory)");
   m.def("wait_flags", &wait_flags, py::arg("flags"), py::arg("epoch"), py::arg("status") = py::none());
   m.def("launch_count", []() { return hb::launch_counter().load(); },

@@ -80,6 +80,9 @@ cudaError_t gemm_bf16(const GemmArgs& args);
 cudaError_t signal_flags(const int64_t* ptrs, int n, int epoch, cudaStream_t stream);
 cudaError_t wait_flags(const int* flags, int n, int epoch, int* status, cudaStream_t stream);
 int gemm_pick_bn(int M, int N);
+// Pair kernel: hand work items out through a counter, or in fixed shares (default). A setting from
+// the environment (HB_GEMM_DYNAMIC=0/1) wins unless `force`.
+void gemm_set_dynamic_schedule(bool on, bool force = false);
 
 bool make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
                        uint64_t ld, uint32_t box_rows, uint32_t box_cols);

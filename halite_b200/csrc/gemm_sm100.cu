@@ -254,6 +254,7 @@ struct SplitParams {
   int items = 0;       // total number of work items
   int prefetch = 0;    // k-blocks of L2 prefetch ahead of the shared-memory loads (0 = off)
   int group_m = 0;     // pair kernel: row tiles that share one column sweep (0 = default)
+  int* tile_counter = nullptr;  // pair kernel: zeroed counter that hands out work items (nullptr = static schedule)
   float* workspace = nullptr;   // [tail][parts][4 quarters][BN/32][32 lanes][32] floats
   int* counters = nullptr;      // [tail][4 quarters], zeroed by the launcher
 };
@@ -681,6 +682,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
 //   empty[s]   one in each CTA, released together by a commit addressed to both
 //   tfull[a]   one in each CTA (both epilogues wait locally), same commit form
 //   tempty[a]  lives in the even CTA; the eight epilogue warps of the pair arrive on it
+// Work items are handed out dynamically when the launcher provides a counter: the even CTA's
+// producer draws the next item number with an atomic add and publishes it through a four-entry
+// ring in both CTAs' shared memory (sfull[i] in each CTA, sempty[i] in the even CTA, on which
+// the pair's other ten consumers arrive). A cluster that starts late, because its SMs were busy
+// with another kernel (a collective running beside the GEMM), then simply takes fewer items
+// instead of holding the whole launch back with a fixed share. Without a counter cluster c
+// takes items c, c + n_clusters, ... .
 struct PairCfg {
   static constexpr int kBN = 256;                       // columns of the pair's tile
   static constexpr int kHalfN = 128;                    // columns of B held by one CTA
@@ -692,6 +700,8 @@ struct PairCfg {
   static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024;
   static constexpr int kTmemCols = 2 * kBN;
   static constexpr int kGroupM = 8;                     // raster group, in 256-row tiles
+  static constexpr int kSched = 4;                      // depth of the work-item ring
+  static constexpr int kSchedReaders = 10;              // MMA + 4 epilogue warps here, producer + 4 epilogue warps there
 };
 
 __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int group_m, int& tm,
@@ -720,6 +730,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
   __shared__ __align__(8) uint64_t bar_empty[kStages];
   __shared__ __align__(8) uint64_t bar_tfull[2];
   __shared__ __align__(8) uint64_t bar_tempty[2];
+  __shared__ __align__(8) uint64_t bar_sfull[PairCfg::kSched];
+  __shared__ __align__(8) uint64_t bar_sempty[PairCfg::kSched];
+  __shared__ int sched_item[PairCfg::kSched];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -744,6 +757,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
       mbar_init(smem_u32(&bar_tfull[s]), 1);   // one commit
       mbar_init(smem_u32(&bar_tempty[s]), 8);  // four epilogue warps in each CTA
     }
+    for (int s = 0; s < C::kSched; ++s) {
+      mbar_init(smem_u32(&bar_sfull[s]), 1);
+      mbar_init(smem_u32(&bar_sempty[s]), C::kSchedReaders);
+    }
     fence_barrier_init();
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
@@ -762,13 +779,56 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
   const int group_m = kp.group_m > 0 ? kp.group_m : C::kGroupM;
   const int first_tile = static_cast<int>(cluster_id_x());
   const int tile_step = static_cast<int>(num_clusters_x());
+  const bool dynamic = kp.tile_counter != nullptr;
+
+  // Next work item of this role (-1: none left, or a wait gave up). `n` counts the items the
+  // role has taken so far; every role of the pair sees the same sequence.
+  auto next_item = [&](int n) -> int {
+    if (!dynamic) {
+      const int w = first_tile + n * tile_step;
+      return w < n_items ? w : -1;
+    }
+    const int slot = n % C::kSched;
+    const uint32_t sphase = (n / C::kSched) & 1;
+    if (!mbar_wait_cluster(smem_u32(&bar_sfull[slot]), sphase, &abort_flag, status, kTimeoutSchedule)) return -1;
+    const int w = *reinterpret_cast<volatile int*>(&sched_item[slot]);
+    const uint32_t release = mapa_shared(smem_u32(&bar_sempty[slot]), 0);
+    if (warp >= 4) {           // epilogue warps come here with all lanes, the other roles with one
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(release);
+    } else {
+      mbar_arrive_cluster(release);
+    }
+    return w;
+  };
+  // The even CTA's producer fills the ring: entry n gets item `w` (already drawn from the counter).
+  auto publish_item = [&](int n, int w) -> int {
+    const int slot = n % C::kSched;
+    const uint32_t sphase = (n / C::kSched) & 1;
+    if (!mbar_wait_cluster(smem_u32(&bar_sempty[slot]), sphase ^ 1, &abort_flag, status, kTimeoutSchedule))
+      return -1;
+    if (w >= n_items) w = -1;
+    *reinterpret_cast<volatile int*>(&sched_item[slot]) = w;
+    st_shared_cluster_u32(mapa_shared(smem_u32(&sched_item[slot]), 1), static_cast<uint32_t>(w));
+    mbar_arrive(smem_u32(&bar_sfull[slot]));
+    mbar_arrive_cluster(mapa_shared(smem_u32(&bar_sfull[slot]), 1));
+    return w;
+  };
 
   if (warp == 0 && lane == 0) {
     // ------------------------------------------------------------ producer (one per CTA)
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int w = first_tile; w < n_items && ok; w += tile_step) {
+    // The even CTA's producer draws item n + 1 from the counter before it loads item n and
+    // publishes it afterwards: the counter's round trip overlaps the loads.
+    const bool scheduler = dynamic && leader;
+    int current = scheduler ? publish_item(0, atomicAdd(kp.tile_counter, 1)) : 0;
+    for (int n = 0; ok; ++n) {
+      const int w = scheduler ? current : next_item(n);
+      int drawn = 0;
+      if (scheduler && w >= 0) drawn = atomicAdd(kp.tile_counter, 1);
+      if (w < 0) break;
       const WorkItem it = decode_item(kp, w, num_kb);
       int tm, tn;
       pair_tile_coords(it.tile, tiles_m, tiles_n, group_m, tm, tn);
@@ -801,6 +861,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
           phase ^= 1;
         }
       }
+      if (scheduler && ok) current = publish_item(n + 1, drawn);
     }
     // The stage releases come from the even CTA's commits: wait until every one addressed to
     // this CTA has landed, so that none arrives after the CTA has left.
@@ -818,7 +879,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
     uint32_t phase = 0;
     int local = 0;
     bool ok = true;
-    for (int w = first_tile; w < n_items && ok; w += tile_step, ++local) {
+    for (; ok; ++local) {
+      const int w = next_item(local);
+      if (w < 0) break;
       const WorkItem it = decode_item(kp, w, num_kb);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
@@ -858,7 +921,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
     const ScatterParams no_scatter;
     int local = 0;
     bool ok = true;
-    for (int w = first_tile; w < n_items && ok; w += tile_step, ++local) {
+    for (; ok; ++local) {
+      const int w = next_item(local);
+      if (w < 0) break;
       const WorkItem it = decode_item(kp, w, num_kb);
       int tm, tn;
       pair_tile_coords(it.tile, tiles_m, tiles_n, group_m, tm, tn);
@@ -1132,6 +1197,23 @@ cudaError_t dispatch_layout(const GemmArgs& g) {
   return launch<BN, true, false, OutT>(g);
 }
 
+// Dynamic hand-out of work items in the pair kernel; HB_GEMM_DYNAMIC=0 keeps the fixed shares.
+// Fixed shares keep neighbouring clusters on neighbouring tiles (best L2 reuse) and are the
+// default; the counter-driven hand-out pays off when another kernel (a collective) holds some
+// SMs while the GEMM runs, and is switched on by the data-parallel wrapper. HB_GEMM_DYNAMIC=0/1
+// overrides both.
+int g_dynamic_schedule = -1;   // -1: not decided yet, 0 / 1: off / on
+bool g_dynamic_forced = false;
+
+bool dynamic_schedule_enabled() {
+  if (g_dynamic_schedule < 0) {
+    const char* env = getenv("HB_GEMM_DYNAMIC");
+    g_dynamic_forced = env != nullptr;
+    g_dynamic_schedule = (env && env[0] == '1') ? 1 : 0;
+  }
+  return g_dynamic_schedule == 1;
+}
+
 int max_pair_clusters(const void* kern, int smem_bytes) {
   // how many 2-CTA clusters of this kernel the device can hold at once
   cudaLaunchConfig_t cfg = {};
@@ -1179,7 +1261,16 @@ cudaError_t launch_pair(const GemmArgs& g) {
   const int tiles = ((g.M + 2 * kBM - 1) / (2 * kBM)) * ((g.N + C::kBN - 1) / C::kBN);
   int clusters = tiles < clusters_max ? tiles : clusters_max;
   SplitParams kp;
-  {
+  // counters[0] hands out work items; the rest are the split tiles' arrival counters
+  float* ws = nullptr;
+  int* counters = nullptr;
+  const bool have_ws = split_workspace(0, 1, g.stream, &ws, &counters) == cudaSuccess;
+  int n_counters = 0;
+  if (have_ws && dynamic_schedule_enabled() && tiles > clusters_max) {
+    kp.tile_counter = counters;
+    n_counters = 1;
+  }
+  if (have_ws) {
     // same tail treatment as the single-CTA kernel, counted in clusters
     const int base = clusters_max;
     const int num_kb = (g.K + kBK - 1) / kBK;
@@ -1190,23 +1281,20 @@ cudaError_t launch_pair(const GemmArgs& g) {
       while (parts > 1 && ((num_kb + parts - 1) / parts < 8 ||
                            (parts - 1) * ((num_kb + parts - 1) / parts) >= num_kb))
         --parts;
-      if (parts > 1) {
-        const size_t ws_bytes = static_cast<size_t>(rem) * parts * 2 * kBM * C::kBN * sizeof(float);
-        float* ws = nullptr;
-        int* counters = nullptr;
-        if (split_workspace(ws_bytes, rem * 8, g.stream, &ws, &counters) == cudaSuccess) {
-          kp.full = tiles - rem;
-          kp.parts = parts;
-          kp.kb_per = (num_kb + parts - 1) / parts;
-          kp.items = kp.full + rem * parts;
-          kp.workspace = ws;
-          kp.counters = counters;
-          cudaMemsetAsync(counters, 0, sizeof(int) * rem * 8, g.stream);
-          clusters = kp.items < base ? kp.items : base;
-        }
+      const size_t ws_bytes = static_cast<size_t>(rem) * parts * 2 * kBM * C::kBN * sizeof(float);
+      if (parts > 1 && ws_bytes <= kSplitWsBytes && 1 + rem * 8 <= kSplitCounters) {
+        kp.full = tiles - rem;
+        kp.parts = parts;
+        kp.kb_per = (num_kb + parts - 1) / parts;
+        kp.items = kp.full + rem * parts;
+        kp.workspace = ws;
+        kp.counters = counters + 1;
+        n_counters = 1 + rem * 8;
+        clusters = kp.items < base ? kp.items : base;
       }
     }
   }
+  if (n_counters > 0) cudaMemsetAsync(counters, 0, sizeof(int) * n_counters, g.stream);
   kern<<<2 * clusters, kThreads, C::kSmemBytes, g.stream>>>(ta, tb, static_cast<OutT*>(g.d), g.M, g.N, g.K,
                                                             g.ldd, g.accumulate ? 1 : 0, g.status, kp);
   return cudaGetLastError();
@@ -1273,6 +1361,12 @@ cudaError_t wait_flags(const int* flags, int n, int epoch, int* status, cudaStre
   if (n > 32) return cudaErrorInvalidValue;
   wait_flags_kernel<<<1, 32, 0, stream>>>(flags, n, epoch, status);
   return cudaGetLastError();
+}
+
+void gemm_set_dynamic_schedule(bool on, bool force) {
+  (void)dynamic_schedule_enabled();   // reads the environment once
+  if (g_dynamic_forced && !force) return;
+  g_dynamic_schedule = on ? 1 : 0;
 }
 
 int gemm_pick_bn(int M, int N) {

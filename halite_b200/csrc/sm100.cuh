@@ -26,6 +26,7 @@ enum WaitCode : int {
   kTimeoutTmemEmpty = 4,
   kTimeoutPeerFlag = 5,
   kTimeoutStore = 6,
+  kTimeoutSchedule = 7,
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -205,6 +206,9 @@ __device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 // arrive on an mbarrier that may live in the other CTA (address from `mapa_shared`)
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {

@@ -12,6 +12,7 @@ import json
 
 import torch
 
+from halite_b200 import ops
 from halite_b200.ops.linear import gemm
 
 
@@ -42,6 +43,8 @@ def main():
     ap.add_argument("--layers", default="", help="comma list of layer names to run (default: all)")
     ap.add_argument("--cases", default="", help="comma list among fwd,dgrad,wgrad_f32 (default: all)")
     ap.add_argument("--no-cublas", action="store_true", help="time only this package's kernel")
+    ap.add_argument("--compare-schedules", action="store_true",
+                    help="time the CTA-pair kernel with dynamic and with fixed work shares, back to back")
     ap.add_argument("--block-n", default="0",
                     help="comma list of tiles to time: 64 / 128 / 256 (one CTA per tile), 512 (CTA pair, 256 x 256), "
                          "0 = the launcher's choice")
@@ -83,10 +86,15 @@ def main():
             if want_cases and case not in want_cases:
                 continue
             t_lib = float("nan") if args.no_cublas else _time(lib, args.iters, flush)
-            for bn in block_ns:
+            variants = [(bn, None) for bn in block_ns]
+            if args.compare_schedules:
+                variants = [(512, True), (512, False)]
+            for bn, dyn in variants:
+                if dyn is not None:
+                    ops.ext().gemm_set_dynamic_schedule(dyn, True)
                 t_ours = _time(cases_for(bn)[case], args.iters, flush)
                 print(json.dumps({"layer": name, "case": case, "M_N_K": [T, n, k] if case == "fwd" else None,
-                                  "block_n": bn, "ours_ms": round(t_ours, 4), "cublas_ms": round(t_lib, 4),
+                                  "block_n": bn, "dynamic": dyn, "ours_ms": round(t_ours, 4), "cublas_ms": round(t_lib, 4),
                                   "ours_tflops": round(flops / t_ours / 1e9, 1),
                                   "cublas_tflops": round(flops / t_lib / 1e9, 1),
                                   "ratio": round(t_lib / t_ours, 3)}), flush=True)

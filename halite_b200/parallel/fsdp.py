@@ -347,6 +347,15 @@ def apply_fsdp(model, mesh=None, param_dtype=torch.bfloat16, reduce_dtype=torch.
             else torch.device("cpu")
     device = torch.device(device)
     comm_stream = torch.cuda.Stream(device) if device.type == "cuda" else None
+    if device.type == "cuda":
+        # collectives will run beside the GEMMs and hold some SMs: let the GEMM hand its tiles
+        # out through a counter so that clusters which start late take fewer tiles
+        n_ranks = (dist.get_world_size(shard_group) if shard_group is not None else 1) * \
+            (dist.get_world_size(replicate_group) if replicate_group is not None else 1)
+        if n_ranks > 1:
+            from halite_b200 import ops
+
+            ops.ext().gemm_set_dynamic_schedule(True)
 
     units = []
     taken: set[int] = set()

@@ -112,6 +112,30 @@ def test_gemm_pair_kernel_waves_and_split_tail(C, shape):
     assert rel_err(dgrad, ref) < 6e-3
 
 
+def test_gemm_pair_kernel_dynamic_schedule_matches_fixed_shares(C):
+    """Work items handed out through the counter give the same bits as fixed shares (many waves,
+    K-sliced tail included), launch after launch."""
+    from halite_b200 import ops
+    from halite_b200.ops import gemm
+
+    torch.manual_seed(5)
+    A = torch.randn(2048, 5120, device="cuda", dtype=torch.bfloat16)      # [K, M]
+    B = torch.randn(2048, 3072, device="cuda", dtype=torch.bfloat16)      # [K, N]: 240 tiles, split tail
+    X = torch.randn(8192, 1024, device="cuda", dtype=torch.bfloat16)
+    W = torch.randn(4096, 1024, device="cuda", dtype=torch.bfloat16)      # 512 tiles
+    ext = ops.ext()
+    try:
+        ext.gemm_set_dynamic_schedule(False, True)
+        fixed = (gemm(A, B, a_mn=True, b_mn=True, out_dtype=torch.float32, block_n=512), gemm(X, W, block_n=512))
+        ext.gemm_set_dynamic_schedule(True, True)
+        for _ in range(3):
+            dyn = (gemm(A, B, a_mn=True, b_mn=True, out_dtype=torch.float32, block_n=512), gemm(X, W, block_n=512))
+            assert torch.equal(dyn[0], fixed[0]) and torch.equal(dyn[1], fixed[1])
+    finally:
+        ext.gemm_set_dynamic_schedule(False, True)
+    assert rel_err(fixed[1], X.float() @ W.float().t()) < 6e-3
+
+
 def test_linear_autograd_matches_torch(C):
     from halite_b200 import ops
 
