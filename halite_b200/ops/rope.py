@@ -57,31 +57,35 @@ def apply_rope_reference(x, cos, sin, positions, interleaved: bool):
 
 
 class _RopeFn(torch.autograd.Function):
-    """Rotates q and k in place (the projections' outputs are not needed un-rotated)."""
+    """Out-of-place rotation of one [.., H, D] tensor (possibly a strided slice of a fused
+    projection output) into a packed result; the backward pass rotates the gradient back."""
 
     @staticmethod
-    def forward(ctx, q, k, cos, sin, positions, interleaved):
+    def forward(ctx, x, cos, sin, pos, interleaved):
         C = ops.ext()
-        rot = cos.shape[-1] * 2
-        pos = positions.contiguous()
-        C.rope_(q, cos, sin, pos, rot, interleaved, False)
-        C.rope_(k, cos, sin, pos, rot, interleaved, False)
+        out = torch.empty(x.shape, device=x.device, dtype=x.dtype)
+        C.rope_copy(_collapsible(x), out, cos, sin, pos, cos.shape[-1] * 2, interleaved, False)
         ctx.save_for_backward(cos, sin, pos)
         ctx.interleaved = interleaved
-        ctx.mark_dirty(q, k)
-        return q, k
+        return out
 
     @staticmethod
-    def backward(ctx, dq, dk):
+    def backward(ctx, dx):
         cos, sin, pos = ctx.saved_tensors
         C = ops.ext()
-        rot = cos.shape[-1] * 2
-        # incoming gradients must not be modified in place: rotate packed copies
-        dq = dq.clone(memory_format=torch.contiguous_format)
-        dk = dk.clone(memory_format=torch.contiguous_format)
-        C.rope_(dq, cos, sin, pos, rot, ctx.interleaved, True)
-        C.rope_(dk, cos, sin, pos, rot, ctx.interleaved, True)
-        return dq, dk, None, None, None, None
+        out = torch.empty(dx.shape, device=dx.device, dtype=dx.dtype)
+        C.rope_copy(_collapsible(dx), out, cos, sin, pos, cos.shape[-1] * 2, ctx.interleaved, True)
+        return out, None, None, None, None
+
+
+def _collapsible(t):
+    """`t` itself when its heads are packed and its leading dims fold into one token stride."""
+    if not _packed(t):
+        return t.contiguous()
+    for d in range(t.dim() - 4, -1, -1):
+        if t.shape[d] != 1 and t.stride(d) != t.stride(d + 1) * t.shape[d + 1]:
+            return t.contiguous()
+    return t
 
 
 def _packed(t):
@@ -91,17 +95,23 @@ def _packed(t):
 def apply_rope(q, k, cos, sin, positions, interleaved: bool):
     """Rotate q [.., Hq, D] and k [.., Hk, D] by the table rows at `positions` (one per token).
 
-    The sm_100a path works in place on views (e.g. slices of a fused QKV projection output).
+    On sm_100a: out of place when a gradient is needed, else in place on the views (e.g. slices of
+    a fused QKV projection output).
     """
     if ops.use_sm100(q) and cos.dtype == torch.float32 and cos.is_cuda:
         ntok = q.numel() // (q.shape[-1] * q.shape[-2])
         pos = positions
         if pos.numel() != ntok:
             pos = pos.expand(q.shape[:-2]).contiguous()
-        if not _packed(q):
-            q = q.contiguous()
-        if not _packed(k):
-            k = k.contiguous()
-        return _RopeFn.apply(q, k, cos, sin, pos.reshape(-1), interleaved)
+        pos = pos.reshape(-1).contiguous()
+        if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad):
+            return (_RopeFn.apply(q, cos, sin, pos, interleaved), _RopeFn.apply(k, cos, sin, pos, interleaved))
+        # nothing to differentiate: rotate in place (on packed copies when the views are not packed)
+        q, k = _collapsible(q), _collapsible(k)
+        C = ops.ext()
+        rot = cos.shape[-1] * 2
+        C.rope_(q, cos, sin, pos, rot, interleaved, False)
+        C.rope_(k, cos, sin, pos, rot, interleaved, False)
+        return q, k
     return (apply_rope_reference(q, cos, sin, positions, interleaved),
             apply_rope_reference(k, cos, sin, positions, interleaved))

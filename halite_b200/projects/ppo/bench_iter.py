@@ -105,6 +105,7 @@ def main(argv=None):
     from halite_b200.projects.common.rollout import Handler, RewardRegistry, Rollout, RolloutGenerator
     from halite_b200.projects.ppo.model import RewardModelScorer, ScalarHead, UnpaddedModel, ValueModel
     from halite_b200.projects.ppo.trainer import KLPenalty, PPOTrainer, compute_ppo_advantage
+    from halite_b200.projects.ppo.train import clean_memory
     from halite_b200.projects.ppo.variants import PPOActorLoss
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -156,7 +157,7 @@ def main(argv=None):
                     n_layers=n_layers, context_len=args.prompt_len + args.new_tokens + 16, device=dev_type,
                     gpu_id=pdims.local_rank, kv_cache_dtype=infer_dtype, vocab_size=mc.vocab_size,
                     memory_fraction_static=0.5, distributed=False),
-        ServerConfig())
+        ServerConfig(max_total_tokens=int(args.prompts * (args.prompt_len + args.new_tokens + 32) * 1.25)))
     generator = RolloutGenerator(engine, RewardRegistry(
         Handler("reward_model", RewardModelScorer(reward_model, args.microbatch, device),
                 args=("input_ids", "output_ids"))))
@@ -182,11 +183,13 @@ def main(argv=None):
 
     def iteration(tag):
         with timer.span("weight_sync"):
+            clean_memory()
             generator.initialize()
             generator.load_state_dict(actor.state_dict())
         with timer.span("rollout_and_reward_model"):
             rollouts = generator.generate(make_prompts(tag))
             generator.cleanup()
+            clean_memory()
         with timer.span("logprobs_values_gae"):
             rb = trainer.compute_advantage(rollouts)
         n_tokens = sum(len(r.output_ids) for r in rollouts)

@@ -193,6 +193,37 @@ def test_rmsnorm(C, dim, residual):
 
 
 @pytest.mark.parametrize("interleaved", [True, False])
+def test_rope_on_slices_of_a_fused_projection(C, interleaved):
+    """q and k as strided views of one [tokens, (H + 2 Hk) D] tensor that needs a gradient, with a
+    partial rotation (rot_dim < head_dim): the case of every non-packed attention path."""
+    from halite_b200 import ops
+    from halite_b200.ops.rope import apply_rope_reference, rope_tables
+
+    torch.manual_seed(6)
+    T, H, Hk, D, rot = 300, 6, 2, 64, 32
+    inv = 1.0 / (10000 ** (torch.arange(0, rot, 2).float() / rot))
+    cos, sin = rope_tables(inv, 256, "cuda")
+    pos = torch.randint(0, 256, (1, T), device="cuda")
+    qkv = torch.randn(1, T, (H + 2 * Hk) * D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+
+    def run(fn, src):
+        q = src[..., : H * D].unflatten(-1, (H, D))
+        k = src[..., H * D:(H + Hk) * D].unflatten(-1, (Hk, D))
+        v = src[..., (H + Hk) * D:]
+        q2, k2 = fn(q, k)
+        return (q2.float().square().sum() + (k2.float() * 0.5).sum() + v.float().sum()), q2, k2
+
+    loss, q2, k2 = run(lambda q, k: ops.apply_rope(q, k, cos, sin, pos, interleaved), qkv * 1.0)
+    loss.backward()
+    ref = qkv.detach().float().requires_grad_(True)
+    loss_r, q3, k3 = run(lambda q, k: (apply_rope_reference(q, cos, sin, pos, interleaved),
+                                       apply_rope_reference(k, cos, sin, pos, interleaved)), ref)
+    loss_r.backward()
+    assert rel_err(q2, q3) < 1e-2 and rel_err(k2, k3) < 1e-2
+    assert rel_err(qkv.grad, ref.grad) < 2e-2
+
+
+@pytest.mark.parametrize("interleaved", [True, False])
 def test_rope_forward_backward(C, interleaved):
     from halite_b200 import ops
     from halite_b200.ops.rope import apply_rope_reference, rope_tables

@@ -66,3 +66,51 @@ def test_loss_decreases_on_fixed_batch(zoo):
                                clip_grad_norm=1.0, calc_loss_in_model=True)
         losses.append(out["loss"].item())
     assert losses[-1] < losses[0] - 0.5, losses
+
+
+def test_packed_varlen_path_matches_reference_path(zoo, monkeypatch):
+    """Padding-free forward/backward (what the PPO trainer runs): kernels against the PyTorch
+    reference path of the same weights, with the fused-residual block variant too."""
+    from halite_b200.models.attention import build_unpad_params, unpad_input
+
+    dev = torch.device("cuda", 0)
+    for fused in (False, True):
+        from halite_b200.conf import instantiate
+        from halite_b200.parallel import ParallelDims, parallelize
+        from tests.conftest import tiny_llama_conf
+
+        cfg = tiny_llama_conf(zoo)
+        if fused:
+            cfg = zoo.use_fused_residual(cfg)
+        torch.manual_seed(0)
+        with torch.device("meta"):
+            model = instantiate(cfg)
+        pd = ParallelDims(dp_shard=1, world_size=1)
+        pd.build_mesh("cuda")
+        model = parallelize(model, pd, pd, param_dtype="bfloat16", device=dev)
+        model.init_weights(dev)
+        mask = torch.ones(3, 96, dtype=torch.int64, device=dev)
+        mask[0, :17] = 0
+        mask[2, :40] = 0                     # left padding, as in rollout batches
+        tokens = torch.randint(0, 1024, (3, 96), device=dev)
+        params = build_unpad_params(mask)
+        ids = unpad_input(tokens.unsqueeze(-1), params).squeeze(-1)
+        pos = unpad_input((mask.cumsum(1) - 1).clamp(min=0).unsqueeze(-1), params).squeeze(-1)
+
+        def run():
+            out = model(ids, position_ids=pos, unpad_params=params)
+            loss = out.logits.float().log_softmax(-1)[..., :7].sum() / ids.numel()
+            loss.backward()
+            model._hb_fsdp.finish_backward()
+            grads = [u.full_grad.clone() for u in model._hb_fsdp.units]
+            for u in model._hb_fsdp.units:
+                u._written.clear()
+            return out.logits.detach().float(), grads
+
+        logits, grads = run()
+        monkeypatch.setenv("HALITE_B200_FORCE_REFERENCE", "1")
+        logits_r, grads_r = run()
+        monkeypatch.delenv("HALITE_B200_FORCE_REFERENCE")
+        assert (logits - logits_r).abs().max() < 0.15
+        for g, r in zip(grads, grads_r):
+            assert (g - r).norm() / r.norm().clamp(min=1e-6) < 5e-2
