@@ -15,9 +15,11 @@ def _full(t):
     return t
 
 
-def reshard_state_dict(source, target, device=None, dtype=None, tp_rank=0, tp_size=1, tp_plan=None):
+def reshard_state_dict(source, target, device=None, dtype=None, tp_rank=0, tp_size=1, tp_plan=None,
+                       in_place=False):
     """Returns {key: tensor} for every key of `target`. `tp_plan` maps key -> ("shard", dim)
-    for tensors the inference model holds a 1/tp_size slice of."""
+    for tensors the inference model holds a 1/tp_size slice of. With `in_place` the values are
+    copied into `target`'s own tensors (which keep their addresses) and `target` is returned."""
     out = {}
     for key, ref in target.items():
         src_key = key
@@ -34,6 +36,13 @@ def reshard_state_dict(source, target, device=None, dtype=None, tp_rank=0, tp_si
             if kind == "shard":
                 n = t.shape[dim] // tp_size
                 t = t.narrow(dim, tp_rank * n, n)
+        if in_place:
+            if tuple(t.shape) != tuple(ref.shape):
+                raise ValueError(f"shape mismatch for {key}: {tuple(t.shape)} vs {tuple(ref.shape)}")
+            with torch.no_grad():
+                ref.copy_(t)
+            out[key] = ref
+            continue
         want_dtype = dtype or (ref.dtype if ref.dtype.is_floating_point and not ref.is_meta else t.dtype)
         if ref.is_meta:
             want_dtype = dtype or t.dtype

@@ -34,7 +34,10 @@ class InferenceEngine:
     def initialize(self):
         if self.initialized:
             return
-        self.model_runner.initialize()
+        if self.model_runner.kv_pool is None:
+            self.model_runner.initialize()
+        else:                              # kept resident: every page and request slot is free again
+            self.model_runner.reset_pools()
         self.scheduler.initialize()
         self.initialized = True
 
@@ -42,7 +45,8 @@ class InferenceEngine:
         if not self.initialized:
             return
         self.scheduler.cleanup()
-        self.model_runner.cleanup()
+        if not self.server_config.keep_resident:
+            self.model_runner.cleanup()
         self.initialized = False
 
     def load_state_dict(self, state_dict, assign=True):

@@ -98,6 +98,12 @@ class ModelRunner:
         b = max_batch or min(self.max_running_requests, 4096)
         return b * q_heads * max_splits * (head_dim + 2)
 
+    def reset_pools(self):
+        """Forget every request and page (pools and graphs stay where they are)."""
+        self.kv_pool.clear()
+        self.req_pool.clear()
+        self.req_pool.free_slots = list(range(self.max_requests))
+
     def cleanup(self):
         """Give the device memory back (weights and pools) so training can use it."""
         self.model.to("meta")
@@ -112,6 +118,11 @@ class ModelRunner:
     def load_state_dict(self, state_dict, assign=True):
         from halite_b200.distributed.state_dict import reshard_state_dict
 
+        resident = self.server_config.keep_resident and not any(p.is_meta for p in self.model.parameters())
+        if resident:
+            # same storage, new values: captured graphs and tensor maps stay valid
+            reshard_state_dict(state_dict, self.model.state_dict(), device=self.device, in_place=True)
+            return
         self.model.to("meta")
         target = self.model.state_dict()
         sd = reshard_state_dict(state_dict, target, device=self.device)

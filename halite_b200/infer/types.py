@@ -107,6 +107,10 @@ class ServerConfig:
     decode_steps_ahead: int = 8              # decode steps launched before the host reads tokens
     disable_radix_cache: bool = False
     radix_backend: str = "auto"            # "native" (C++ tree), "python", or "auto"
+    # cleanup() keeps weights, KV pool and captured CUDA graphs on the device and load_state_dict()
+    # copies new weights into place (same addresses), so rollouts after the first need no
+    # allocation and no graph capture; for jobs where training and the engine fit side by side
+    keep_resident: bool = False
     seed: int = 0
 
 

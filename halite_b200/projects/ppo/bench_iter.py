@@ -94,6 +94,9 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=1)
     ap.add_argument("--layers", type=int, default=0, help="keep only the first N blocks (0 = all)")
     ap.add_argument("--kl-coef", type=float, default=0.05)
+    ap.add_argument("--release-engine", action="store_true",
+                    help="free the engine's weights, KV pool and CUDA graphs after every rollout (for jobs where "
+                         "training needs that memory) instead of keeping them resident")
     ap.add_argument("--device", default=None)
     args = ap.parse_args(argv)
 
@@ -157,7 +160,8 @@ def main(argv=None):
                     n_layers=n_layers, context_len=args.prompt_len + args.new_tokens + 16, device=dev_type,
                     gpu_id=pdims.local_rank, kv_cache_dtype=infer_dtype, vocab_size=mc.vocab_size,
                     memory_fraction_static=0.5, distributed=False),
-        ServerConfig(max_total_tokens=int(args.prompts * (args.prompt_len + args.new_tokens + 32) * 1.25)))
+        ServerConfig(max_total_tokens=int(args.prompts * (args.prompt_len + args.new_tokens + 32) * 1.25),
+                     use_cudagraph=dev_type == "cuda", decode_steps_ahead=8, keep_resident=not args.release_engine))
     generator = RolloutGenerator(engine, RewardRegistry(
         Handler("reward_model", RewardModelScorer(reward_model, args.microbatch, device),
                 args=("input_ids", "output_ids"))))

@@ -128,6 +128,32 @@ def test_stop_token_and_lifecycle(zoo):
     assert again.output_ids == base.output_ids
 
 
+def test_resident_engine_takes_new_weights_in_place(zoo):
+    """`keep_resident`: cleanup() leaves weights and pools where they are, load_state_dict() copies
+    new values into the same storage, and the next rollout follows the new weights."""
+    model, eng = build(zoo, ServerConfig(max_total_tokens=4096, keep_resident=True))
+    prompts = torch.randint(0, 1024, (4, 12), generator=torch.Generator().manual_seed(1)).tolist()
+    reqs = lambda: [InferenceRequest(i, p, {"max_new_tokens": 8, "top_k": 1}) for i, p in enumerate(prompts)]
+    first = eng.infer_batch(reqs())
+    pool, weight = eng.model_runner.kv_pool, next(eng.model_runner.model.parameters())
+    ptr = weight.data_ptr()
+    eng.cleanup()
+    assert eng.model_runner.kv_pool is pool and not weight.is_meta
+    with torch.no_grad():
+        for p in model.parameters():
+            p.add_(0.05 * torch.randn_like(p))
+    eng.initialize()
+    eng.load_state_dict(model.state_dict())
+    assert next(eng.model_runner.model.parameters()).data_ptr() == ptr
+    assert eng.model_runner.kv_pool.available_pages() == pool.num_pages if hasattr(pool, "num_pages") else True
+    second = eng.infer_batch(reqs())
+    for r in second:
+        want, lp = dense_check(model, r)
+        assert want == r.output_ids[0]
+        assert (lp - torch.tensor(r.output_logprobs[0])).abs().max() < 1e-4
+    assert any(a.output_ids != b.output_ids for a, b in zip(first, second))
+
+
 def test_sampler_distribution_and_filters():
     from halite_b200.infer.batch import BatchSamplingParams
     from halite_b200.infer.sampler import Sampler
