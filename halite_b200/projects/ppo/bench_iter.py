@@ -76,8 +76,11 @@ class PhaseTimer:
         if self.cuda:
             torch.cuda.synchronize()
         out = {}
+        self.each = {}
         for name, a, b in self.spans:
-            out[name] = out.get(name, 0.0) + (a.elapsed_time(b) if b is not None else a)
+            ms = a.elapsed_time(b) if b is not None else a
+            out[name] = out.get(name, 0.0) + ms
+            self.each.setdefault(name, []).append(round(ms / 1e3, 4))
         self.spans = []
         return out
 
@@ -94,9 +97,9 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=1)
     ap.add_argument("--layers", type=int, default=0, help="keep only the first N blocks (0 = all)")
     ap.add_argument("--kl-coef", type=float, default=0.05)
-    ap.add_argument("--release-engine", action="store_true",
-                    help="free the engine's weights, KV pool and CUDA graphs after every rollout (for jobs where "
-                         "training needs that memory) instead of keeping them resident")
+    ap.add_argument("--resident-engine", action="store_true",
+                    help="keep the engine's weights, KV pool and CUDA graphs on the device between rollouts "
+                         "instead of freeing them for the training phases")
     ap.add_argument("--device", default=None)
     args = ap.parse_args(argv)
 
@@ -161,10 +164,16 @@ def main(argv=None):
                     gpu_id=pdims.local_rank, kv_cache_dtype=infer_dtype, vocab_size=mc.vocab_size,
                     memory_fraction_static=0.5, distributed=False),
         ServerConfig(max_total_tokens=int(args.prompts * (args.prompt_len + args.new_tokens + 32) * 1.25),
-                     use_cudagraph=dev_type == "cuda", decode_steps_ahead=8, keep_resident=not args.release_engine))
+                     use_cudagraph=dev_type == "cuda", decode_steps_ahead=8, keep_resident=args.resident_engine))
+    timer = PhaseTimer(device)
+    scorer = RewardModelScorer(reward_model, args.microbatch, device)
+
+    def timed_scorer(input_ids, output_ids):
+        with timer.span("reward_model"):
+            return scorer(input_ids, output_ids)
+
     generator = RolloutGenerator(engine, RewardRegistry(
-        Handler("reward_model", RewardModelScorer(reward_model, args.microbatch, device),
-                args=("input_ids", "output_ids"))))
+        Handler("reward_model", timed_scorer, args=("input_ids", "output_ids"))))
 
     trainer = PPOTrainer(
         actor=UnpaddedModel(actor), ref=UnpaddedModel(ref), critic=critic, device=device,
@@ -177,7 +186,6 @@ def main(argv=None):
     head_opt = torch.optim.AdamW(value_head.parameters(), lr=1e-5)
 
     rng = random.Random(1234 + rank)
-    timer = PhaseTimer(device)
 
     def make_prompts(tag):
         return [Rollout(id=f"{tag}-{rank}-{i}", input_ids=[rng.randrange(mc.vocab_size) for _ in range(args.prompt_len)],
@@ -192,6 +200,7 @@ def main(argv=None):
             generator.load_state_dict(actor.state_dict())
         with timer.span("rollout_and_reward_model"):
             rollouts = generator.generate(make_prompts(tag))
+        with timer.span("engine_release"):
             generator.cleanup()
             clean_memory()
         with timer.span("logprobs_values_gae"):
@@ -256,7 +265,12 @@ def main(argv=None):
            "minibatches": args.minibatches, "microbatch": args.microbatch, "layers": n_layers,
            "sampled_tokens_per_iteration_per_rank": tokens // args.iters,
            "phases_s_per_iteration": {k: round(v / 1e3 / args.iters, 4) for k, v in zip(sorted(phases), stat[1:])},
+           "rollout_s_each_iteration_rank0": timer.each.get("rollout_and_reward_model"),
            "dtype": dtype, "data": "synthetic uniform-random prompts, random-init weights"}
+    try:
+        out["engine_stats"] = {k: (round(v, 3) if isinstance(v, float) else v) for k, v in dict(engine.stats).items()}
+    except Exception:  # noqa: BLE001
+        pass
     if dev_type == "cuda":
         out["peak_mem_gib"] = round(torch.cuda.max_memory_allocated() / 2 ** 30, 2)
     if rank == 0:

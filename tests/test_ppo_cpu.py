@@ -227,5 +227,5 @@ def test_ppo_iteration_benchmark_runs_four_models():
     out = bench_iter.main(["--conf", conf, "--prompts", "8", "--prompt-len", "12", "--new-tokens", "10",
                            "--microbatch", "2", "--iters", "1", "--warmup", "0", "--device", "cpu"])
     assert out["sampled_tokens_per_iteration_per_rank"] == 80 and out["value"] > 0
-    assert set(out["phases_s_per_iteration"]) == {"weight_sync", "rollout_and_reward_model",
-                                                  "logprobs_values_gae", "update"}
+    assert set(out["phases_s_per_iteration"]) == {"weight_sync", "rollout_and_reward_model", "reward_model",
+                                                  "engine_release", "logprobs_values_gae", "update"}
