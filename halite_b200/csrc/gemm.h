@@ -8,6 +8,7 @@
 namespace hb {
 
 constexpr int kMaxPeers = 8;
+constexpr int kClusterSplitBlockN = 1064;   // GemmArgs::block_n value that forces the cluster split-K kernel (64-column tiles)
 constexpr int kPairBlockN = 512;   // GemmArgs::block_n value that forces the CTA-pair (cta_group::2) kernel
 
 // Side job that a GEMM launch can carry: a few CTAs copy `n_chunks` equal chunks (each from a

@@ -958,6 +958,200 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
   }
 }
 
+// ------------------------------------------------------------------ skinny GEMM: K split over a cluster
+// Decode-time projections have at most 128 rows and a handful of 64-column tiles, so a launch of
+// one CTA per tile leaves most SMs idle while each busy one streams its whole K range through a
+// single TMA queue. Here a cluster of S CTAs (2..8) shares one 128 x 64 tile: CTA r accumulates
+// k-blocks [r * per, (r + 1) * per) in its own tensor memory, the CTAs with r > 0 then write
+// their fp32 partial into CTA 0's shared memory (distributed shared memory stores), the cluster
+// meets at a barrier and CTA 0 adds the S partials in rank order and writes the tile. No global
+// workspace, counters or second kernel. A, B K-major.
+struct KSplitCfg {
+  static constexpr int kBN = 64;
+  static constexpr int kStages = 4;
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = kBN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;              // 24 KB
+  static constexpr int kMaxSplit = 8;
+  static constexpr int kQuarterBytes = 32 * kBN * 4;                 // 32 rows of one CTA's fp32 tile: 8 KB
+  static constexpr int kPartialArea = 12 * kQuarterBytes;            // room for the partials of ranks 1..S-1
+  static constexpr int kSmemBytes = kStages * kStageBytes + kPartialArea + 1024;
+  static constexpr int kTmemCols = 64;
+};
+
+// Byte offset inside a partial (only the row quarters below M are stored) of the 16-byte piece `i` (0..7) of lane `lane`'s 32-float
+// chunk `c` of lane quarter `q`; pieces are XOR-swizzled so that neither the remote writer nor
+// the local reader has bank conflicts.
+__device__ __forceinline__ uint32_t partial_offset(int q, int c, int lane, int i) {
+  return static_cast<uint32_t>(((q * (KSplitCfg::kBN / 32) + c) * 32 + lane) * 128 + ((i ^ (lane & 7)) << 4));
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_ksplit_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                        OutT* __restrict__ D, int M, int N, int K, int ldd, int accumulate, int split,
+                        int* __restrict__ status) {
+  using C = KSplitCfg;
+  constexpr int kStages = C::kStages;
+  constexpr int BN = C::kBN;
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kStages];
+  __shared__ __align__(8) uint64_t bar_empty[kStages];
+  __shared__ __align__(8) uint64_t bar_tfull;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t partial_base = smem_base + kStages * C::kStageBytes;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int rank = static_cast<int>(cluster_ctarank());
+  const int tile = static_cast<int>(cluster_id_x());
+
+  const int tiles_n = (N + BN - 1) / BN;
+  const int tm = tile / tiles_n, tn = tile - tm * tiles_n;
+  const int m0 = tm * kBM, n0 = tn * BN;
+  const int num_kb = (K + kBK - 1) / kBK;
+  const int per = (num_kb + split - 1) / split;
+  const int kb_begin = rank * per;
+  const int kb_end = min(num_kb, kb_begin + per);
+  const bool has_work = kb_end > kb_begin;
+  const int quarters = (min(M - m0, kBM) + 31) / 32;                 // row quarters that hold rows of D
+  const uint32_t partial_bytes = static_cast<uint32_t>(quarters) * C::kQuarterBytes;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&bar_tfull), 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32(&tmem_slot), C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ------------------------------------------------------------ producer
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int kb = kb_begin; kb < kb_end; ++kb) {
+      if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1, &abort_flag, status, kTimeoutEmpty)) break;
+      const uint32_t full = smem_u32(&bar_full[stage]);
+      const uint32_t sa = smem_base + stage * C::kStageBytes;
+      mbar_expect_tx(full, C::kStageBytes);
+      tma_load_2d(sa, &tma_a, full, kb * kBK, m0);
+      tma_load_2d(sa + C::kABytes, &tma_b, full, kb * kBK, n0);
+      if (++stage == kStages) {
+        stage = 0;
+        phase ^= 1;
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc = make_idesc_bf16(kBM, BN, false, false);
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int kb = kb_begin; kb < kb_end && ok; ++kb) {
+      ok = mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag, status, kTimeoutFull);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t sa = smem_base + stage * C::kStageBytes;
+      const uint32_t sb = sa + C::kABytes;
+#pragma unroll
+      for (int k = 0; k < kBK / kUK; ++k)
+        umma_bf16(tmem_base, make_smem_desc(sa + k * 32, 0, 1024), make_smem_desc(sb + k * 32, 0, 1024), idesc,
+                  ((kb - kb_begin) | k) != 0);
+      umma_commit(smem_u32(&bar_empty[stage]));
+      if (++stage == kStages) {
+        stage = 0;
+        phase ^= 1;
+      }
+    }
+    if (ok && has_work) umma_commit(smem_u32(&bar_tfull));
+  } else if (warp >= 4 && rank != 0 && has_work) {
+    // ------------------------------------------------------------ partial -> CTA 0's shared memory
+    const int q = warp & 3;
+    bool ok = mbar_wait(smem_u32(&bar_tfull), 0, &abort_flag, status, kTimeoutTmemFull);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok && m0 + q * 32 < M) {     // row quarters past M hold zeros nobody reads
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+      const uint32_t dst = mapa_shared(partial_base + (rank - 1) * partial_bytes, 0);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          st_shared_cluster_v4(dst + partial_offset(q, c, lane, i), v[4 * i], v[4 * i + 1], v[4 * i + 2],
+                               v[4 * i + 3]);
+      }
+    }
+    tc_fence_before();
+  }
+
+  // every partial is in place (or its CTA gave up) before CTA 0 reads them
+  cluster_sync_all();
+
+  if (warp >= 4 && rank == 0 && !abort_flag) {
+    // ------------------------------------------------------------ CTA 0: sum in rank order, write the tile
+    const int q = warp & 3;
+    const bool vec_ok = (ldd % (16 / (int)sizeof(OutT)) == 0) && ((reinterpret_cast<uintptr_t>(D) & 15) == 0);
+    bool ok = mbar_wait(smem_u32(&bar_tfull), 0, &abort_flag, status, kTimeoutTmemFull);
+    ok = __all_sync(0xffffffffu, ok);
+    const int row = m0 + q * 32 + lane;
+    if (ok && m0 + q * 32 < M) {
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + c * 32, v);
+        tmem_ld_wait();
+        for (int p = 1; p < split; ++p) {
+          if (p * per >= num_kb) break;      // that rank had no k-blocks
+          const uint32_t src = partial_base + (p - 1) * partial_bytes;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint4 x = ld_shared_v4(src + partial_offset(q, c, lane, i));
+            v[4 * i] = __float_as_uint(__uint_as_float(v[4 * i]) + __uint_as_float(x.x));
+            v[4 * i + 1] = __float_as_uint(__uint_as_float(v[4 * i + 1]) + __uint_as_float(x.y));
+            v[4 * i + 2] = __float_as_uint(__uint_as_float(v[4 * i + 2]) + __uint_as_float(x.z));
+            v[4 * i + 3] = __float_as_uint(__uint_as_float(v[4 * i + 3]) + __uint_as_float(x.w));
+          }
+        }
+        const int col = n0 + c * 32;
+        if (row < M && col < N)
+          store_chunk<OutT>(D + static_cast<size_t>(row) * ldd + col, v, min(32, N - col), vec_ok,
+                            accumulate != 0);
+      }
+    }
+    tc_fence_before();
+  }
+
+  if (abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
 // ------------------------------------------------------------------ host side
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -1308,6 +1502,83 @@ cudaError_t dispatch_pair(const GemmArgs& g) {
   return launch_pair<true, false, OutT>(g);
 }
 
+template <typename OutT>
+cudaError_t launch_ksplit(const GemmArgs& g, int split) {
+  using C = KSplitCfg;
+  CUtensorMap ta, tb;
+  if (!make_tmap_bf16_2d(&ta, g.a, g.M, g.K, g.lda, kBM, kBK)) return cudaErrorInvalidPitchValue;
+  if (!make_tmap_bf16_2d(&tb, g.b, g.N, g.K, g.ldb, C::kBN, kBK)) return cudaErrorInvalidPitchValue;
+  auto kern = gemm_bf16_ksplit_kernel<OutT>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  (void)cudaGetLastError();
+  const int tiles = ((g.M + kBM - 1) / kBM) * ((g.N + C::kBN - 1) / C::kBN);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(tiles * split, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = g.stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = split;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, ta, tb, static_cast<OutT*>(g.d), g.M, g.N, g.K, g.ldd,
+                            g.accumulate ? 1 : 0, split, g.status);
+}
+
+// How many clusters of `size` CTAs of the split kernel the device holds at once (clusters are
+// placed on whole TPCs inside one GPC, so this is less than SMs / size for most sizes).
+int ksplit_max_clusters(int size) {
+  static int cached[KSplitCfg::kMaxSplit + 1] = {};
+  if (cached[size] == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(sm_count() / size * size, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = KSplitCfg::kSmemBytes;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = size;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    auto kern = gemm_bf16_ksplit_kernel<__nv_bfloat16>;
+    int n = 0;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, KSplitCfg::kSmemBytes) !=
+            cudaSuccess ||
+        cudaOccupancyMaxActiveClusters(&n, reinterpret_cast<const void*>(kern), &cfg) != cudaSuccess || n <= 0) {
+      (void)cudaGetLastError();
+      n = sm_count() / size / 2;   // conservative guess
+    }
+    cached[size] = n;
+  }
+  return cached[size];
+}
+
+// K split for skinny K-major problems: the largest power-of-two cluster whose clusters are all
+// resident at once (one wave), as long as every CTA keeps at least four k-blocks and the partials
+// fit CTA 0's shared memory. Odd sizes waste the second SM of a TPC and measured slower.
+int ksplit_factor(const GemmArgs& g) {
+  if (g.a_mn_major || g.b_mn_major || g.M > kBM) return 1;
+  const int tiles = (g.N + KSplitCfg::kBN - 1) / KSplitCfg::kBN;
+  const int num_kb = (g.K + kBK - 1) / kBK;
+  const int quarters = (g.M + 31) / 32;
+  const int fit = 1 + KSplitCfg::kPartialArea / (quarters * KSplitCfg::kQuarterBytes);
+  for (int split = KSplitCfg::kMaxSplit; split >= 2; split /= 2) {
+    if (split > fit || split > num_kb / 4) continue;
+    if ((split - 1) * ((num_kb + split - 1) / split) >= num_kb) continue;   // a rank without k-blocks
+    if (tiles <= ksplit_max_clusters(split)) return split;
+  }
+  return 1;
+}
+
 // The pair kernel is chosen for plain GEMMs that give every SM pair at least one 256 x 256 tile.
 // HB_GEMM_PAIR=0 turns it off.
 bool pair_kernel_enabled() {
@@ -1396,6 +1667,11 @@ cudaError_t gemm_bf16(const GemmArgs& g) {
     pair = pair_tiles >= sm_count() / 2;
   }
   if (pair) return g.out_f32 ? dispatch_pair<float>(g) : dispatch_pair<__nv_bfloat16>(g);
+  if (g.block_n == kClusterSplitBlockN || (g.block_n == 0 && plain)) {
+    const int split = plain ? ksplit_factor(g) : 1;
+    if (g.block_n == kClusterSplitBlockN && split < 2) return cudaErrorInvalidValue;
+    if (split >= 2) return g.out_f32 ? launch_ksplit<float>(g, split) : launch_ksplit<__nv_bfloat16>(g, split);
+  }
   const int bn = g.block_n > 0 ? g.block_n : gemm_pick_bn(g.M, g.N);
   if (bn == 256) {
     return g.out_f32 ? dispatch_layout<256, float>(g) : dispatch_layout<256, __nv_bfloat16>(g);

@@ -43,6 +43,8 @@ def main():
     ap.add_argument("--layers", default="", help="comma list of layer names to run (default: all)")
     ap.add_argument("--cases", default="", help="comma list among fwd,dgrad,wgrad_f32 (default: all)")
     ap.add_argument("--no-cublas", action="store_true", help="time only this package's kernel")
+    ap.add_argument("--decode", type=int, default=0, metavar="BATCH",
+                    help="time the forward GEMMs at this many rows (a decode step) instead of the training shapes")
     ap.add_argument("--compare-schedules", action="store_true",
                     help="time the CTA-pair kernel with dynamic and with fixed work shares, back to back")
     ap.add_argument("--block-n", default="0",
@@ -51,7 +53,7 @@ def main():
     args = ap.parse_args()
     dev = "cuda"
     flush = torch.zeros(192 << 20, dtype=torch.uint8, device=dev)       # > 126 MB of L2
-    T = args.tokens
+    T = args.decode or args.tokens
     block_ns = [int(b) for b in args.block_n.split(",")]
     layers = [("qkv", args.dim, args.qkv), ("attn_out", args.dim, args.dim), ("up_gate", args.dim, 2 * args.ff),
               ("down", args.ff, args.dim)]
@@ -83,7 +85,7 @@ def main():
         }
         flops = 2.0 * T * k * n
         for case, lib in lib_cases.items():
-            if want_cases and case not in want_cases:
+            if (want_cases and case not in want_cases) or (args.decode and case != "fwd"):
                 continue
             t_lib = float("nan") if args.no_cublas else _time(lib, args.iters, flush)
             variants = [(bn, None) for bn in block_ns]
