@@ -173,7 +173,11 @@ def test_shipped_experiment_configs_load_and_validate():
 
     root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "configs", "lm")
     expect = {"dense_662m.py": (0.55e9, 0.8e9), "dense_1.7b.py": (1.4e9, 2.0e9), "diff_transformer_383m.py": (0.3e9, 0.5e9),
-              "moe_383m.py": (1.5e9, 5e9), "ngpt_383m.py": (0.3e9, 0.5e9), "scale_383m_soap.py": (0.3e9, 0.5e9)}
+              "moe_383m.py": (1.5e9, 5e9), "ngpt_383m.py": (0.3e9, 0.5e9), "scale_383m_soap.py": (0.3e9, 0.5e9),
+              "dense_scaling.py": (0.3e9, 0.5e9), "diff_transformer_large.py": (0.8e9, 1.1e9),
+              "scaling/scale_383m.py": (0.3e9, 0.5e9), "scaling/scale_large.py": (0.8e9, 1.1e9),
+              "scaling/moe.py": (1.5e9, 5e9), "stacking/base_900m.py": (0.2e9, 0.4e9),
+              "stacking/scratch_900m.py": (0.8e9, 1.0e9)}
     for name, (lo, hi) in expect.items():
         conf = load_config(os.path.join(root, name), schema=LMConfig)
         assert conf.training.train_batch_size == 320 and conf.data.preprocess is not None
@@ -181,3 +185,10 @@ def test_shipped_experiment_configs_load_and_validate():
             model = instantiate(conf.model.model)
         n = sum(p.numel() for p in model.parameters())
         assert lo < n < hi, (name, n)
+    # hyper-parameter driven experiment: overrides of `hparams` reach every dependent value
+    conf = load_config(os.path.join(root, "farseer.py"), "scale_202m", overrides=["hparams.batch_size=32"],
+                       schema=LMConfig)
+    assert conf.training.train_batch_size == 32 and conf.training.max_iter == 8192 * 10 ** 6 // 2048 // 32
+    assert instantiate(conf.output.name)(conf.hparams).startswith("202m@lr-0.00781_batch-32")
+    small = load_config(os.path.join(root, "scaling", "scale_1.py"), schema=LMConfig)
+    assert small.training.train_batch_size == 64
