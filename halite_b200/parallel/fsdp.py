@@ -334,11 +334,15 @@ def _unit_params(module: nn.Module, exclude: set[int]):
 
 
 def apply_fsdp(model, mesh=None, param_dtype=torch.bfloat16, reduce_dtype=torch.float32,
-               reshard_after_forward=False, device=None, blocks_attr="blocks", force_fsdp=False):
+               reshard_after_forward=False, device=None, blocks_attr="blocks", force_fsdp=False,
+               block_iterator=None):
     """Shard `model` over the mesh's data-parallel dimensions. Returns the same module, with
     parameters re-homed into flat unit buffers and `model._hb_fsdp` set.
 
     `mesh` is a `ParallelDims` after `build_mesh()` (or None for a single process).
+    `block_iterator(model)` may yield `(key, block, container)` for models whose blocks live in
+    more than one container (an encoder's blocks followed by the model's own); each yielded block
+    becomes a unit. Without it the units are the entries of `model.<blocks_attr>`.
     """
     shard_group = mesh.group("dp_shard") if mesh is not None else None
     replicate_group = mesh.group("dp_replicate") if mesh is not None else None
@@ -359,17 +363,27 @@ def apply_fsdp(model, mesh=None, param_dtype=torch.bfloat16, reduce_dtype=torch.
 
     units = []
     taken: set[int] = set()
-    blocks = getattr(model, blocks_attr, None)
+    calls_block_hooks = hasattr(model, "block_hooks")     # the model's forward announces each block
     block_units = {}
-    if blocks is not None:
-        for key, block in blocks.items():
-            ps = _unit_params(block, taken)
-            taken.update(id(p) for _, _, p in ps)
-            u = FlatUnit(f"{blocks_attr}.{key}", ps, shard_group, replicate_group, param_dtype,
-                         reduce_dtype, device, comm_stream)
-            units.append(u)
-            block_units[int(key)] = u
-            taken.update(id(p) for p in u.params())   # the re-homed Parameter objects
+    if block_iterator is not None:
+        names = {id(m): n for n, m in model.named_modules()}
+        listed = [(f"{names.get(id(container), blocks_attr)}.{key}", block, None)
+                  for key, block, container in block_iterator(model)]
+        calls_block_hooks = False
+    else:
+        blocks = getattr(model, blocks_attr, None)
+        listed = [(f"{blocks_attr}.{key}", block, int(key)) for key, block in blocks.items()] \
+            if blocks is not None else []
+    for name, block, index in listed:
+        ps = _unit_params(block, taken)
+        if not ps:
+            continue
+        taken.update(id(p) for _, _, p in ps)
+        u = FlatUnit(name, ps, shard_group, replicate_group, param_dtype, reduce_dtype, device, comm_stream)
+        units.append(u)
+        if index is not None:
+            block_units[index] = u
+        taken.update(id(p) for p in u.params())   # the re-homed Parameter objects
     # tied head/embedding weights are one parameter: `_unit_params` de-duplicates by identity
     root_ps = _unit_params(model, taken)
     root = FlatUnit("root", root_ps, shard_group, replicate_group, param_dtype, reduce_dtype, device,
@@ -390,7 +404,9 @@ def apply_fsdp(model, mesh=None, param_dtype=torch.bfloat16, reduce_dtype=torch.
     _install_fused_views(model, units)
 
     def pre_block(i, x):
-        u = block_units[i]
+        u = block_units.get(i)
+        if u is None:
+            return x
         u.pre_forward()
         if torch.is_grad_enabled() and x.requires_grad:
             x = _UnitBoundary.apply(x, u)
@@ -403,6 +419,10 @@ def apply_fsdp(model, mesh=None, param_dtype=torch.bfloat16, reduce_dtype=torch.
 
     def root_pre_forward(module, args, kwargs):
         root.pre_forward()
+        if not calls_block_hooks:
+            # this model's forward does not announce its blocks: every unit must be whole now
+            for u in units:
+                u.pre_forward()
         return None
 
     model.register_forward_pre_hook(root_pre_forward, with_kwargs=True)

@@ -171,3 +171,30 @@ def test_jit_and_diffusion_objectives():
     t = torch.tensor([0.0, 0.8, 1.0]).view(-1, 1, 1, 1)
     assert e.get_c_t(t).flatten().tolist() == pytest.approx([4.0, 4.0, 0.0], abs=1e-5)
     assert torch.isfinite(e.loss(model, x, lab)) and e.generate(model, lab, seed=0).shape == x.shape
+
+
+def test_encoder_jit_on_a_small_vision_encoder_and_its_unit_layout():
+    """Encoder-JiT from its config builder on a tiny SigLIP-style encoder: forward shape, zero
+    output at initialisation (adaLN-Zero head), frozen encoder, and one sharding unit per block
+    of both block lists when wrapped with the block iterator."""
+    from halite_b200.models.models.jit import encoder_jit_block_iterator
+    from halite_b200.parallel import parallelize
+
+    siglip = load_module(os.path.join(ROOT, "configs/models/siglip2/siglip_vision.py"))
+    enc_jit = load_module(os.path.join(ROOT, "configs/models/encoder_jit.py"))
+    encoder = build(zoo.transformer(**siglip.vision_config(32, 2, 2, 64, 16, 4)))
+    wrap = instantiate(enc_jit.encoder_jit(image_size=16, patch_size=4, n_labels=10, dim=32, patch_dim=16, n_heads=2,
+                                           head_dim=16, n_layers=3, intermediate_size=64, in_context_len=2,
+                                           qk_norm=True, cond_start_id=1))
+    model = wrap(encoder)
+    model.init_weights("cpu")
+    model.freeze_encoder()
+    x, lab = torch.randn(2, 3, 16, 16), torch.randint(0, 10, (2,))
+    out = model(x, torch.rand(2), lab)
+    assert out.shape == x.shape and out.abs().max() == 0
+    assert not any(p.requires_grad for p in model.encoder.parameters())
+    model = parallelize(model, param_dtype="float32", reduce_dtype="float32", device="cpu",
+                        block_iterator=encoder_jit_block_iterator)
+    names = [u.name for u in model._hb_fsdp.units]
+    assert names == ["encoder.blocks.0", "encoder.blocks.1", "blocks.0", "blocks.1", "blocks.2", "root"]
+    assert model(x, torch.rand(2), lab).shape == x.shape
