@@ -139,6 +139,13 @@ def run_ours(args):
         e2e_ms = te.max_ms()
     ops.check_status()
 
+    fused_units = [u for u in model._hb_fsdp.units if u.fused is not None]
+    gather_mode = "none (one rank)" if world == 1 else "NCCL all-gather per unit, overlapped"
+    if fused_units:
+        carried = sum(u.fused.launches - u.fused.standalone for u in fused_units)
+        gather_mode = (f"{len(fused_units)} block units: peers' shards copied over NVLink by CTAs inside GEMM launches "
+                       f"({carried} carried, {sum(u.fused.standalone for u in fused_units)} launched alone so far); "
+                       "root unit: NCCL")
     tokens_per_step = seqs * S * world
     value = tokens_per_step * K / (ms / 1e3)
     e2e = tokens_per_step * K / (e2e_ms / 1e3)
@@ -157,7 +164,8 @@ def run_ours(args):
                        "global_batch": seqs * world, "seq_len": S,
                        "parallelism": f"fsdp{world}", "optimizer": "AdamW fp32 master, clip 1.0",
                        "l2": "inputs larger than L2 (activations of 32768 tokens/GPU)",
-                       "attention": "torch SDPA core inside packed-QKV op"},
+                       "attention": "torch SDPA core inside packed-QKV op",
+                       "fsdp_all_gather": gather_mode},
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": e2e_ms / K,
                     "h2d_bytes_per_step": seqs * (S + 1) * 8, "d2h_bytes_per_step": 4},
             "gpu_launches": int(launches),

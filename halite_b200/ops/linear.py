@@ -51,7 +51,9 @@ class _LinearFn(torch.autograd.Function):
         if not _gemm_ready(x2):
             x2 = x2.contiguous()
         w = weight if _gemm_ready(weight) else weight.contiguous()
-        out = gemm(x2, w)
+        # a data-parallel wrapper may hang another unit's parameter gather on this launch
+        carry = getattr(weight, "_hb_carry", None)
+        out = gemm(x2, w, gather=carry() if carry is not None else None)
         if bias is not None:
             out += bias
         ctx.save_for_backward(x2, weight)

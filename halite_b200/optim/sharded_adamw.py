@@ -64,6 +64,9 @@ class ShardedAdamW(torch.optim.Optimizer):
         self.fsdp.finish_backward()
         self.fsdp.wait_reductions()
         self._step += 1
+        for u in self.units:
+            if u.fused is not None:
+                u.fused.wait_readers()     # peers still copying last step's shard finish first
         for u, lo, hi, gi in self._slots:
             g = self.param_groups[self._gidx[gi]]
             ops.fused_adamw_step(
@@ -72,7 +75,7 @@ class ShardedAdamW(torch.optim.Optimizer):
                 g["weight_decay"], self._step, 1.0, self.clip_coef)
         self.clip_coef = None
         for u in self.units:
-            u.start_gather()
+            u.start_gather(epoch=self._step)
 
     # ------------------------------------------------------------------ checkpoint
     def state_dict(self):
@@ -93,7 +96,9 @@ class ShardedAdamW(torch.optim.Optimizer):
             self.exp_avg[id(u)].copy_(state[f"{u.name}.exp_avg"])
             self.exp_avg_sq[id(u)].copy_(state[f"{u.name}.exp_avg_sq"])
             u.param_shard().copy_(u.master)
-            u.start_gather()
+            if u.fused is not None:
+                u.fused.wait_readers()
+            u.start_gather(epoch=self._step)
 
 
 @torch.no_grad()

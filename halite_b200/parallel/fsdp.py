@@ -95,6 +95,7 @@ class FlatUnit:
         self._reduce_work = None
         self._gather_work = None
         self._backward_done = False
+        self.fused = None         # FusedGather state once `enable_fused_gather` has run
         self._adopt_params()
 
     # ------------------------------------------------------------------ parameter views
@@ -111,6 +112,15 @@ class FlatUnit:
                 new_p._hb_tp_replicated = p._hb_tp_replicated
             # keep initialiser-visible attributes
             m._parameters[n] = new_p
+
+    def rehome(self, buffer):
+        """Move `full_param` into `buffer` (same length and dtype, e.g. symmetric memory): values
+        are copied and every parameter keeps its identity, only its storage changes."""
+        buffer.copy_(self.full_param)
+        self.full_param = buffer
+        for m, n, _, off, numel in self.entries:
+            p = m._parameters[n]
+            p.data = buffer[off:off + numel].view(p.shape)
 
     def params(self):
         return [m._parameters[n] for m, n, _, _, _ in self.entries]
@@ -169,6 +179,9 @@ class FlatUnit:
 
     def pre_forward(self):
         self.wait_gather()
+        if self.fused is not None and self.fused.pending:
+            # nobody carried this unit's gather (first block, or the carrying GEMM did not run)
+            self.fused.run_standalone()
         self._backward_done = False
 
     def wait_gather(self):
@@ -244,9 +257,14 @@ class FlatUnit:
         d_hi = min(max(self.decay_end - self.lo, 0), self.shard_numel)
         return (0, d_hi), (d_hi, self.shard_numel)
 
-    def start_gather(self):
-        """All-gather the updated shard into `full_param` (in place) on the comm stream."""
+    def start_gather(self, epoch=None):
+        """Make the updated shards visible everywhere: an all-gather into `full_param` (in place)
+        on the comm stream, or, with the fused path, a flag that lets the peers' copy CTAs pull
+        this rank's shard from inside one of their GEMM launches."""
         if self.ws == 1:
+            return
+        if self.fused is not None and epoch is not None:
+            self.fused.publish(epoch)
             return
         if self.device.type == "cuda" and self.comm_stream is not None:
             ev = torch.cuda.Event()
@@ -268,6 +286,116 @@ class FlatUnit:
                            group=self.replicate_group)
 
 
+class FusedGather:
+    """All-gather of one unit's parameters carried by a GEMM launch: a few CTAs of that launch
+    copy the peers' shards out of their symmetric-memory `full_param` into the local one with
+    plain loads over NVLink while the other CTAs compute (`GatherParams` of the GEMM kernel).
+
+    Protocol per optimizer step (epoch = step number, flags only ever grow):
+      owner   after AdamW rewrote its shard: writes `ready[owner]` = epoch on every peer
+      reader  copy CTAs wait for `ready[c]` >= epoch before touching chunk c; when the last copy
+              CTA is done it writes `done[reader]` = epoch on every owner
+      owner   before the next AdamW overwrites the shard: waits for `done[r]` >= epoch of all r
+    """
+
+    GRANULE = 256 * 1024
+    COPY_CTAS = 16
+
+    def __init__(self, unit, heap, offset, f_ready, f_done):
+        self.unit, self.heap, self.offset = unit, heap, offset
+        self.f_ready, self.f_done = f_ready, f_done
+        self.chunk_bytes = unit.shard_numel * unit.full_param.element_size()
+        n_gran = unit.ws * ((self.chunk_bytes + self.GRANULE - 1) // self.GRANULE)
+        self.gran_flags = torch.zeros(n_gran, dtype=torch.int32, device=unit.device)
+        self.counter = torch.zeros(1, dtype=torch.int32, device=unit.device)
+        self.pending = 0          # epoch whose gather has not been launched yet
+        self.published = 0        # last epoch this rank announced
+        self.launches = 0         # gathers carried by a model GEMM / launched on their own
+        self.standalone = 0
+
+    def publish(self, epoch):
+        from halite_b200 import ops
+
+        u, h = self.unit, self.heap
+        ptrs = [h.flag_ptr(p, self.f_ready + u.rank) for p in range(u.ws) if p != u.rank]
+        ptrs.append(h.flag_ptr(u.rank, self.f_done + u.rank))      # own slot of the reader accounting
+        ops.ext().signal_flags(ptrs, epoch)
+        self.pending = self.published = epoch
+
+    def wait_readers(self):
+        """Block the stream until every peer has read the shard announced last."""
+        if self.published:
+            from halite_b200 import ops
+
+            flags = self.heap.flags[self.f_done:self.f_done + self.unit.ws]
+            ops.ext().wait_flags(flags, self.published, ops.status_word(self.unit.device))
+
+    def take(self):
+        """Gather description for the GEMM that carries this unit's gather (None when there is
+        nothing to fetch); hands the job over, so only one launch gets it."""
+        if not self.pending:
+            return None
+        epoch, self.pending = self.pending, 0
+        u, h = self.unit, self.heap
+        self.launches += 1
+        return dict(
+            src_ptrs=[0 if c == u.rank else h.data_ptr(c, self.offset + c * self.chunk_bytes) for c in range(u.ws)],
+            peer_done_ptrs=[0 if c == u.rank else h.flag_ptr(c, self.f_done + u.rank) for c in range(u.ws)],
+            dst_ptr=u.full_param.data_ptr(), chunk_bytes=self.chunk_bytes, granule_bytes=self.GRANULE,
+            n_copy_ctas=self.COPY_CTAS, flags_ptr=self.gran_flags.data_ptr(),
+            ready_ptr=h.flag_ptr(u.rank, self.f_ready), done_counter_ptr=self.counter.data_ptr(),
+            epoch=epoch, dep=0, dep_row_bytes=0, dep_base_offset=0, first_chunk=u.rank)
+
+    def run_standalone(self):
+        """The same copy CTAs under a one-tile GEMM on scratch operands."""
+        from halite_b200.ops.linear import gemm
+
+        gather = self.take()
+        if gather is None:
+            return
+        self.standalone += 1
+        dev = self.unit.device
+        scratch = getattr(FusedGather, "_scratch", {}).get(dev)
+        if scratch is None:
+            scratch = (torch.zeros(128, 64, dtype=torch.bfloat16, device=dev),
+                       torch.zeros(64, 64, dtype=torch.bfloat16, device=dev),
+                       torch.zeros(128, 64, dtype=torch.bfloat16, device=dev))
+            FusedGather._scratch = {**getattr(FusedGather, "_scratch", {}), dev: scratch}
+        gemm(scratch[0], scratch[1], out=scratch[2], gather=gather)
+
+
+def enable_fused_gather(state, carried=True):
+    """Move the block units' `full_param` buffers into one symmetric-memory heap and switch their
+    post-optimizer all-gather to the GEMM-carried copy. The root unit (embedding, head, final
+    norm: used before any GEMM of the step) keeps the collective. With `carried`, the gather of
+    block i + 1 rides on the last GEMM of block i's forward; otherwise (and for the first block)
+    it is launched on its own right before the block runs."""
+    from halite_b200.parallel.symm import SymmetricHeap
+
+    units = [u for u in state.units if u is not state.root_unit and u.ws > 1]
+    if not units or units[0].device.type != "cuda":
+        return False
+    elem = units[0].full_param.element_size()
+    sizes = [(u.padded * elem + 255) // 256 * 256 for u in units]
+    heap = SymmetricHeap(sum(sizes) + 256 * len(units), group=state.shard_group, device=units[0].device)
+    state.gather_heap = heap
+    for u, nbytes in zip(units, sizes):
+        off = heap.alloc(nbytes)
+        u.rehome(heap.tensor(off, (u.padded,), u.full_param.dtype))
+        u.fused = FusedGather(u, heap, off, heap.alloc_flags(u.ws), heap.alloc_flags(u.ws))
+    _install_fused_views(state.model, state.units)
+    if carried:
+        for prev, nxt in zip(units[:-1], units[1:]):
+            # last weight matrix of the previous block in module order (the down projection)
+            mats = [(m, n) for m, n, p, _, _ in prev.entries if p.ndim == 2 and isinstance(m, nn.Linear)]
+            if mats:
+                m, n = mats[-1]
+                m._parameters[n]._hb_carry = nxt.fused.take
+    torch.cuda.synchronize(units[0].device)
+    dist.barrier(state.shard_group)
+    return True
+
+
 class ShardedModel:
     """Book-keeping object attached to a wrapped model as `model._hb_fsdp`."""
 
@@ -278,6 +406,15 @@ class ShardedModel:
         self.shard_group = shard_group
         self.replicate_group = replicate_group
         self.comm_stream = comm_stream
+        self.gather_heap = None
+
+    def flush_gathers(self):
+        """Launch every gather that is still waiting for its carrier (before anything other than
+        the model's own forward reads the parameters: state_dict, weight export, evaluation of a
+        sub-module)."""
+        for u in self.units:
+            if u.fused is not None and u.fused.pending:
+                u.fused.run_standalone()
 
     def finish_backward(self):
         """Run after `loss.backward()`: closes the root unit (and any unit whose boundary did
@@ -335,7 +472,7 @@ def _unit_params(module: nn.Module, exclude: set[int]):
 
 def apply_fsdp(model, mesh=None, param_dtype=torch.bfloat16, reduce_dtype=torch.float32,
                reshard_after_forward=False, device=None, blocks_attr="blocks", force_fsdp=False,
-               block_iterator=None):
+               block_iterator=None, fused_all_gather=None):
     """Shard `model` over the mesh's data-parallel dimensions. Returns the same module, with
     parameters re-homed into flat unit buffers and `model._hb_fsdp` set.
 
@@ -343,6 +480,8 @@ def apply_fsdp(model, mesh=None, param_dtype=torch.bfloat16, reduce_dtype=torch.
     `block_iterator(model)` may yield `(key, block, container)` for models whose blocks live in
     more than one container (an encoder's blocks followed by the model's own); each yielded block
     becomes a unit. Without it the units are the entries of `model.<blocks_attr>`.
+    `fused_all_gather` (default: the HB_FSDP_FUSED_GATHER environment variable) replaces the block
+    units' parameter all-gather collective by copies carried inside GEMM launches (`FusedGather`).
     """
     shard_group = mesh.group("dp_shard") if mesh is not None else None
     replicate_group = mesh.group("dp_replicate") if mesh is not None else None
@@ -426,6 +565,13 @@ def apply_fsdp(model, mesh=None, param_dtype=torch.bfloat16, reduce_dtype=torch.
         return None
 
     model.register_forward_pre_hook(root_pre_forward, with_kwargs=True)
+    if fused_all_gather is None:
+        import os
+
+        fused_all_gather = os.environ.get("HB_FSDP_FUSED_GATHER", "0") == "1"
+    if fused_all_gather and shard_group is not None and device.type == "cuda" and calls_block_hooks:
+        if enable_fused_gather(state):
+            model.register_state_dict_pre_hook(lambda module, prefix, keep_vars: state.flush_gathers())
     return model
 
 

@@ -27,3 +27,11 @@ def test_pynccl_communicator_on_two_gpus():
     outs = run_ranks(os.path.join(ROOT, "tests/ranks/pynccl_ranks.py"), 2, args=[free_port()], timeout=300,
                      env_extra={"HB_TEST_CUDA_VISIBLE": "0,1", "CUDA_VISIBLE_DEVICES": "0,1"})
     assert all("RESULT" in o for o in outs), outs[0][-2000:]
+
+
+def test_fsdp_parameter_gather_carried_by_gemm_launches():
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", str(free_port()), os.path.join(ROOT, "tests/ranks/fsdp_fused_gather_ranks.py")]
+    env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE="0")
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0 and "RESULT ok" in out.stdout, (out.stdout + out.stderr)[-3000:]
