@@ -54,6 +54,11 @@ bool fill_gather(const c10::optional<py::dict>& d, hb::GatherParams& gp) {
   gp.dep_base_offset = g.contains("dep_base_offset") ? g["dep_base_offset"].cast<int64_t>() : 0;
   gp.m_rot = g.contains("m_rot") ? g["m_rot"].cast<int>() : 0;
   gp.first_chunk = g.contains("first_chunk") ? g["first_chunk"].cast<int>() : 0;
+  if (g.contains("reduce_out_ptr")) {
+    gp.reduce_out = reinterpret_cast<float*>(g["reduce_out_ptr"].cast<int64_t>());
+    gp.reduce_numel = g["reduce_numel"].cast<int64_t>();
+    gp.reduce_scale = g["reduce_scale"].cast<float>();
+  }
   return true;
 }
 

@@ -37,6 +37,14 @@ struct GatherParams {
   long dep_base_offset = 0;          // byte offset of operand row 0 inside the destination
   int m_rot = 0;                     // first M tile to compute (start on the local chunk)
   int first_chunk = 0;               // chunk handled first by the copy CTAs (the local one)
+  // Reduce mode (reduce_out != nullptr): instead of copying, the copy CTAs compute
+  //   reduce_out[i] = reduce_scale * sum over chunks c of ((const float*)src[c])[i],  i < reduce_numel
+  // in chunk order (the same order on every rank), i.e. this rank's part of a reduce-scatter of
+  // fp32 buffers that live in every rank's memory; src[c] is chunk c's buffer already offset to
+  // this rank's range (own buffer included). `ready` / `peer_done` work as above.
+  float* reduce_out = nullptr;
+  long reduce_numel = 0;
+  float reduce_scale = 1.f;
 };
 
 // Fused GEMM -> reduce-scatter over the M dimension. Output rows are split into `n_chunks`

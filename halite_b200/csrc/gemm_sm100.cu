@@ -181,10 +181,16 @@ __device__ __forceinline__ bool wait_rows(const GatherParams& gp, long row0, lon
   const long hi = gp.dep_base_offset + r1 * gp.dep_row_bytes - 1;
   const long total = gp.chunk_bytes * gp.n_chunks;
   if (hi < 0 || lo >= total) return true;
-  const long g0 = max(lo, 0L) / gp.granule_bytes;
-  const long g1 = min(hi, total - 1) / gp.granule_bytes;
-  for (long g = g0; g <= g1; ++g)
-    if (!wait_flag(gp.flags + g, gp.epoch, false, abort_flag, status)) return false;
+  // flags are numbered chunk by chunk (a chunk's last granule may be short), like the copy CTAs do
+  const long gpc = (gp.chunk_bytes + gp.granule_bytes - 1) / gp.granule_bytes;
+  const long b0 = max(lo, 0L), b1 = min(hi, total - 1);
+  for (long c = b0 / gp.chunk_bytes; c <= b1 / gp.chunk_bytes; ++c) {
+    const long base = c * gp.chunk_bytes;
+    const long g0 = (max(b0, base) - base) / gp.granule_bytes;
+    const long g1 = (min(b1, base + gp.chunk_bytes - 1) - base) / gp.granule_bytes;
+    for (long g = g0; g <= g1; ++g)
+      if (!wait_flag(gp.flags + c * gpc + g, gp.epoch, false, abort_flag, status)) return false;
+  }
   return true;
 }
 
@@ -231,6 +237,63 @@ __device__ __forceinline__ void gather_copy_cta(const GatherParams& gp, int cta,
     }
   }
   // the last copy CTA to finish tells every source owner that its chunk has been read
+  __syncthreads();
+  if (threadIdx.x == 0 && gp.done_counter) {
+    __threadfence();
+    const int prev = atomicAdd(gp.done_counter, 1);
+    if (prev == gp.n_copy_ctas - 1) {
+      for (int c = 0; c < gp.n_chunks; ++c)
+        if (gp.peer_done[c]) st_release_sys(gp.peer_done[c], gp.epoch);
+    }
+  }
+}
+
+// Body of a copy CTA in reduce mode: this rank's slice of an fp32 reduce-scatter, read from every
+// rank's buffer with plain loads, summed in chunk order and scaled.
+__device__ __forceinline__ void reduce_copy_cta(const GatherParams& gp, int cta, volatile int* abort_flag,
+                                                int* status) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    s_ok = 1;
+    for (int c = 0; c < gp.n_chunks && s_ok; ++c)
+      if (gp.ready && c != gp.first_chunk && !wait_flag(gp.ready + c, gp.epoch, true, abort_flag, status)) s_ok = 0;
+  }
+  __syncthreads();
+  if (s_ok) {
+    const long n4 = gp.reduce_numel >> 2;
+    float4* out = reinterpret_cast<float4*>(gp.reduce_out);
+    const long stride = static_cast<long>(gp.n_copy_ctas) * blockDim.x;
+    constexpr int kUnroll = 4;     // elements per thread and pass: kUnroll * ranks 16-byte loads in flight
+    for (long base = static_cast<long>(cta) * blockDim.x + threadIdx.x; base < n4; base += stride * kUnroll) {
+      float4 v[kUnroll][kMaxPeers];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const long i = base + u * stride;
+#pragma unroll
+        for (int c = 0; c < kMaxPeers; ++c)
+          if (c < gp.n_chunks && i < n4) v[u][c] = reinterpret_cast<const float4*>(gp.src[c])[i];
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const long i = base + u * stride;
+        if (i >= n4) break;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int c = 0; c < kMaxPeers; ++c)
+          if (c < gp.n_chunks) {
+            acc.x += v[u][c].x;
+            acc.y += v[u][c].y;
+            acc.z += v[u][c].z;
+            acc.w += v[u][c].w;
+          }
+        acc.x *= gp.reduce_scale;
+        acc.y *= gp.reduce_scale;
+        acc.z *= gp.reduce_scale;
+        acc.w *= gp.reduce_scale;
+        out[i] = acc;
+      }
+    }
+  }
   __syncthreads();
   if (threadIdx.x == 0 && gp.done_counter) {
     __threadfence();
@@ -475,7 +538,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
   const int tile_step = static_cast<int>(gridDim.x) - n_copy;
 
   if (first_tile < 0) {
-    gather_copy_cta(gp, blockIdx.x, &abort_flag, status);
+    if (gp.reduce_out) reduce_copy_cta(gp, blockIdx.x, &abort_flag, status);
+    else gather_copy_cta(gp, blockIdx.x, &abort_flag, status);
   } else if (warp == 0 && lane == 0) {
     // ------------------------------------------------------------ producer
     int stage = 0;
@@ -1330,6 +1394,8 @@ cudaError_t launch(const GemmArgs& g) {
   if (gp.n_copy_ctas > 0) {
     // every CTA must be resident at once (compute CTAs wait on copy CTAs): one CTA per SM
     if (gp.n_copy_ctas >= sm_count() || gp.granule_bytes % 16 || gp.chunk_bytes % 16)
+      return cudaErrorInvalidValue;
+    if (gp.reduce_out && (gp.reduce_numel % 4 || (reinterpret_cast<uintptr_t>(gp.reduce_out) & 15)))
       return cudaErrorInvalidValue;
     const int compute = tiles < sm_count() - gp.n_copy_ctas ? tiles : sm_count() - gp.n_copy_ctas;
     grid = compute + gp.n_copy_ctas;

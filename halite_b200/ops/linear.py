@@ -72,7 +72,9 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             # dX[M,K] = dY[M,N] @ W[N,K]: B operand is W read "MN-major"
             w = weight if _gemm_ready(weight) else weight.contiguous()
-            dx = gemm(dy2, w, b_mn=True).view(ctx.x_shape)
+            # the gradient reduction of the unit whose backward just ended may ride on this launch
+            carry = getattr(ctx.weight_ref, "_hb_carry_bwd", None)
+            dx = gemm(dy2, w, b_mn=True, gather=carry() if carry is not None else None).view(ctx.x_shape)
         wref = ctx.weight_ref
         main = getattr(wref, "_hb_grad", None)
         if main is not None:

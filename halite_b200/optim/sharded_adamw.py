@@ -67,6 +67,8 @@ class ShardedAdamW(torch.optim.Optimizer):
         for u in self.units:
             if u.fused is not None:
                 u.fused.wait_readers()     # peers still copying last step's shard finish first
+            if u.fused_reduce is not None:
+                u.fused_reduce.wait_readers()   # ... and peers still summing this step's gradients
         for u, lo, hi, gi in self._slots:
             g = self.param_groups[self._gidx[gi]]
             ops.fused_adamw_step(

@@ -96,6 +96,7 @@ class FlatUnit:
         self._gather_work = None
         self._backward_done = False
         self.fused = None         # FusedGather state once `enable_fused_gather` has run
+        self.fused_reduce = None  # FusedReduce state once `enable_fused_reduce` has run
         self._adopt_params()
 
     # ------------------------------------------------------------------ parameter views
@@ -121,6 +122,15 @@ class FlatUnit:
         for m, n, _, off, numel in self.entries:
             p = m._parameters[n]
             p.data = buffer[off:off + numel].view(p.shape)
+
+    def rehome_grad(self, buffer):
+        """Move `full_grad` into `buffer` (fp32, same length); every parameter's main-grad view
+        follows."""
+        buffer.copy_(self.full_grad)
+        self.full_grad = buffer
+        for m, n, _, off, numel in self.entries:
+            p = m._parameters[n]
+            p._hb_grad = buffer[off:off + numel].view(p.shape)
 
     def params(self):
         return [m._parameters[n] for m, n, _, _, _ in self.entries]
@@ -220,6 +230,9 @@ class FlatUnit:
     def start_reduce(self):
         if self.ws == 1 and self.replicate_group is None:
             return
+        if self.fused_reduce is not None:
+            self.fused_reduce.publish()
+            return
         if self.device.type == "cuda" and self.comm_stream is not None:
             ev = torch.cuda.Event()
             ev.record()
@@ -238,6 +251,8 @@ class FlatUnit:
             comm.all_reduce(self.grad_shard, self.replicate_group, average=True)
 
     def wait_reduce(self):
+        if self.fused_reduce is not None and self.fused_reduce.pending:
+            self.fused_reduce.run_standalone()       # nobody carried it (last unit of the backward pass)
         if self._reduce_event is not None:
             torch.cuda.current_stream().wait_event(self._reduce_event)
             self._reduce_event = None
@@ -354,14 +369,113 @@ class FusedGather:
         if gather is None:
             return
         self.standalone += 1
-        dev = self.unit.device
-        scratch = getattr(FusedGather, "_scratch", {}).get(dev)
-        if scratch is None:
-            scratch = (torch.zeros(128, 64, dtype=torch.bfloat16, device=dev),
-                       torch.zeros(64, 64, dtype=torch.bfloat16, device=dev),
-                       torch.zeros(128, 64, dtype=torch.bfloat16, device=dev))
-            FusedGather._scratch = {**getattr(FusedGather, "_scratch", {}), dev: scratch}
-        gemm(scratch[0], scratch[1], out=scratch[2], gather=gather)
+        a, b, out = _scratch_gemm_operands(self.unit.device)
+        gemm(a, b, out=out, gather=gather)
+
+
+class FusedReduce:
+    """Reduce-scatter of one unit's fp32 gradients carried by a GEMM launch of the backward pass:
+    a few CTAs of that launch read this rank's range out of every rank's symmetric-memory
+    `full_grad` with plain loads over NVLink, add the ranks in rank order, scale by 1 / ranks and
+    write the rank's `grad_shard`, while the other CTAs compute. Flags as in `FusedGather`:
+    `ready[owner]` = epoch once a rank's gradients of the unit are complete, `done[reader]` =
+    epoch once a rank has read everybody's range (the buffer may be overwritten after that)."""
+
+    COPY_CTAS = 32
+
+    def __init__(self, unit, heap, offset, f_ready, f_done):
+        self.unit, self.heap, self.offset = unit, heap, offset
+        self.f_ready, self.f_done = f_ready, f_done
+        self.counter = torch.zeros(1, dtype=torch.int32, device=unit.device)
+        self.epoch = 0
+        self.pending = 0
+        self.launches = 0
+        self.standalone = 0
+
+    def publish(self):
+        from halite_b200 import ops
+
+        u, h = self.unit, self.heap
+        self.epoch += 1
+        ptrs = [h.flag_ptr(p, self.f_ready + u.rank) for p in range(u.ws) if p != u.rank]
+        ptrs.append(h.flag_ptr(u.rank, self.f_done + u.rank))
+        ops.ext().signal_flags(ptrs, self.epoch)
+        self.pending = self.epoch
+
+    def wait_readers(self):
+        """Block the stream until every peer has read this rank's gradients of the last pass."""
+        if self.epoch:
+            from halite_b200 import ops
+
+            flags = self.heap.flags[self.f_done:self.f_done + self.unit.ws]
+            ops.ext().wait_flags(flags, self.epoch, ops.status_word(self.unit.device))
+
+    def take(self):
+        if not self.pending:
+            return None
+        epoch, self.pending = self.pending, 0
+        u, h = self.unit, self.heap
+        self.launches += 1
+        mine = self.offset + u.lo * 4      # this rank's range inside every rank's fp32 buffer
+        return dict(
+            src_ptrs=[h.data_ptr(c, mine) for c in range(u.ws)],
+            peer_done_ptrs=[0 if c == u.rank else h.flag_ptr(c, self.f_done + u.rank) for c in range(u.ws)],
+            dst_ptr=0, chunk_bytes=16, granule_bytes=16, n_copy_ctas=self.COPY_CTAS, flags_ptr=0,
+            ready_ptr=h.flag_ptr(u.rank, self.f_ready), done_counter_ptr=self.counter.data_ptr(),
+            epoch=epoch, dep=0, dep_row_bytes=0, first_chunk=u.rank,
+            reduce_out_ptr=u.grad_shard.data_ptr(), reduce_numel=u.shard_numel, reduce_scale=1.0 / u.ws)
+
+    def run_standalone(self):
+        from halite_b200.ops.linear import gemm
+
+        gather = self.take()
+        if gather is None:
+            return
+        self.standalone += 1
+        a, b, out = _scratch_gemm_operands(self.unit.device)
+        gemm(a, b, out=out, gather=gather)
+
+
+_SCRATCH = {}
+
+
+def _scratch_gemm_operands(device):
+    """Operands of the one-tile GEMM that hosts copy CTAs when no model GEMM is at hand."""
+    key = torch.device(device)
+    if key not in _SCRATCH:
+        _SCRATCH[key] = (torch.zeros(128, 64, dtype=torch.bfloat16, device=key),
+                         torch.zeros(64, 64, dtype=torch.bfloat16, device=key),
+                         torch.zeros(128, 64, dtype=torch.bfloat16, device=key))
+    return _SCRATCH[key]
+
+
+def enable_fused_reduce(state):
+    """Move the block units' fp32 `full_grad` buffers into one symmetric-memory heap and replace
+    their reduce-scatter collective by `FusedReduce`: the reduction of block i rides on the first
+    backward GEMM of block i - 1; the first block's runs on its own when the backward pass ends.
+    The root unit keeps the collective."""
+    from halite_b200.parallel.symm import SymmetricHeap
+
+    units = [u for u in state.units if u is not state.root_unit and u.ws > 1]
+    if not units or units[0].device.type != "cuda" or state.replicate_group is not None \
+            or units[0].reduce_dtype != torch.float32:
+        return False
+    sizes = [(u.padded * 4 + 255) // 256 * 256 for u in units]
+    heap = SymmetricHeap(sum(sizes) + 256 * len(units), group=state.shard_group, device=units[0].device)
+    state.reduce_heap = heap
+    for u, nbytes in zip(units, sizes):
+        off = heap.alloc(nbytes)
+        u.rehome_grad(heap.tensor(off, (u.padded,), torch.float32))
+        u.fused_reduce = FusedReduce(u, heap, off, heap.alloc_flags(u.ws), heap.alloc_flags(u.ws))
+    _install_fused_views(state.model, state.units)
+    for prev, nxt in zip(units[:-1], units[1:]):
+        mats = [(m, n) for m, n, p, _, _ in prev.entries if p.ndim == 2 and isinstance(m, nn.Linear)]
+        if mats:
+            m, n = mats[-1]
+            m._parameters[n]._hb_carry_bwd = nxt.fused_reduce.take
+    torch.cuda.synchronize(units[0].device)
+    dist.barrier(state.shard_group)
+    return True
 
 
 def enable_fused_gather(state, carried=True):
@@ -407,6 +521,7 @@ class ShardedModel:
         self.replicate_group = replicate_group
         self.comm_stream = comm_stream
         self.gather_heap = None
+        self.reduce_heap = None
 
     def flush_gathers(self):
         """Launch every gather that is still waiting for its carrier (before anything other than
@@ -472,7 +587,7 @@ def _unit_params(module: nn.Module, exclude: set[int]):
 
 def apply_fsdp(model, mesh=None, param_dtype=torch.bfloat16, reduce_dtype=torch.float32,
                reshard_after_forward=False, device=None, blocks_attr="blocks", force_fsdp=False,
-               block_iterator=None, fused_all_gather=None):
+               block_iterator=None, fused_all_gather=None, fused_reduce_scatter=None):
     """Shard `model` over the mesh's data-parallel dimensions. Returns the same module, with
     parameters re-homed into flat unit buffers and `model._hb_fsdp` set.
 
@@ -481,7 +596,9 @@ def apply_fsdp(model, mesh=None, param_dtype=torch.bfloat16, reduce_dtype=torch.
     more than one container (an encoder's blocks followed by the model's own); each yielded block
     becomes a unit. Without it the units are the entries of `model.<blocks_attr>`.
     `fused_all_gather` (default: the HB_FSDP_FUSED_GATHER environment variable) replaces the block
-    units' parameter all-gather collective by copies carried inside GEMM launches (`FusedGather`).
+    units' parameter all-gather collective by copies carried inside GEMM launches (`FusedGather`);
+    `fused_reduce_scatter` (HB_FSDP_FUSED_REDUCE) does the same for the gradient reduce-scatter
+    (`FusedReduce`).
     """
     shard_group = mesh.group("dp_shard") if mesh is not None else None
     replicate_group = mesh.group("dp_replicate") if mesh is not None else None
@@ -572,6 +689,12 @@ def apply_fsdp(model, mesh=None, param_dtype=torch.bfloat16, reduce_dtype=torch.
     if fused_all_gather and shard_group is not None and device.type == "cuda" and calls_block_hooks:
         if enable_fused_gather(state):
             model.register_state_dict_pre_hook(lambda module, prefix, keep_vars: state.flush_gathers())
+    if fused_reduce_scatter is None:
+        import os
+
+        fused_reduce_scatter = os.environ.get("HB_FSDP_FUSED_REDUCE", "0") == "1"
+    if fused_reduce_scatter and shard_group is not None and device.type == "cuda" and calls_block_hooks:
+        enable_fused_reduce(state)
     return model
 
 

@@ -16,7 +16,8 @@ def parallelize(model, mesh=None, parallel_dims=None, param_dtype="bfloat16", re
                 tensor_parallel_config=None, activation_checkpointing=False,
                 activation_checkpointing_config=None, compile=False, compile_config=None,
                 reshard_after_forward=False, data_parallel="fsdp", force_fsdp=False, device=None,
-                loss_parallel=False, block_iterator=None, fused_all_gather=None, **unused):
+                loss_parallel=False, block_iterator=None, fused_all_gather=None,
+                fused_reduce_scatter=None, **unused):
     pd = parallel_dims if parallel_dims is not None else mesh
     param_dtype = get_torch_dtype(param_dtype)
     reduce_dtype = get_torch_dtype(reduce_dtype)
@@ -36,4 +37,4 @@ def parallelize(model, mesh=None, parallel_dims=None, param_dtype="bfloat16", re
         return apply_ddp(model, pd, param_dtype=param_dtype, reduce_dtype=reduce_dtype, device=device)
     return apply_fsdp(model, pd, param_dtype=param_dtype, reduce_dtype=reduce_dtype,
                       reshard_after_forward=reshard_after_forward, device=device, block_iterator=block_iterator,
-                      fused_all_gather=fused_all_gather)
+                      fused_all_gather=fused_all_gather, fused_reduce_scatter=fused_reduce_scatter)

@@ -1,7 +1,8 @@
 """Launched by torchrun on >= 2 GPUs: trains a small decoder for a few steps twice from the same
 seed, once with the parameter all-gather as a collective and once carried inside GEMM launches
-over symmetric memory, and checks that losses and final parameters agree (the carrying GEMMs
-run on a different tile schedule, so sums differ in the last bits)."""
+over symmetric memory (then with the gradient reduce-scatter carried too), and checks that
+losses and final parameters agree (the carrying GEMMs run on a different tile schedule and the
+reduction adds the ranks in another order than the collective, so sums differ in the last bits)."""
 
 import os
 import sys
@@ -34,11 +35,12 @@ def main():
     torch.manual_seed(1 + rank)
     batches = [torch.randint(0, 1024, (4, 257), device=dev) for _ in range(5)]
 
-    def train(fused):
+    def train(fused, fused_reduce=False):
         torch.manual_seed(0)
         with torch.device("meta"):
             model = instantiate(cfg)
-        model = parallelize(model, pd, pd, param_dtype="bfloat16", device=dev, fused_all_gather=fused)
+        model = parallelize(model, pd, pd, param_dtype="bfloat16", device=dev, fused_all_gather=fused,
+                            fused_reduce_scatter=fused_reduce)
         model.init_weights(dev)
         model._hb_fsdp.sync_parameters()
         opt = build_optimizer(partial(torch.optim.AdamW, lr=1e-3, betas=(0.9, 0.95)), model, weight_decay=0.1)
@@ -65,9 +67,22 @@ def main():
     for k in base_sd:
         a, b = sd[k].float(), base_sd[k].float()
         assert (a - b).norm() <= 2e-2 * b.norm().clamp(min=1e-6), k
+    # gradient reduce-scatter carried by backward GEMMs as well
+    losses2, sd2, model2 = train(True, True)
+    reducers = [u.fused_reduce for u in model2._hb_fsdp.units if u.fused_reduce is not None]
+    assert len(reducers) == 4
+    carried = sum(r.launches - r.standalone for r in reducers)
+    alone = sum(r.standalone for r in reducers)
+    assert carried == 3 * 5 and alone == 5, (carried, alone)     # per step: three ride, the first block's runs alone
+    assert all(abs(a - b) < 2e-3 for a, b in zip(losses2, base_losses)), (losses2, base_losses)
+    for k in base_sd:
+        a, b = sd2[k].float(), base_sd[k].float()
+        assert (a - b).norm() <= 2e-2 * b.norm().clamp(min=1e-6), k
+    torch.cuda.synchronize()
+    ops.check_status()
     dist.barrier()
     if rank == 0:
-        print("RESULT ok", losses)
+        print("RESULT ok", losses, losses2)
     dist.destroy_process_group()
 
 

@@ -83,6 +83,38 @@ def test_allgather_gemm_b_operand_inside_flat_buffer():
     assert ((y.float() - ref).abs().max() / ref.abs().max()) < 6e-3
 
 
+def test_reduce_scatter_slice_carried_by_a_gemm_launch():
+    """Reduce mode of the copy CTAs, four ranks' fp32 buffers emulated in local memory: the
+    launch computes its GEMM and, beside it, scale * (sum of the ranks' slices) in rank order."""
+    from halite_b200 import ops
+    from halite_b200.ops import gemm
+
+    torch.manual_seed(3)
+    world, rank, n = 4, 2, 1 << 20
+    grads = [torch.randn(world * n, device="cuda") for _ in range(world)]      # every rank's full buffer
+    out = torch.zeros(n, device="cuda")
+    epoch = 7
+    ready, done, counter = _i32(world, epoch), _i32(world), _i32(1)
+    x = torch.randn(512, 256, device="cuda").bfloat16()
+    w = torch.randn(384, 256, device="cuda").bfloat16()
+    gather = dict(
+        src_ptrs=[g[rank * n:].data_ptr() for g in grads], dst_ptr=0, chunk_bytes=16, granule_bytes=16,
+        n_copy_ctas=8, flags_ptr=0, ready_ptr=ready.data_ptr(), done_counter_ptr=counter.data_ptr(),
+        peer_done_ptrs=[0 if c == rank else done[c:].data_ptr() for c in range(world)],
+        epoch=epoch, dep=0, dep_row_bytes=0, first_chunk=rank,
+        reduce_out_ptr=out.data_ptr(), reduce_numel=n, reduce_scale=0.25)
+    y = gemm(x, w, gather=gather)
+    torch.cuda.synchronize()
+    ops.check_status()
+    want = grads[0][rank * n:(rank + 1) * n].clone()
+    for g in grads[1:]:
+        want += g[rank * n:(rank + 1) * n]
+    assert torch.equal(out, want * 0.25)
+    assert done.tolist() == [epoch if c != rank else 0 for c in range(world)]
+    ref = x.float() @ w.float().t()
+    assert ((y.float() - ref).abs().max() / ref.abs().max()) < 6e-3
+
+
 @pytest.mark.parametrize("rank", [0, 1])
 def test_gemm_reduce_scatter(rank):
     from halite_b200 import ops
