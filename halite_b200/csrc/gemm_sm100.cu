@@ -784,7 +784,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
                       const __grid_constant__ CUtensorMap tma_b, OutT* __restrict__ D, int M, int N,
                       int K, int ldd, int accumulate, int* __restrict__ status,
-                      const __grid_constant__ SplitParams kp) {
+                      const __grid_constant__ SplitParams kp, const __grid_constant__ GatherParams gp) {
   using C = PairCfg;
   constexpr int kStages = C::kStages;
   constexpr int BN = C::kBN;
@@ -805,6 +805,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();   // 0: issues the MMAs, 1: its partner
   const bool leader = rank == 0;
+  // The first n_copy_ctas / 2 clusters of a launch that carries a copy or reduction job (no tile
+  // depends on it: gp.dep == 0) only run that job; they take part in the two cluster barriers
+  // and in nothing else.
+  const int copy_clusters = gp.n_copy_ctas >> 1;
+  const bool copy_cluster = static_cast<int>(cluster_id_x()) < copy_clusters;
 
   const int tiles_m = (M + 2 * kBM - 1) / (2 * kBM);
   const int tiles_n = (N + BN - 1) / BN;
@@ -829,7 +834,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
   }
-  if (warp == 2) {
+  if (warp == 2 && !copy_cluster) {
     tmem_alloc_pair(smem_u32(&tmem_slot), C::kTmemCols);
     tmem_relinquish_pair();
   }
@@ -837,12 +842,12 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
   // both CTAs' barriers exist before either sends the other a signal
   cluster_sync_all();
   tc_fence_after();
-  const uint32_t tmem_base = tmem_slot;
+  const uint32_t tmem_base = copy_cluster ? 0u : tmem_slot;
 
   const int n_items = kp.parts > 1 ? kp.items : num_tiles;
   const int group_m = kp.group_m > 0 ? kp.group_m : C::kGroupM;
-  const int first_tile = static_cast<int>(cluster_id_x());
-  const int tile_step = static_cast<int>(num_clusters_x());
+  const int first_tile = static_cast<int>(cluster_id_x()) - copy_clusters;
+  const int tile_step = static_cast<int>(num_clusters_x()) - copy_clusters;
   const bool dynamic = kp.tile_counter != nullptr;
 
   // Next work item of this role (-1: none left, or a wait gave up). `n` counts the items the
@@ -879,7 +884,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
     return w;
   };
 
-  if (warp == 0 && lane == 0) {
+  if (copy_cluster) {
+    if (gp.reduce_out) reduce_copy_cta(gp, blockIdx.x, &abort_flag, status);
+    else gather_copy_cta(gp, blockIdx.x, &abort_flag, status);
+  } else if (warp == 0 && lane == 0) {
     // ------------------------------------------------------------ producer (one per CTA)
     int stage = 0;
     uint32_t phase = 0;
@@ -1016,7 +1024,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
   // neither CTA leaves (or frees tensor memory) while its partner may still signal its
   // barriers or read its shared memory
   cluster_sync_all();
-  if (warp == 2) {
+  if (warp == 2 && !copy_cluster) {
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, C::kTmemCols);
   }
@@ -1519,20 +1527,31 @@ cudaError_t launch_pair(const GemmArgs& g) {
   }
   (void)cudaGetLastError();
   const int tiles = ((g.M + 2 * kBM - 1) / (2 * kBM)) * ((g.N + C::kBN - 1) / C::kBN);
-  int clusters = tiles < clusters_max ? tiles : clusters_max;
+  GatherParams gp;
+  if (g.gather) {
+    gp = *g.gather;
+    // only jobs no tile waits for, on whole clusters, leaving at least half of the machine to the tiles
+    if (gp.dep != 0 || gp.n_copy_ctas % 2 || gp.n_copy_ctas / 2 * 2 > clusters_max) return cudaErrorInvalidValue;
+    if (gp.reduce_out && (gp.reduce_numel % 4 || (reinterpret_cast<uintptr_t>(gp.reduce_out) & 15)))
+      return cudaErrorInvalidValue;
+    if (gp.done_counter) cudaMemsetAsync(gp.done_counter, 0, sizeof(int), g.stream);
+  }
+  const int copy_clusters = gp.n_copy_ctas / 2;
+  const int compute_max = clusters_max - copy_clusters;
+  int clusters = tiles < compute_max ? tiles : compute_max;
   SplitParams kp;
   // counters[0] hands out work items; the rest are the split tiles' arrival counters
   float* ws = nullptr;
   int* counters = nullptr;
   const bool have_ws = split_workspace(0, 1, g.stream, &ws, &counters) == cudaSuccess;
   int n_counters = 0;
-  if (have_ws && dynamic_schedule_enabled() && tiles > clusters_max) {
+  if (have_ws && dynamic_schedule_enabled() && tiles > compute_max) {
     kp.tile_counter = counters;
     n_counters = 1;
   }
   if (have_ws) {
     // same tail treatment as the single-CTA kernel, counted in clusters
-    const int base = clusters_max;
+    const int base = compute_max;
     const int num_kb = (g.K + kBK - 1) / kBK;
     const int rem = tiles % base;
     if (tiles > base && rem > 0 && rem * 2 <= base && num_kb >= 16) {
@@ -1555,8 +1574,8 @@ cudaError_t launch_pair(const GemmArgs& g) {
     }
   }
   if (n_counters > 0) cudaMemsetAsync(counters, 0, sizeof(int) * n_counters, g.stream);
-  kern<<<2 * clusters, kThreads, C::kSmemBytes, g.stream>>>(ta, tb, static_cast<OutT*>(g.d), g.M, g.N, g.K,
-                                                            g.ldd, g.accumulate ? 1 : 0, g.status, kp);
+  kern<<<2 * (clusters + copy_clusters), kThreads, C::kSmemBytes, g.stream>>>(
+      ta, tb, static_cast<OutT*>(g.d), g.M, g.N, g.K, g.ldd, g.accumulate ? 1 : 0, g.status, kp, gp);
   return cudaGetLastError();
 }
 
@@ -1726,9 +1745,12 @@ cudaError_t gemm_bf16(const GemmArgs& g) {
       (g.lda % 8) || (g.ldb % 8))
     return cudaErrorInvalidValue;
   const bool plain = !g.gather && !g.scatter && g.max_ctas == 0;
-  if (g.block_n == kPairBlockN && !plain) return cudaErrorInvalidValue;
+  // the pair kernel also hosts copy / reduce jobs that no tile depends on
+  const bool pairable = plain || (g.gather && !g.scatter && g.max_ctas == 0 && g.gather->dep == 0 &&
+                                  g.gather->n_copy_ctas % 2 == 0);
+  if (g.block_n == kPairBlockN && !pairable) return cudaErrorInvalidValue;
   bool pair = g.block_n == kPairBlockN;
-  if (g.block_n == 0 && plain && pair_kernel_enabled()) {
+  if (g.block_n == 0 && pairable && pair_kernel_enabled()) {
     const long pair_tiles = static_cast<long>((g.M + 255) / 256) * ((g.N + 255) / 256);
     pair = pair_tiles >= sm_count() / 2;
   }

@@ -83,9 +83,12 @@ def test_allgather_gemm_b_operand_inside_flat_buffer():
     assert ((y.float() - ref).abs().max() / ref.abs().max()) < 6e-3
 
 
-def test_reduce_scatter_slice_carried_by_a_gemm_launch():
+@pytest.mark.parametrize("gemm_shape", [(512, 384, 256), (4096, 5120, 512)])
+def test_reduce_scatter_slice_carried_by_a_gemm_launch(gemm_shape):
     """Reduce mode of the copy CTAs, four ranks' fp32 buffers emulated in local memory: the
-    launch computes its GEMM and, beside it, scale * (sum of the ranks' slices) in rank order."""
+    launch computes its GEMM and, beside it, scale * (sum of the ranks' slices) in rank order.
+    The small GEMM runs on the single-CTA kernel, the large one on the CTA-pair kernel (whose
+    first clusters then do the reduction)."""
     from halite_b200 import ops
     from halite_b200.ops import gemm
 
@@ -95,8 +98,9 @@ def test_reduce_scatter_slice_carried_by_a_gemm_launch():
     out = torch.zeros(n, device="cuda")
     epoch = 7
     ready, done, counter = _i32(world, epoch), _i32(world), _i32(1)
-    x = torch.randn(512, 256, device="cuda").bfloat16()
-    w = torch.randn(384, 256, device="cuda").bfloat16()
+    M, N, K = gemm_shape
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = torch.randn(N, K, device="cuda").bfloat16()
     gather = dict(
         src_ptrs=[g[rank * n:].data_ptr() for g in grads], dst_ptr=0, chunk_bytes=16, granule_bytes=16,
         n_copy_ctas=8, flags_ptr=0, ready_ptr=ready.data_ptr(), done_counter_ptr=counter.data_ptr(),
