@@ -77,6 +77,7 @@ class ShardedAdamW(torch.optim.Optimizer):
                 g["weight_decay"], self._step, 1.0, self.clip_coef)
         self.clip_coef = None
         for u in self.units:
+            u._written.clear()          # the next backward pass starts a new sum
             u.start_gather(epoch=self._step)
 
     # ------------------------------------------------------------------ checkpoint

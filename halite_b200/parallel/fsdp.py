@@ -218,7 +218,10 @@ class FlatUnit:
                 p.grad = None
             elif id(p) not in self._written:
                 p._hb_grad.zero_()
-        self._written.clear()
+                self._written.add(id(p))
+        # `_written` stays set until the optimizer has consumed the gradients (or `zero_grad`):
+        # a further backward pass of the same step (micro-batches) accumulates into the buffer and
+        # the reduction below then runs again on the running sum
         # parameters replicated over tensor-parallel ranks saw only this rank's token shard
         for m, n, _, off, numel in self.entries:
             p = m._parameters[n]

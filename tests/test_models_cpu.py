@@ -162,3 +162,32 @@ def test_activation_checkpointing_same_grads(zoo):
     model(x).logits.square().mean().backward()
     for a, p in zip(g0, model.parameters()):
         assert torch.allclose(a, p.grad, atol=1e-6)
+
+
+def test_micro_batches_accumulate_in_every_sharding_unit(zoo):
+    """Several backward passes before one optimizer step (PPO micro-batches): the flat gradient
+    buffers of the block units and of the root unit hold the sum, and the optimizer step starts
+    a new sum."""
+    from halite_b200.optim import build_optimizer
+    from halite_b200.parallel import parallelize
+
+    torch.manual_seed(0)
+    model = parallelize(instantiate(tiny_llama_conf(zoo, n_layers=2)), param_dtype="float32",
+                        reduce_dtype="float32", device="cpu")
+    model.init_weights("cpu")
+    opt = build_optimizer(partial(torch.optim.AdamW, lr=0.0), model, weight_decay=0.0)
+    a, b = torch.randint(0, 1024, (2, 16)), torch.randint(0, 1024, (2, 16))
+
+    def grads(batches):
+        opt.zero_grad()
+        for x in batches:
+            model(x).logits.float().logsumexp(-1).sum().backward()
+        model._hb_fsdp.finish_backward()
+        return [u.full_grad.clone() for u in model._hb_fsdp.units]
+
+    ga, gb, gab = grads([a]), grads([b]), grads([a, b])
+    for x, y, z in zip(ga, gb, gab):
+        torch.testing.assert_close(z, x + y, atol=1e-5, rtol=1e-5)
+    opt.step()                                   # consumes the sum (learning rate 0: weights unchanged)
+    for x, z in zip(ga, grads([a])):
+        torch.testing.assert_close(z, x, atol=1e-6, rtol=1e-6)
