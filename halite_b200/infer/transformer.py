@@ -87,6 +87,15 @@ class InferTransformerDecoder(nn.Module, ModelMixin):
         if self.pos_embed is not None:
             pos_emb = self.pos_embed(forward_batch.positions, forward_batch.max_seq_len, None,
                                      out.device, out.dtype)
+        from halite_b200.nn.normalization import RMSNorm
+
+        fused = isinstance(self.post_blocks, RMSNorm) and self.post_blocks.weight is not None and \
+            all(getattr(b, "fuses_residual", lambda: False)() for b in self.blocks.values())
+        if fused:
+            residual = None
+            for block in self.blocks.values():
+                out, residual = block.forward_fused(out, residual, forward_batch, pos_emb)
+            return self.post_blocks(out, residual)[0] if residual is not None else self.post_blocks(out)
         for block in self.blocks.values():
             out = block(out, forward_batch, pos_emb)
         if self.post_blocks is not None:
