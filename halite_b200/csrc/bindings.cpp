@@ -86,6 +86,24 @@ bool fill_scatter(const c10::optional<py::dict>& d, hb::ScatterParams& sp) {
   return true;
 }
 
+// Grouped (mixture-of-experts) description from a Python dict (see hb::GroupParams).
+bool fill_group(const c10::optional<py::dict>& d, hb::GroupParams& gq) {
+  if (!d.has_value()) return false;
+  const py::dict& g = *d;
+  gq.mode = g["mode"].cast<int>();
+  if (gq.mode == 1) {
+    gq.tile_group = reinterpret_cast<const int*>(g["tile_group_ptr"].cast<int64_t>());
+    gq.b_group_rows = g["b_group_rows"].cast<int64_t>();
+    gq.b_total_rows = g["b_total_rows"].cast<int64_t>();
+  } else {
+    gq.n_groups = g["n_groups"].cast<int>();
+    gq.k_begin = reinterpret_cast<const int*>(g["k_begin_ptr"].cast<int64_t>());
+    gq.k_end = reinterpret_cast<const int*>(g["k_end_ptr"].cast<int64_t>());
+    gq.d_group_elems = g["d_group_elems"].cast<int64_t>();
+  }
+  return true;
+}
+
 void signal_flags(const std::vector<int64_t>& ptrs, int64_t epoch) {
   cudaError_t e = hb::signal_flags(ptrs.data(), (int)ptrs.size(), (int)epoch, cur_stream());
   TORCH_CHECK(e == cudaSuccess, "signal_flags failed: ", cudaGetErrorString(e));
@@ -104,21 +122,29 @@ void wait_flags(const at::Tensor& flags, int64_t epoch, const c10::optional<at::
 void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& out, bool a_mn, bool b_mn,
           bool accumulate, int64_t block_n, int64_t max_ctas,
           const c10::optional<at::Tensor>& status, const c10::optional<py::dict>& gather,
-          const c10::optional<py::dict>& scatter) {
+          const c10::optional<py::dict>& scatter, const c10::optional<py::dict>& group) {
   HB_CHECK_CUDA(a); HB_CHECK_CUDA(b); HB_CHECK_CUDA(out);
   HB_CHECK_BF16(a); HB_CHECK_BF16(b);
-  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && out.dim() == 2, "gemm wants 2-D tensors");
-  TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && out.stride(1) == 1,
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && (out.dim() == 2 || group.has_value()), "gemm wants 2-D tensors");
+  TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && out.stride(-1) == 1,
               "gemm wants unit inner stride");
   TORCH_CHECK(out.scalar_type() == at::kBFloat16 || out.scalar_type() == at::kFloat,
               "gemm output must be bf16 or fp32");
   const int64_t M = a_mn ? a.size(1) : a.size(0);
   const int64_t K = a_mn ? a.size(0) : a.size(1);
-  const int64_t N = b_mn ? b.size(1) : b.size(0);
-  const int64_t Kb = b_mn ? b.size(0) : b.size(1);
+  int64_t N = b_mn ? b.size(1) : b.size(0);
+  int64_t Kb = b_mn ? b.size(0) : b.size(1);
+  hb::GroupParams gq;
+  const bool grouped = fill_group(group, gq);
+  if (grouped && gq.mode == 1) {
+    // B stacks the groups along its rows: one group's share is the GEMM's N (K-major) or K (MN-major)
+    if (b_mn) Kb = gq.b_group_rows; else N = gq.b_group_rows;
+  }
   TORCH_CHECK(K == Kb, "gemm inner dimensions differ: ", K, " vs ", Kb);
   if (scatter.has_value()) {
     TORCH_CHECK(out.size(1) == N && out.is_contiguous(), "scatter mode wants a contiguous [rows, N] partial buffer");
+  } else if (group.has_value()) {
+    TORCH_CHECK(out.size(-1) == N && out.is_contiguous(), "grouped mode wants a contiguous output with N columns");
   } else {
     TORCH_CHECK(out.size(0) == M && out.size(1) == N, "gemm output shape mismatch");
   }
@@ -126,7 +152,8 @@ void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& out, bool a_mn, 
   hb::GemmArgs g;
   g.a = a.data_ptr(); g.b = b.data_ptr(); g.d = out.data_ptr();
   g.M = (int)M; g.N = (int)N; g.K = (int)K;
-  g.lda = (int)a.stride(0); g.ldb = (int)b.stride(0); g.ldd = (int)out.stride(0);
+  g.lda = (int)a.stride(0); g.ldb = (int)b.stride(0); g.ldd = (int)out.stride(-2);
+  if (grouped) g.group = &gq;
   g.a_mn_major = a_mn; g.b_mn_major = b_mn;
   g.out_f32 = out.scalar_type() == at::kFloat;
   g.accumulate = accumulate;
@@ -156,7 +183,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, "bf16 tcgen05 GEMM", py::arg("a"), py::arg("b"), py::arg("out"),
         py::arg("a_mn") = false, py::arg("b_mn") = false, py::arg("accumulate") = false,
         py::arg("block_n") = 0, py::arg("max_ctas") = 0, py::arg("status") = py::none(),
-        py::arg("gather") = py::none(), py::arg("scatter") = py::none());
+        py::arg("gather") = py::none(), py::arg("scatter") = py::none(), py::arg("group") = py::none());
   m.def("gemm_set_dynamic_schedule", [](bool on, bool force) { hb::gemm_set_dynamic_schedule(on, force); },
         "CTA-pair GEMM: hand work items out through a counter (true) or in fixed shares (false)",
         py::arg("on"), py::arg("force") = false);

@@ -67,6 +67,26 @@ struct ScatterParams {
   int m_rot = 0;                    // first M tile to compute (start on a peer's rows so they travel early)
 };
 
+// Grouped GEMM (mixture-of-experts layers): one launch covers every expert, with the tile table on
+// the device so the host never needs the per-expert token counts.
+//   mode 1 (forward, dgrad): A / D rows are laid out expert by expert, every expert's block padded
+//     to a multiple of 128 rows, so each 128-row tile belongs to one expert: `tile_group[tile]`
+//     (-1: no expert, the tile is skipped). B stacks the experts' matrices along its row
+//     dimension (`b_group_rows` rows each, `b_total_rows` in all).
+//   mode 2 (wgrad): D[e] = A[rows of e]^T B[rows of e] for every expert e; the K range of expert e is
+//     rows [k_begin[e], k_end[e]) (multiples of 64, padding rows are zero), outputs are
+//     `d_group_elems` apart. GemmArgs::K is the total number of rows.
+struct GroupParams {
+  int mode = 0;
+  const int* tile_group = nullptr;
+  long b_group_rows = 0;
+  long b_total_rows = 0;
+  int n_groups = 0;
+  const int* k_begin = nullptr;
+  const int* k_end = nullptr;
+  long d_group_elems = 0;
+};
+
 struct GemmArgs {
   const void* a = nullptr;  // bf16
   const void* b = nullptr;  // bf16
@@ -82,6 +102,7 @@ struct GemmArgs {
   int* status = nullptr;    // device int: set to a WaitCode when a bounded wait gave up
   const GatherParams* gather = nullptr;  // optional fused gather (see above)
   const ScatterParams* scatter = nullptr;  // optional fused reduce-scatter (bf16 output only)
+  const GroupParams* group = nullptr;      // optional grouped mode (single-CTA kernel, no split / collectives)
   cudaStream_t stream = nullptr;
 };
 

@@ -486,7 +486,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
                  int K, int ldd, int accumulate, int* __restrict__ status,
                  const __grid_constant__ GatherParams gp,
                  const __grid_constant__ ScatterParams sp,
-                 const __grid_constant__ SplitParams kp) {
+                 const __grid_constant__ SplitParams kp,
+                 const __grid_constant__ GroupParams gq) {
   using C = Cfg<BN>;
   constexpr int kStages = C::kStages;
 
@@ -532,8 +533,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
 
   // With a fused gather the first `n_copy` CTAs only copy; the rest share the tiles.
   const int m_rot = gp.m_rot + sp.m_rot;
-  const int n_items = kp.parts > 1 ? kp.items : num_tiles;
+  const int n_items = kp.parts > 1 ? kp.items : (gq.mode == 2 ? num_tiles * gq.n_groups : num_tiles);
   const int n_copy = gp.n_copy_ctas;
+  // Grouped launches: work item -> (tile, K range, operand / output offsets); false = nothing to do.
+  auto grouped = [&](int w, WorkItem& it, int& tm, int& tn, long& b_rows, long& d_off) -> bool {
+    b_rows = 0;
+    d_off = 0;
+    if (gq.mode == 2) {
+      const int e = w / num_tiles;
+      it.tile = w - e * num_tiles;
+      it.kb_begin = gq.k_begin[e] >> 6;
+      it.kb_end = gq.k_end[e] >> 6;
+      d_off = static_cast<long>(e) * gq.d_group_elems;
+      if (it.kb_end <= it.kb_begin) return false;
+    }
+    tile_coords(it.tile, tiles_m, tiles_n, tm, tn);
+    if (gq.mode == 1) {
+      const int g = gq.tile_group[tm];
+      if (g < 0) return false;
+      b_rows = static_cast<long>(g) * gq.b_group_rows;
+    }
+    return true;
+  };
   const int first_tile = static_cast<int>(blockIdx.x) - n_copy;
   const int tile_step = static_cast<int>(gridDim.x) - n_copy;
 
@@ -546,11 +567,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
     uint32_t phase = 0;
     bool ok = true;
     for (int w = first_tile; w < n_items && ok; w += tile_step) {
-      const WorkItem it = decode_item(kp, w, num_kb);
+      WorkItem it = decode_item(kp, w, num_kb);
       int tm, tn;
-      tile_coords(it.tile, tiles_m, tiles_n, tm, tn);
+      long b_rows = 0, d_off = 0;
+      if (gq.mode) {
+        if (!grouped(w, it, tm, tn, b_rows, d_off)) continue;
+      } else {
+        tile_coords(it.tile, tiles_m, tiles_n, tm, tn);
+      }
       if (m_rot) tm = (tm + m_rot) % tiles_m;
       const int m0 = tm * kBM, n0 = tn * BN;
+      const int bq = static_cast<int>(b_rows);
       if (gp.dep == 1) ok = wait_rows(gp, m0, kBM, M, &abort_flag, status);
       if (gp.dep == 2) ok = wait_rows(gp, n0, BN, N, &abort_flag, status);
       if (!ok) break;
@@ -586,10 +613,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
           for (int c = 0; c < kBM / 64; ++c) tma_load_2d(sa + c * 8192, &tma_a, full, m0 + c * 64, k0);
         }
         if (!B_MN) {
-          tma_load_2d(sb, &tma_b, full, k0, n0);
+          tma_load_2d(sb, &tma_b, full, k0, n0 + bq);
         } else {
 #pragma unroll
-          for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * 8192, &tma_b, full, n0 + c * 64, k0);
+          for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * 8192, &tma_b, full, n0 + c * 64, k0 + bq);
         }
         if (++stage == kStages) {
           stage = 0;
@@ -605,7 +632,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
     int local = 0;
     bool ok = true;
     for (int w = first_tile; w < n_items && ok; w += tile_step, ++local) {
-      const WorkItem it = decode_item(kp, w, num_kb);
+      WorkItem it = decode_item(kp, w, num_kb);
+      if (gq.mode) {
+        int tm, tn;
+        long b_rows, d_off;
+        if (!grouped(w, it, tm, tn, b_rows, d_off)) {
+          --local;       // skipped items use no accumulator
+          continue;
+        }
+      }
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       ok = mbar_wait(smem_u32(&bar_tempty[acc]), acc_phase ^ 1, &abort_flag, status,
@@ -645,9 +680,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
     int local = 0;
     bool ok = true;
     for (int w = first_tile; w < n_items && ok; w += tile_step, ++local) {
-      const WorkItem it = decode_item(kp, w, num_kb);
+      WorkItem it = decode_item(kp, w, num_kb);
       int tm, tn;
-      tile_coords(it.tile, tiles_m, tiles_n, tm, tn);
+      long b_rows = 0, d_off = 0;
+      if (gq.mode) {
+        if (!grouped(w, it, tm, tn, b_rows, d_off)) {
+          --local;
+          continue;
+        }
+      } else {
+        tile_coords(it.tile, tiles_m, tiles_n, tm, tn);
+      }
       if (m_rot) tm = (tm + m_rot) % tiles_m;
       const int m0 = tm * kBM, n0 = tn * BN;
       const int acc = local & 1;
@@ -658,7 +701,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
       const uint32_t tempty = smem_u32(&bar_tempty[acc]);
-      drain_quarter<BN, OutT>(taddr, smem_base + kStages * C::kStageBytes, D, M, N, ldd, accumulate != 0, vec_ok,
+      drain_quarter<BN, OutT>(taddr, smem_base + kStages * C::kStageBytes, D + d_off, M, N, ldd, accumulate != 0, vec_ok,
                               staged_epilogue, m0, n0, q, lane, sp, kp, it.part, it.tail_index, [&]() {
                                 if (lane == 0) mbar_arrive(tempty);
                               });
@@ -1379,8 +1422,25 @@ cudaError_t launch(const GemmArgs& g) {
   if (!A_MN) ok = make_tmap_bf16_2d(&ta, g.a, g.M, g.K, g.lda, kBM, kBK);
   else       ok = make_tmap_bf16_2d(&ta, g.a, g.K, g.M, g.lda, kBK, 64);
   if (!ok) return cudaErrorInvalidPitchValue;
-  if (!B_MN) ok = make_tmap_bf16_2d(&tb, g.b, g.N, g.K, g.ldb, BN, kBK);
-  else       ok = make_tmap_bf16_2d(&tb, g.b, g.K, g.N, g.ldb, kBK, 64);
+  GroupParams gq;
+  if (g.group) {
+    gq = *g.group;
+    if (g.gather || g.scatter) return cudaErrorInvalidValue;
+    if (gq.mode == 1) {
+      // a K-major B is addressed by (k, n + group * N): rows past N would belong to the next expert, which is
+      // harmless (masked columns); an MN-major B is addressed by (n, k + group * K), so K must fill whole k-blocks
+      if (!gq.tile_group || gq.b_group_rows <= 0 || gq.b_total_rows <= 0 || (B_MN && g.K % kBK)) return cudaErrorInvalidValue;
+    } else if (gq.mode == 2) {
+      if (!A_MN || !B_MN || !gq.k_begin || !gq.k_end || gq.n_groups <= 0 || gq.d_group_elems % 8)
+        return cudaErrorInvalidValue;
+    } else {
+      return cudaErrorInvalidValue;
+    }
+  }
+  const uint64_t b_rows = (gq.mode == 1) ? static_cast<uint64_t>(gq.b_total_rows)
+                                         : static_cast<uint64_t>(B_MN ? g.K : g.N);
+  if (!B_MN) ok = make_tmap_bf16_2d(&tb, g.b, b_rows, g.K, g.ldb, BN, kBK);
+  else       ok = make_tmap_bf16_2d(&tb, g.b, b_rows, g.N, g.ldb, kBK, 64);
   if (!ok) return cudaErrorInvalidPitchValue;
 
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, OutT>;
@@ -1395,7 +1455,8 @@ cudaError_t launch(const GemmArgs& g) {
     attr_set = true;
   }
   (void)cudaGetLastError();  // do not report an error left behind by an earlier, unrelated call
-  const int tiles = ((g.M + kBM - 1) / kBM) * ((g.N + BN - 1) / BN);
+  int tiles = ((g.M + kBM - 1) / kBM) * ((g.N + BN - 1) / BN);
+  if (gq.mode == 2) tiles *= gq.n_groups;
   GatherParams gp;
   if (g.gather) gp = *g.gather;
   int grid;
@@ -1414,7 +1475,7 @@ cudaError_t launch(const GemmArgs& g) {
   }
   SplitParams kp;
   kp.prefetch = l2_prefetch_distance();
-  if (!g.gather && !g.scatter) {
+  if (!g.gather && !g.scatter && !g.group) {
     // cut the tiles of a mostly idle last wave along K (see SplitParams)
     const int base = (g.max_ctas > 0 && g.max_ctas < sm_count()) ? g.max_ctas : sm_count();
     const int num_kb = (g.K + kBK - 1) / kBK;
@@ -1453,7 +1514,7 @@ cudaError_t launch(const GemmArgs& g) {
     cudaMemsetAsync(sp.cta_counter, 0, sizeof(int), g.stream);
   }
   kern<<<grid, kThreads, C::kSmemBytes, g.stream>>>(ta, tb, static_cast<OutT*>(g.d), g.M, g.N, g.K,
-                                                    g.ldd, g.accumulate ? 1 : 0, g.status, gp, sp, kp);
+                                                    g.ldd, g.accumulate ? 1 : 0, g.status, gp, sp, kp, gq);
   return cudaGetLastError();
 }
 
@@ -1744,9 +1805,9 @@ cudaError_t gemm_bf16(const GemmArgs& g) {
   if ((reinterpret_cast<uintptr_t>(g.a) & 15) || (reinterpret_cast<uintptr_t>(g.b) & 15) ||
       (g.lda % 8) || (g.ldb % 8))
     return cudaErrorInvalidValue;
-  const bool plain = !g.gather && !g.scatter && g.max_ctas == 0;
+  const bool plain = !g.gather && !g.scatter && !g.group && g.max_ctas == 0;
   // the pair kernel also hosts copy / reduce jobs that no tile depends on
-  const bool pairable = plain || (g.gather && !g.scatter && g.max_ctas == 0 && g.gather->dep == 0 &&
+  const bool pairable = plain || (g.gather && !g.scatter && !g.group && g.max_ctas == 0 && g.gather->dep == 0 &&
                                   g.gather->n_copy_ctas % 2 == 0);
   if (g.block_n == kPairBlockN && !pairable) return cudaErrorInvalidValue;
   bool pair = g.block_n == kPairBlockN;

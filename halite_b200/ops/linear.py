@@ -19,7 +19,7 @@ from halite_b200.utils import probe as _probe
 
 
 def gemm(a, b, out=None, a_mn=False, b_mn=False, accumulate=False, out_dtype=None, block_n=0,
-         max_ctas=0, gather=None, scatter=None):
+         max_ctas=0, gather=None, scatter=None, group=None):
     """out[M,N] (+)= op(a) @ op(b)^T on the sm_100a kernel.
 
     a: [M,K] (or [K,M] when a_mn); b: [N,K] (or [K,N] when b_mn); all bf16, row-major with
@@ -30,7 +30,7 @@ def gemm(a, b, out=None, a_mn=False, b_mn=False, accumulate=False, out_dtype=Non
     if out is None:
         out = torch.empty(M, N, device=a.device, dtype=out_dtype or torch.bfloat16)
     ops.ext().gemm(a, b, out, a_mn, b_mn, accumulate, block_n, max_ctas, ops.status_word(a.device),
-                   gather, scatter)
+                   gather, scatter, group)
     return out
 
 

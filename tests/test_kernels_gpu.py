@@ -448,3 +448,45 @@ def test_packed_qkv_attention_matches_eager(C):
     ref.backward(g.float())
     assert rel_err(out, ref) < 2e-2
     assert rel_err(qkv.grad, qr.grad) < 3e-2
+
+
+def test_moe_experts_padded_grouped_path_matches_reference(C, monkeypatch):
+    """Expert feed-forward on the grouped GEMM modes (device-side tile table, no host sync) against
+    the per-expert reference path of the same weights: output and all gradients, with an expert
+    that receives no token and with dropped slots."""
+    from halite_b200.models.moe.experts import ExpertLinear, FeedForward
+    from halite_b200.nn.activation import SwiGLU
+
+    torch.manual_seed(8)
+    E, dim, inter, top_k, T = 6, 128, 192, 2, 300
+    ff = FeedForward(ExpertLinear(E, dim, 2 * inter), SwiGLU(), ExpertLinear(E, inter, dim), top_k).cuda().bfloat16()
+    ff.init_weights()
+    with torch.no_grad():
+        ff.linear1.weight.mul_(3)
+        ff.linear2.weight.mul_(3)
+    x = torch.randn(T, dim, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    idx = torch.randint(0, E - 1, (T, top_k), device="cuda")           # expert E-1 never chosen
+    idx[::17, 1] = E                                                    # dropped slots
+    probs = torch.rand(T, top_k, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    g = torch.randn(T, dim, device="cuda", dtype=torch.bfloat16)
+
+    def run():
+        for t in (x, probs, ff.linear1.weight, ff.linear2.weight):
+            t.grad = None
+        out = ff(x, probs, idx)
+        out.backward(g)
+        return out.detach().float(), [t.grad.float() for t in (x, probs, ff.linear1.weight, ff.linear2.weight)]
+
+    out, grads = run()
+    torch.cuda.synchronize()
+    torch.cuda.set_sync_debug_mode("error")        # the grouped path must not wait for the device anywhere
+    try:
+        run()
+    finally:
+        torch.cuda.set_sync_debug_mode("default")
+    monkeypatch.setenv("HALITE_B200_FORCE_REFERENCE", "1")
+    out_r, grads_r = run()
+    assert rel_err(out, out_r) < 2e-2
+    for a, b in zip(grads, grads_r):
+        assert rel_err(a, b) < 3e-2
+    assert grads[2][E - 1].abs().max() == 0 and grads[3][E - 1].abs().max() == 0
