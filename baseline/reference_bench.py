@@ -33,7 +33,7 @@ def _unavailable(reason: str):
 
 def run(args):
     if not os.path.isdir(os.path.join(REF, "halite")):
-        _unavailable("baseline/_ref/halite is missing (pip install --target baseline/_ref /root/reference was not run)")
+        _unavailable("baseline/_ref/halite is missing (the reference was not installed with pip --target baseline/_ref)")
         return
     try:
         _run(args)

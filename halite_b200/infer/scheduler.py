@@ -166,7 +166,7 @@ class Scheduler:
             if not adder.add(req):
                 if req not in adder.can_run:
                     break
-                # admitted as a partial chunk: nothing more fits this round
+                # admitted as a partial chunk: nothing more fits in this batch
                 break
         if not adder.can_run:
             return None
