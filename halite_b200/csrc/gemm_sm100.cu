@@ -530,6 +530,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
+  pdl_trigger();
+  pdl_wait();      // nothing above reads or writes global memory
 
   // With a fused gather the first `n_copy` CTAs only copy; the rest share the tiles.
   const int m_rot = gp.m_rot + sp.m_rot;
@@ -1154,6 +1156,8 @@ gemm_bf16_ksplit_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
+  pdl_trigger();
+  pdl_wait();      // nothing above reads or writes global memory
 
   if (warp == 0 && lane == 0) {
     // ------------------------------------------------------------ producer
@@ -1273,6 +1277,16 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// Programmatic dependent launch of the plain single-CTA and split-K launches (HB_GEMM_PDL=0: off).
+bool pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* env = getenv("HB_GEMM_PDL");
+    on = (env && env[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
 
 constexpr int kDefaultL2Prefetch = 0;
 // k-blocks of L2 prefetch issued ahead of the pipeline (HB_GEMM_L2_PREFETCH overrides; 0 = off).
@@ -1513,6 +1527,22 @@ cudaError_t launch(const GemmArgs& g) {
       return cudaErrorInvalidValue;
     cudaMemsetAsync(sp.cta_counter, 0, sizeof(int), g.stream);
   }
+  if (!g.gather && !g.scatter && !g.group && kp.parts <= 1 && pdl_enabled()) {
+    // plain launch with nothing enqueued in front of it (no counter memset): let it start under
+    // the previous kernel's tail
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cfg.stream = g.stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, ta, tb, static_cast<OutT*>(g.d), g.M, g.N, g.K, g.ldd,
+                              g.accumulate ? 1 : 0, g.status, gp, sp, kp, gq);
+  }
   kern<<<grid, kThreads, C::kSmemBytes, g.stream>>>(ta, tb, static_cast<OutT*>(g.d), g.M, g.N, g.K,
                                                     g.ldd, g.accumulate ? 1 : 0, g.status, gp, sp, kp, gq);
   return cudaGetLastError();
@@ -1668,13 +1698,15 @@ cudaError_t launch_ksplit(const GemmArgs& g, int split) {
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = C::kSmemBytes;
   cfg.stream = g.stream;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = split;
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
+  cudaLaunchAttribute attrs[2];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = split;
+  attrs[0].val.clusterDim.y = 1;
+  attrs[0].val.clusterDim.z = 1;
+  attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attrs[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attrs;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   return cudaLaunchKernelEx(&cfg, kern, ta, tb, static_cast<OutT*>(g.d), g.M, g.N, g.K, g.ldd,
                             g.accumulate ? 1 : 0, split, g.status);
 }

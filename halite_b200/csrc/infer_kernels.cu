@@ -42,6 +42,7 @@ __global__ void rope_append_kernel(__nv_bfloat16* __restrict__ q, const __nv_bfl
                                    const int64_t* __restrict__ out_loc, int hq, int hk, int dim,
                                    int rot, long q_stride, long k_stride, long v_stride,
                                    int interleaved, long cache_slots) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // a dependent launch may set itself up under this kernel
   const long t = blockIdx.x;
   const long slot = out_loc[t];
   const bool slot_ok = slot >= 0 && slot < cache_slots;
@@ -130,6 +131,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   using S = DecodeSmem<D>;
   constexpr int TILE = S::kTile;
   constexpr int ROW = S::kRow;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // a dependent launch may set itself up under this kernel
   extern __shared__ __align__(16) unsigned char decode_smem_raw[];
   __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(decode_smem_raw);
   constexpr int NT = kDecodeThreads;
@@ -352,6 +354,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 template <int D>
 __global__ void decode_merge_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ out,
                                     int splits) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // a dependent launch may set itself up under this kernel
   const long bh = blockIdx.x;
   const float* w = ws + bh * splits * (D + 2);
   float M = -INFINITY;

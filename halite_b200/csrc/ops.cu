@@ -194,6 +194,7 @@ rmsnorm_fwd_row_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
                        __nv_bfloat16* __restrict__ h_out, float* __restrict__ rstd_out, int dim, float eps,
                        float w_offset) {
   __shared__ float red[4];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // a dependent launch may set itself up under this kernel
   const long row = blockIdx.x;
   const int nvec = dim >> 3;
   const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * dim);
@@ -486,6 +487,7 @@ __global__ void gated_fwd_kernel(const __nv_bfloat16* __restrict__ gate,
                                  const __nv_bfloat16* __restrict__ up,
                                  __nv_bfloat16* __restrict__ out, long nvec, int row_vec,
                                  long gate_ld, long up_ld, int kind) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // a dependent launch may set itself up under this kernel
   for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < nvec;
        i += static_cast<long>(gridDim.x) * blockDim.x) {
     const long r = i / row_vec;

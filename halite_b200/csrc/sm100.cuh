@@ -39,6 +39,15 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
   return t;
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-serialization attribute may start while the previous
+// kernel of the stream is still running: everything before `pdl_wait()` (barrier set-up, tensor
+// memory allocation, descriptor prefetch) overlaps that kernel's tail, and no global memory is
+// touched before it. `pdl_trigger()` in the earlier kernel lets the next one start that early.
+// Both are no-ops for launches without the attribute / without a dependent.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
