@@ -996,8 +996,16 @@ cudaError_t rope_apply(const void* src, void* dst, const float* cos, const float
 #undef HB_ROPE_VEC
     return cudaGetLastError();
   }
-  // narrow fallback: in place only
-  if (!in_place || rot_dim % 4 != 0 || head_dim % 4 != 0 || src_stride % 4 != 0 || rot_dim == 0)
+  // narrow fallback (rotation widths the 16-byte kernel does not cover): works in place, so an
+  // out-of-place call first copies the rows over
+  if (!in_place) {
+    cudaError_t e = cudaMemcpy2DAsync(dst, static_cast<size_t>(dst_stride) * 2, src, static_cast<size_t>(src_stride) * 2,
+                                      static_cast<size_t>(heads) * head_dim * 2, tokens, cudaMemcpyDeviceToDevice,
+                                      stream);
+    if (e != cudaSuccess) return e;
+    if (rot_dim == 0) return cudaSuccess;
+  }
+  if (rot_dim % 4 != 0 || head_dim % 4 != 0 || dst_stride % 4 != 0 || rot_dim == 0)
     return cudaErrorInvalidValue;
   const long total = static_cast<long>(tokens) * heads * (rot_dim / 4);
   const int grid = grid_for(total, 256);

@@ -90,7 +90,10 @@ class _LinearFn(torch.autograd.Function):
 
 
 def linear(x, weight, bias=None):
-    if ops.use_sm100(x) and weight.dtype == torch.bfloat16:
+    # the kernel wants 16-byte rows in every layout it reads the operands in (forward, dgrad, wgrad):
+    # both weight dimensions must be multiples of 8, otherwise the library path runs
+    if ops.use_sm100(x) and weight.dtype == torch.bfloat16 and weight.shape[0] % 8 == 0 \
+            and weight.shape[1] % 8 == 0 and x.dtype == torch.bfloat16:
         out = _LinearFn.apply(x, weight, bias)
     else:
         out = F.linear(x, weight, bias)

@@ -226,6 +226,14 @@ def test_rope_on_slices_of_a_fused_projection(C, interleaved):
 
     torch.manual_seed(6)
     T, H, Hk, D, rot = 300, 6, 2, 64, 32
+    _rope_on_slices(interleaved, T, H, Hk, D, rot)
+    _rope_on_slices(interleaved, 77, 4, 4, 16, 8)        # narrow rotation: the 4-element kernel after a row copy
+
+
+def _rope_on_slices(interleaved, T, H, Hk, D, rot):
+    from halite_b200 import ops
+    from halite_b200.ops.rope import apply_rope_reference, rope_tables
+
     inv = 1.0 / (10000 ** (torch.arange(0, rot, 2).float() / rot))
     cos, sin = rope_tables(inv, 256, "cuda")
     pos = torch.randint(0, 256, (1, T), device="cuda")

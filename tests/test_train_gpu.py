@@ -148,3 +148,34 @@ def test_moe_decoder_trains_on_the_grouped_gemm_path():
         losses.append(float(out["loss_dict"]["cross entropy"]))
         assert "router-z-loss" in out["loss_dict"] or "load-balance-loss" in out["loss_dict"]
     assert losses[-1] < losses[0] - 0.5, losses
+
+
+def test_hnet_runs_in_bf16_on_the_kernel_path():
+    """Two-stage H-Net (Mamba-2 encoder / decoder blocks, attention main network) sharded in bf16:
+    forward, ratio losses, backward and a few update steps on the GPU kernels."""
+    from halite_b200.conf import instantiate, load_config
+    from halite_b200.nn.loss import CrossEntropyLoss
+    from halite_b200.optim import build_optimizer
+    from halite_b200.parallel import ParallelDims, parallelize
+    from halite_b200.projects.common.train_fn import optimization_step
+
+    dev = torch.device("cuda", 0)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    conf = load_config(os.path.join(root, "configs/lm/hnet.py"), "stage2_tiny")
+    torch.manual_seed(0)
+    with torch.device("meta"):
+        model = instantiate(conf.model.model)
+    pd = ParallelDims(dp_shard=1, world_size=1)
+    pd.build_mesh("cuda")
+    model = parallelize(model, pd, pd, param_dtype="bfloat16", device=dev)
+    model.init_weights(dev)
+    opt = build_optimizer(partial(torch.optim.AdamW, lr=3e-3), model, weight_decay=0.0)
+    pattern = torch.arange(64, device=dev) % 7
+    ids = torch.stack([(pattern + k) % 256 for k in range(4)])
+    losses = []
+    for _ in range(20):
+        out = optimization_step(model, {"input": ids[:, :-1], "target": ids[:, 1:]}, opt,
+                                criterion=CrossEntropyLoss(), clip_grad_norm=1.0)
+        losses.append(float(out["loss_dict"]["cross entropy"]))
+        assert "ratio_loss" in out["loss_dict"]
+    assert losses[-1] < 0.7 * losses[0], losses
