@@ -153,7 +153,8 @@ class _SelfAttentionBase(nn.Module):
 
     def _packed_ok(self, input, attention_mask, attention_bias, pos_emb, cache, use_cache, unpad):
         a = self.attention
-        return (ops.use_sm100(input) and attention_mask is None and attention_bias is None
+        return (type(a) is Attention                     # subclasses (differential attention) have their own core
+                and ops.use_sm100(input) and attention_mask is None and attention_bias is None
                 and cache is None and not use_cache and unpad is None
                 and a.q_norm is None and a.k_norm is None and not a.softcap and a.window_size is None
                 and a.processor != "native" and self.scaler is None
@@ -288,8 +289,8 @@ class SelfAttentionQKV(_SelfAttentionBase):
                 self._packed_ok(input, attention_mask, attention_bias, pos_emb, cache, use_cache, unpad_params):
             return self._packed_forward(input, fused, None, pos_emb), None
         if fused is not None and ops.use_sm100(input):
-            H, Hk, D = self.n_heads, self.n_key_value_heads, self.head_dim
-            q, k, v = ops.linear(input, fused).split((H * D, Hk * D, Hk * D), -1)
+            q, k, v = ops.linear(input, fused).split(
+                (self.q.weight.shape[0], self.k.weight.shape[0], self.v.weight.shape[0]), -1)
         else:
             q = ops.linear(input, self.q.weight, self.q.bias)
             k = ops.linear(input, self.k.weight, self.k.bias)

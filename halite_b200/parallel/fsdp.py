@@ -676,13 +676,21 @@ def apply_fsdp(model, mesh=None, param_dtype=torch.bfloat16, reduce_dtype=torch.
 
     model.block_hooks = (pre_block, post_block)
 
+    def _to_param_dtype(value):
+        if torch.is_tensor(value) and value.is_floating_point() and value.dtype != param_dtype:
+            return value.to(param_dtype)
+        return value
+
     def root_pre_forward(module, args, kwargs):
         root.pre_forward()
         if not calls_block_hooks:
             # this model's forward does not announce its blocks: every unit must be whole now
             for u in units:
                 u.pre_forward()
-        return None
+        if param_dtype == torch.float32:
+            return None
+        # floating-point inputs (images, diffusion times, soft tokens) enter in the parameter dtype
+        return tuple(_to_param_dtype(a) for a in args), {k: _to_param_dtype(v) for k, v in kwargs.items()}
 
     model.register_forward_pre_hook(root_pre_forward, with_kwargs=True)
     if fused_all_gather is None:
