@@ -107,6 +107,8 @@ class ModelRunner:
     def cleanup(self):
         """Give the device memory back (weights and pools) so training can use it."""
         self.model.to("meta")
+        if hasattr(self.model, "set_kv_pool"):
+            self.model.set_kv_pool(None)       # the attention layers hold the pool too
         self.req_pool = None
         self.kv_pool = None
         self.graphs = {}

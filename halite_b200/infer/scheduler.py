@@ -69,6 +69,10 @@ class Scheduler:
         self.running_batch = None
         self.chunked_req = None
         self.tree_cache = None
+        self.last_tokens = None
+        # the pools belong to the model runner; a reference kept here would keep their memory
+        self.req_pool = None
+        self.kv_pool = None
 
     # ------------------------------------------------------------------ requests
     def build_batch_request(self, requests):

@@ -29,9 +29,22 @@ def gemm(a, b, out=None, a_mn=False, b_mn=False, accumulate=False, out_dtype=Non
     N = b.shape[1] if b_mn else b.shape[0]
     if out is None:
         out = torch.empty(M, N, device=a.device, dtype=out_dtype or torch.bfloat16)
+    if gather is None and scatter is None and group is None and not (_tma_ready(a) and _tma_ready(b)):
+        # rows that are not 16-byte multiples (a vocabulary of 260, say): the library computes it
+        prod = torch.matmul((a.t() if a_mn else a).float(), (b if b_mn else b.t()).float())
+        if accumulate:
+            out += prod.to(out.dtype)
+        else:
+            out.copy_(prod)
+        return out
     ops.ext().gemm(a, b, out, a_mn, b_mn, accumulate, block_n, max_ctas, ops.status_word(a.device),
                    gather, scatter, group)
     return out
+
+
+def _tma_ready(t):
+    """What a TMA descriptor over a 2-D operand needs: unit inner stride, 16-byte base and rows."""
+    return t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0
 
 
 def _as_2d(x):

@@ -21,8 +21,12 @@ def fused_adamw_step(master, exp_avg, exp_avg_sq, grad, param_lowp, lr, betas, e
     """Decoupled-weight-decay Adam on an fp32 master shard; `param_lowp` (bf16 copy) is
     refreshed in the same pass. Order of operations matches `torch.optim.AdamW`."""
     if master.is_cuda and not ops.force_reference():
-        ops.ext().adamw_(master, exp_avg, exp_avg_sq, grad, param_lowp, lr, betas[0], betas[1], eps,
+        # the kernel refreshes a bf16 copy; parameters kept in another dtype are copied afterwards
+        lowp = param_lowp if param_lowp is not None and param_lowp.dtype == torch.bfloat16 else None
+        ops.ext().adamw_(master, exp_avg, exp_avg_sq, grad, lowp, lr, betas[0], betas[1], eps,
                          weight_decay, step, grad_scale, grad_scale_t)
+        if param_lowp is not None and lowp is None:
+            param_lowp.copy_(master)
         return
     g = grad.float() * grad_scale
     if grad_scale_t is not None:

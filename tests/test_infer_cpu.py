@@ -119,9 +119,13 @@ def test_stop_token_and_lifecycle(zoo):
                                                         "stop_token_ids": [stop]})])[0]
     assert cut.output_ids[0] == base.output_ids[0][: first + 1] and cut.finish_reason == ["stop"]
     # hand the memory back and take it again, with the same weights reloaded
+    import weakref
+
     sd = model.state_dict()
+    pool = weakref.ref(eng.model_runner.kv_pool)
     eng.cleanup()
     assert eng.model_runner.kv_pool is None
+    assert pool() is None                     # scheduler and attention layers let go of it too
     eng.initialize()
     eng.load_state_dict(sd)
     again = eng.infer_batch([InferenceRequest(2, prompt, {"max_new_tokens": 12, "top_k": 1})])[0]
