@@ -1114,4 +1114,66 @@ cudaError_t gae(const float* rewards, const float* values, const float* mask, fl
   return cudaGetLastError();
 }
 
+// ---- first-order linear recurrence over a packed row -------------------------------------------
+// h[t] = a[t] * h[prev] + b[t] * x[t] inside each sequence [cu[s], cu[s+1]) of a packed row, with
+// h = 0 before a sequence's first step; REVERSE walks each sequence from its last token down.
+// One thread owns one channel of one sequence: the recurrence is serial in t, the loads are not,
+// so eight steps of x, a and b are fetched before the eight dependent FMAs run.
+template <typename T> __device__ __forceinline__ float scan_load(const T* p);
+template <> __device__ __forceinline__ float scan_load<float>(const float* p) { return __ldg(p); }
+template <> __device__ __forceinline__ float scan_load<__nv_bfloat16>(const __nv_bfloat16* p) {
+  return __bfloat162float(*p);
+}
+
+template <typename T, bool REVERSE>
+__global__ void __launch_bounds__(128)
+linear_scan_kernel(const T* __restrict__ x, const float* __restrict__ a, const float* __restrict__ b,
+                   const int* __restrict__ cu, float* __restrict__ out, int dim) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= dim) return;
+  const int lo = cu[blockIdx.y], hi = cu[blockIdx.y + 1];
+  const int n = hi - lo;
+  constexpr int U = 8;
+  float h = 0.f;
+  for (int i = 0; i < n; i += U) {
+    float xv[U], av[U], bv[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int k = i + u;
+      if (k < n) {
+        const int t = REVERSE ? hi - 1 - k : lo + k;
+        xv[u] = scan_load(x + (long)t * dim + c);
+        av[u] = __ldg(a + t);
+        bv[u] = __ldg(b + t);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int k = i + u;
+      if (k < n) {
+        const int t = REVERSE ? hi - 1 - k : lo + k;
+        h = fmaf(av[u], h, bv[u] * xv[u]);
+        out[(long)t * dim + c] = h;
+      }
+    }
+  }
+}
+
+cudaError_t linear_scan(const void* x, bool x_bf16, const float* a, const float* b, const int* cu_seqlens,
+                        int n_seqs, int dim, bool reverse, float* out, cudaStream_t stream) {
+  if (n_seqs == 0 || dim == 0) return cudaSuccess;
+  if (n_seqs > 65535) return cudaErrorInvalidValue;
+  const dim3 grid((dim + 127) / 128, n_seqs);
+  if (x_bf16) {
+    auto xp = static_cast<const __nv_bfloat16*>(x);
+    if (reverse) linear_scan_kernel<__nv_bfloat16, true><<<grid, 128, 0, stream>>>(xp, a, b, cu_seqlens, out, dim);
+    else linear_scan_kernel<__nv_bfloat16, false><<<grid, 128, 0, stream>>>(xp, a, b, cu_seqlens, out, dim);
+  } else {
+    auto xp = static_cast<const float*>(x);
+    if (reverse) linear_scan_kernel<float, true><<<grid, 128, 0, stream>>>(xp, a, b, cu_seqlens, out, dim);
+    else linear_scan_kernel<float, false><<<grid, 128, 0, stream>>>(xp, a, b, cu_seqlens, out, dim);
+  }
+  return cudaGetLastError();
+}
+
 }  // namespace hb

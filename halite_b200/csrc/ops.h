@@ -118,4 +118,11 @@ cudaError_t cast_bf16_to_f32(const void* src, float* dst, long n, float scale, b
 cudaError_t gae(const float* rewards, const float* values, const float* mask, float* adv,
                 float* ret, int B, int T, float gamma, float lam, cudaStream_t stream);
 
+// ---- linear recurrence h[t] = a[t] * h[t-1] + b[t] * x[t] over each sequence of a packed row
+// x[total, dim] (bf16 or fp32), a, b [total] fp32, cu_seqlens [n_seqs + 1] int32, out [total, dim] fp32;
+// `reverse` runs every sequence from its last token to its first (the adjoint recurrence). Replaces the
+// borrowed mamba-ssm scan of the reference's H-Net dechunk (transformers/models/hnet.py:112).
+cudaError_t linear_scan(const void* x, bool x_bf16, const float* a, const float* b, const int* cu_seqlens,
+                        int n_seqs, int dim, bool reverse, float* out, cudaStream_t stream);
+
 }  // namespace hb

@@ -359,6 +359,25 @@ std::tuple<at::Tensor, at::Tensor> gae(const at::Tensor& rewards, const at::Tens
   return {adv, ret};
 }
 
+// out[t] = a[t] * out[t -/+ 1] + b[t] * x[t] within each sequence of the packed row x[total, dim].
+at::Tensor linear_scan(const at::Tensor& x, const at::Tensor& a, const at::Tensor& b, const at::Tensor& cu_seqlens,
+                       bool reverse) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous() &&
+                  (x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kFloat),
+              "x must be a contiguous CUDA bf16/fp32 [total, dim]");
+  check_f32(a, "a");
+  check_f32(b, "b");
+  TORCH_CHECK(a.numel() == x.size(0) && b.numel() == x.size(0), "a and b hold one coefficient per row of x");
+  TORCH_CHECK(cu_seqlens.is_cuda() && cu_seqlens.is_contiguous() && cu_seqlens.scalar_type() == at::kInt &&
+                  cu_seqlens.numel() >= 1, "cu_seqlens must be contiguous CUDA int32");
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor out = at::empty(x.sizes(), x.options().dtype(at::kFloat));
+  HB_CUDA_OK(hb::linear_scan(x.data_ptr(), x.scalar_type() == at::kBFloat16, a.data_ptr<float>(),
+                             b.data_ptr<float>(), cu_seqlens.data_ptr<int>(), (int)cu_seqlens.numel() - 1,
+                             (int)x.size(1), reverse, out.data_ptr<float>(), cur_stream()));
+  return out;
+}
+
 }  // namespace
 
 void register_elementwise(pybind11::module_& m) {
@@ -395,4 +414,6 @@ void register_elementwise(pybind11::module_& m) {
         py::arg("accumulate") = false);
   m.def("gae", &gae, py::arg("rewards"), py::arg("values"), py::arg("mask") = py::none(),
         py::arg("gamma") = 1.0, py::arg("lam") = 0.95);
+  m.def("linear_scan", &linear_scan, py::arg("x"), py::arg("a"), py::arg("b"), py::arg("cu_seqlens"),
+        py::arg("reverse") = false);
 }

@@ -7,9 +7,10 @@ probability) -> `chunk` (keep boundary tokens) -> the next stage on the shorter 
 stands for) -> straight-through residual -> decoder blocks. The innermost stage is a plain block
 stack. Everything runs on one packed row [1, total, dim] described by `cu_seqlens`.
 
-The reference's dechunk borrows mamba-ssm's fused scan; here the EMA is the same chunked scan
-the Mamba-2 mixer uses (`ssd_scan`), with A = -1, dt = log(1 / (1 - p)), B = p, C = 1 and the
-input divided by dt, which reduces to  h_t = (1 - p_t) h_{t-1} + p_t x_t.
+The reference's dechunk borrows mamba-ssm's fused scan. On a GPU the EMA here is a recurrence
+kernel of its own (`ops/scan.py:ema_scan`); on CPU it is the same chunked scan the Mamba-2 mixer
+uses (`ssd_scan`), with A = -1, dt = log(1 / (1 - p)), B = p, C = 1 and the input divided by dt,
+which reduces to  h_t = (1 - p_t) h_{t-1} + p_t x_t.
 """
 
 from __future__ import annotations
@@ -21,7 +22,9 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
+from ... import ops
 from ...nn.normalization import RMSNorm
+from ...ops.scan import ema_scan
 from ..feedforward import _project
 from ..block import ResidualBlock, TransformerEncoderBlock
 from ..generation import GenerationMixin
@@ -99,6 +102,11 @@ def dechunk(input: torch.Tensor, boundary_mask: torch.Tensor, boundary_prob: tor
     chunked row (`input` [1, kept, dim]); the result is [1, total, dim]."""
     p = torch.clamp(boundary_prob[..., -1].float(), 1e-4, 1 - 1e-4)[boundary_mask][None]      # [1, kept]
     kept, dim = input.shape[1], input.shape[2]
+    plug_back = boundary_mask.cumsum(0) - 1
+    if input.is_cuda and not ops.force_reference():
+        # one recurrence kernel per direction instead of the chunked formulation
+        out = ema_scan(input[0], p[0], cu_seqlens)[None]
+        return out[:, plug_back].to(input.dtype)
     seq_idx = get_seq_idx(cu_seqlens, device=input.device, total=kept)
     dt = torch.log(1 / (1 - p))
     x = (input.float() / dt[..., None]).to(dtype)
@@ -107,7 +115,6 @@ def dechunk(input: torch.Tensor, boundary_mask: torch.Tensor, boundary_prob: tor
                       p.to(dtype).view(1, kept, 1, 1), torch.ones(1, kept, 1, 1, device=input.device, dtype=dtype),
                       chunk_size=block_size, seq_idx=seq_idx)
     out = out.reshape(1, kept, dim)
-    plug_back = boundary_mask.cumsum(0) - 1
     return out[:, plug_back].to(input.dtype)
 
 

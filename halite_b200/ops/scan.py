@@ -1,0 +1,72 @@
+"""First-order recurrences over packed rows.
+
+`linear_scan`  h[t] = a[t] * h[t-1] + b[t] * x[t]  inside every sequence of a packed row (h = 0
+before a sequence's first token), forward in time or, with `reverse`, from each sequence's last
+token down to its first, which is the adjoint of the forward recurrence.
+
+`ema_scan`  h[t] = (1 - p[t]) * h[t-1] + p[t] * x[t]: the smoothing the H-Net dechunk applies to the
+chunk vectors, with gradients for x and p. The reference gets it from mamba-ssm's chunked-scan
+Triton kernel (transformers/models/hnet.py:88-131: A = -1, dt = log(1 / (1 - p)), B = p, C = 1);
+here it is one CUDA kernel per direction (`linear_scan_kernel` in csrc/ops.cu) and a handful of
+elementwise ops for the two gradients:
+
+    adj[t] = g[t] + (1 - p[t+1]) * adj[t+1]          (reverse scan of the incoming gradient)
+    dx[t]  = p[t] * adj[t]
+    dp[t]  = sum_c adj[t, c] * (x[t, c] - h[t-1, c])
+"""
+
+from __future__ import annotations
+
+import torch
+
+from halite_b200 import ops
+
+
+def _linear_scan_reference(x, a, b, cu_seqlens, reverse=False):
+    """Plain PyTorch: a loop over time, vectorised over channels (CPU path and test oracle)."""
+    out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+    xf, bounds = x.float(), cu_seqlens.tolist()
+    for lo, hi in zip(bounds[:-1], bounds[1:]):
+        h = torch.zeros(x.shape[1], dtype=torch.float32, device=x.device)
+        steps = range(hi - 1, lo - 1, -1) if reverse else range(lo, hi)
+        for t in steps:
+            h = a[t] * h + b[t] * xf[t]
+            out[t] = h
+    return out
+
+
+def linear_scan(x, a, b, cu_seqlens, reverse=False):
+    """x [total, dim] (bf16 or fp32), a, b [total] fp32, cu_seqlens [n + 1] -> fp32 [total, dim]."""
+    if x.is_cuda and not ops.force_reference():
+        return ops.ext().linear_scan(x.contiguous(), a.float().contiguous(), b.float().contiguous(),
+                                     cu_seqlens.to(device=x.device, dtype=torch.int32).contiguous(), reverse)
+    return _linear_scan_reference(x, a.float(), b.float(), cu_seqlens, reverse)
+
+
+class _EmaScanFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, p, cu_seqlens):
+        p = p.float()
+        h = linear_scan(x, 1 - p, p, cu_seqlens)
+        ctx.save_for_backward(x, p, h, cu_seqlens)
+        return h
+
+    @staticmethod
+    def backward(ctx, g):
+        x, p, h, cu = ctx.saved_tensors
+        total = x.shape[0]
+        carry = torch.roll(1 - p, -1)                      # carry[t] = 1 - p[t+1]; unused at a sequence's end
+        adj = linear_scan(g.contiguous(), carry, torch.ones_like(p), cu, reverse=True)
+        # h[t-1], with zeros where a sequence starts (one spare row takes the start marker of an
+        # empty trailing sequence)
+        h_prev = h.new_zeros(total + 1, h.shape[1])
+        h_prev[1:total] = h[: total - 1]
+        h_prev.index_fill_(0, cu[:-1].to(device=h.device, dtype=torch.long), 0.0)
+        dx = (p[:, None] * adj).to(x.dtype) if ctx.needs_input_grad[0] else None
+        dp = (adj * (x.float() - h_prev[:total])).sum(-1) if ctx.needs_input_grad[1] else None
+        return dx, dp, None
+
+
+def ema_scan(x, p, cu_seqlens):
+    """h[t] = (1 - p[t]) h[t-1] + p[t] x[t] per sequence: x [total, dim], p [total] -> fp32 [total, dim]."""
+    return _EmaScanFn.apply(x, p, cu_seqlens)

@@ -187,3 +187,30 @@ def test_hnet_through_sharded_optimisation_step():
         first = last if first is None else first
         assert "ratio_loss" in res["loss_dict"]
     assert last < 0.5 * first
+
+
+def test_ema_scan_matches_a_plain_loop_with_gradients():
+    """The recurrence front-end (CPU path of `ops/scan.py`) against a naive float64 loop: values and
+    both gradients, over sequences of length 4, 1 and 6 in one packed row."""
+    from halite_b200.ops.scan import ema_scan
+
+    torch.manual_seed(0)
+    total, dim = 11, 5
+    cu = torch.tensor([0, 4, 5, 11])
+    x = torch.randn(total, dim, dtype=torch.float64, requires_grad=True)
+    p = torch.rand(total, dtype=torch.float64).clamp(0.05, 0.95).requires_grad_()
+    w = torch.randn(total, dim, dtype=torch.float64)
+    rows = []
+    for lo, hi in zip(cu.tolist()[:-1], cu.tolist()[1:]):
+        h = torch.zeros(dim, dtype=torch.float64)
+        for t in range(lo, hi):
+            h = (1 - p[t]) * h + p[t] * x[t]
+            rows.append(h)
+    ref = torch.stack(rows)
+    (ref * w).sum().backward()
+    xf, pf = x.detach().float().requires_grad_(), p.detach().float().requires_grad_()
+    out = ema_scan(xf, pf, cu)
+    (out * w.float()).sum().backward()
+    torch.testing.assert_close(out, ref.float(), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(xf.grad, x.grad.float(), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(pf.grad, p.grad.float(), rtol=1e-5, atol=1e-5)

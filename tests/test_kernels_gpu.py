@@ -498,3 +498,63 @@ def test_moe_experts_padded_grouped_path_matches_reference(C, monkeypatch):
     for a, b in zip(grads, grads_r):
         assert rel_err(a, b) < 3e-2
     assert grads[2][E - 1].abs().max() == 0 and grads[3][E - 1].abs().max() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("reverse", [False, True])
+def test_linear_scan_kernel_matches_a_plain_loop(dtype, reverse):
+    """h[t] = a[t] h[t-1] + b[t] x[t] per sequence of a packed row: lengths 1, 7, 8, 9 and 275 (the
+    kernel fetches eight steps at a time), 200 channels (not a multiple of the CTA width)."""
+    from halite_b200.ops.scan import _linear_scan_reference, linear_scan
+
+    torch.manual_seed(0)
+    cu = torch.tensor([0, 1, 8, 16, 25, 300], device="cuda", dtype=torch.int32)
+    x = torch.randn(300, 200, device="cuda").to(dtype)
+    a = torch.rand(300, device="cuda")
+    b = torch.rand(300, device="cuda")
+    out = linear_scan(x, a, b, cu, reverse=reverse)
+    ref = _linear_scan_reference(x.cpu(), a.cpu(), b.cpu(), cu.cpu(), reverse)
+    torch.testing.assert_close(out.cpu(), ref, rtol=1e-5, atol=1e-5)
+
+
+def test_ema_scan_gradients_and_dechunk_match_the_chunked_formulation(monkeypatch):
+    """`ema_scan` on the GPU against its PyTorch path on CPU (values, dx, dp), then the H-Net dechunk
+    with the kernel against the chunked-scan formulation it replaces."""
+    from halite_b200.models.models.hnet import dechunk
+    from halite_b200.ops.scan import ema_scan
+
+    torch.manual_seed(1)
+    cu = torch.tensor([0, 40, 41, 150])
+    x = torch.randn(150, 96)
+    p = torch.rand(150).clamp(0.05, 0.95)
+    w = torch.randn(150, 96)
+    got = []
+    for dev in ("cpu", "cuda"):
+        xd, pd = x.clone().to(dev).requires_grad_(), p.clone().to(dev).requires_grad_()
+        out = ema_scan(xd, pd, cu.to(dev))
+        (out * w.to(dev)).sum().backward()
+        got.append((out.detach().cpu(), xd.grad.cpu(), pd.grad.cpu()))
+    for c, g in zip(*got):
+        torch.testing.assert_close(g, c, rtol=1e-4, atol=1e-4)
+
+    # dechunk: 3 sequences of 64 tokens, every fourth token (and each first) a boundary
+    total = 192
+    mask = torch.zeros(total, dtype=torch.bool, device="cuda")
+    mask[::4] = True
+    prob = torch.rand(total, device="cuda").clamp(0.1, 0.9)
+    prob[::64] = 1.0
+    bp = torch.stack((1 - prob, prob), -1)
+    kept = int(mask.sum())
+    cu_kept = torch.tensor([0, 16, 32, 48], device="cuda", dtype=torch.int32)
+    inp = torch.randn(1, kept, 64, device="cuda", dtype=torch.bfloat16)
+    outs = []
+    for force in ("0", "1"):
+        monkeypatch.setenv("HALITE_B200_FORCE_REFERENCE", force)
+        xi, bi = inp.clone().requires_grad_(), bp.clone().requires_grad_()
+        o = dechunk(xi, mask, bi, cu_kept)
+        o.float().square().sum().backward()
+        outs.append((o.detach().float(), xi.grad.float(), bi.grad[:, 1]))
+    assert outs[0][0].shape == (1, total, 64)
+    torch.testing.assert_close(outs[0][0], outs[1][0], rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(outs[0][1], outs[1][1], rtol=5e-2, atol=5e-2)
+    torch.testing.assert_close(outs[0][2], outs[1][2], rtol=5e-2, atol=5e-2)
