@@ -11,22 +11,30 @@ namespace hb {
 
 namespace {
 
+// Eight bf16 values as one 16-byte word. The member is a plain uint4 so that copying the struct
+// is a single 128-bit load or store (a struct of __nv_bfloat162 members is copied member by member:
+// four 32-bit accesses, four times the load/store wavefronts for the same bytes).
 struct alignas(16) bf16x8 {
-  __nv_bfloat162 v[4];
+  uint4 u;
 };
 
 __device__ __forceinline__ void unpack8(const bf16x8& p, float (&f)[8]) {
+  const uint32_t w[4] = {p.u.x, p.u.y, p.u.z, p.u.w};
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    float2 t = __bfloat1622float2(p.v[i]);
-    f[2 * i] = t.x;
-    f[2 * i + 1] = t.y;
+    f[2 * i] = __uint_as_float(w[i] << 16);              // low half: element 2i
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);  // high half: element 2i + 1
   }
 }
 __device__ __forceinline__ bf16x8 pack8(const float (&f)[8]) {
-  bf16x8 p;
+  uint32_t w[4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) p.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 t = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&t);
+  }
+  bf16x8 p;
+  p.u = make_uint4(w[0], w[1], w[2], w[3]);
   return p;
 }
 
@@ -1122,7 +1130,7 @@ cudaError_t gae(const float* rewards, const float* values, const float* mask, fl
 template <typename T> __device__ __forceinline__ float scan_load(const T* p);
 template <> __device__ __forceinline__ float scan_load<float>(const float* p) { return __ldg(p); }
 template <> __device__ __forceinline__ float scan_load<__nv_bfloat16>(const __nv_bfloat16* p) {
-  return __bfloat162float(*p);
+  return __uint_as_float(static_cast<uint32_t>(__ldg(reinterpret_cast<const unsigned short*>(p))) << 16);
 }
 
 template <typename T, bool REVERSE>

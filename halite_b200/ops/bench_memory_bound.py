@@ -46,6 +46,9 @@ def main(argv=None):
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--ema-seqs", type=int, default=16, help="sequences in the packed row of the EMA cases")
+    ap.add_argument("--ema-len", type=int, default=1024, help="chunk vectors per sequence in the EMA cases")
+    ap.add_argument("--ema-dim", type=int, default=1536)
     args = ap.parse_args(argv)
     dev = "cuda"
     C = ops.ext()
@@ -88,6 +91,28 @@ def main(argv=None):
     gate, up, dout = (torch.randn(T, FF, device=dev, dtype=bf) for _ in range(3))
     cases.append(("swiglu_fwd", lambda: gated_act(gate, up, "silu"), 3 * T * FF * 2))
     cases.append(("swiglu_bwd", lambda: C.gated_act_bwd(gate, up, dout, 0, None, None), 5 * T * FF * 2))
+
+    # the H-Net dechunk EMA: the recurrence kernel and, for its time only, the chunked formulation
+    from halite_b200.models.models.mamba2 import ssd_scan
+    from halite_b200.ops.scan import linear_scan
+
+    S, L, De = args.ema_seqs, args.ema_len, args.ema_dim
+    ex = torch.randn(S * L, De, device=dev, dtype=bf)
+    ep = torch.rand(S * L, device=dev).clamp(0.05, 0.95)
+    eq, one = 1 - ep, torch.ones_like(ep)
+    eg = torch.randn(S * L, De, device=dev)
+    cu = torch.arange(0, S * L + 1, L, device=dev, dtype=torch.int32)
+    seq_idx = torch.arange(S, device=dev, dtype=torch.int32).repeat_interleave(L)[None]
+    cases.append(("ema_scan_fwd", lambda: linear_scan(ex, eq, ep, cu), S * L * De * 6))
+    cases.append(("ema_scan_adjoint", lambda: linear_scan(eg, eq, one, cu, reverse=True), S * L * De * 8))
+
+    def chunked():
+        dt = torch.log(1 / eq)[None]
+        xs = (ex.float()[None] / dt[..., None]).view(1, S * L, 1, De)
+        return ssd_scan(xs, dt[..., None], -torch.ones(1, device=dev), ep.view(1, -1, 1, 1),
+                        torch.ones(1, S * L, 1, 1, device=dev), chunk_size=64, seq_idx=seq_idx)[0]
+
+    cases.append(("ema_chunked_formulation_fwd", chunked, S * L * De * 6))
 
     for name, fn, nbytes in cases:
         ms = _time(fn, args.iters, flush)
