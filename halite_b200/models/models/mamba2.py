@@ -4,8 +4,9 @@ configs/models/hnet.py:89-95, transformers/models/hnet.py:104-121).
 
 Recurrence per head: h_t = exp(A dt_t) h_{t-1} + dt_t B_t x_t^T,  y_t = C_t h_t + D x_t.
 `ssd_scan` evaluates it chunk by chunk: inside a chunk the output is a masked, decay-weighted
-(C B^T) X product; between chunks a small state is carried. Sequences packed into one row are
-kept apart by `seq_idx` (no decay path across a sequence boundary).
+(C B^T) X product (batched matrix products); between chunks a small state is carried, on a GPU by
+one recurrence kernel over the chunk axis (`ops/scan.py:linear_scan_autograd`), on CPU by a loop.
+Sequences packed into one row are kept apart by `seq_idx` (no decay path across a sequence boundary).
 """
 
 from __future__ import annotations
@@ -16,7 +17,14 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
+from ... import ops
+from ...ops.scan import linear_scan_autograd
 from ..feedforward import _project
+
+
+def _scan_kernel_for(x):
+    """Whether the chunk-to-chunk state passing runs on the recurrence kernel (CUDA tensors)."""
+    return x.is_cuda and not ops.force_reference()
 
 
 def _segsum(x):
@@ -61,28 +69,38 @@ def ssd_scan(x, dt, A, B, C, chunk_size=64, seq_idx=None, initial_state=None):
         last = s[:, :, -1:]
         decay_to_end = decay_to_end * (s == last)[:, None].to(f32)
     states = torch.einsum("bcshn,bhcs,bcshp->bchpn", Bc, decay_to_end, xs)
-    # ---- carry states across chunks
-    if initial_state is None:
-        initial_state = states.new_zeros(b, H, P, N)
-    carried = [initial_state]
+    # ---- carry states across chunks: carried[c + 1] = carried[c] * keep[c] + states[c]
     chunk_decay = torch.exp(a_cum[..., -1])                                                 # [b,H,nc]
-    for c in range(nc):
-        keep = chunk_decay[:, :, c]
-        if seq_idx is not None:
-            # the carried state survives a chunk only if the chunk ends in the sequence it began in
-            cont = (s[:, c, 0] == s[:, c, -1]).to(f32)[:, None]
-            if c > 0:
-                cont = cont * (s[:, c, 0] == s[:, c - 1, -1]).to(f32)[:, None]
-            keep = keep * cont
-        carried.append(carried[-1] * keep[..., None, None] + states[:, c])
-    prev = torch.stack(carried[:-1], 1)                                                     # state entering chunk c
+    keep = chunk_decay
+    if seq_idx is not None:
+        # the carried state survives a chunk only if the chunk ends in the sequence it began in
+        # and began in the sequence the previous chunk ended in
+        cont = s[:, :, 0] == s[:, :, -1]                                                    # [b,nc]
+        cont = cont & torch.cat((torch.ones_like(cont[:, :1]), s[:, 1:, 0] == s[:, :-1, -1]), 1)
+        keep = keep * cont.to(f32)[:, None]
+    if initial_state is None and _scan_kernel_for(x):
+        # one recurrence kernel over the chunk axis: a row per (batch, head, chunk), P*N channels
+        rows = states.permute(0, 2, 1, 3, 4).reshape(b * H * nc, P * N)
+        cu = torch.arange(0, b * H * nc + 1, nc, device=x.device, dtype=torch.int32)
+        after = linear_scan_autograd(rows, keep.reshape(-1), torch.ones(b * H * nc, device=x.device), cu)
+        after = after.view(b, H, nc, P, N)
+        prev = F.pad(after[:, :, :-1], (0, 0, 0, 0, 1, 0)).permute(0, 2, 1, 3, 4)           # state entering chunk c
+        final_state = after[:, :, -1]
+    else:
+        if initial_state is None:
+            initial_state = states.new_zeros(b, H, P, N)
+        carried = [initial_state]
+        for c in range(nc):
+            carried.append(carried[-1] * keep[:, :, c, None, None] + states[:, c])
+        prev = torch.stack(carried[:-1], 1)                                                 # state entering chunk c
+        final_state = carried[-1]
     decay_from_start = torch.exp(a_cum)                                                     # [b,H,nc,Q]
     if seq_idx is not None:
         first_prev = torch.cat((s[:, :1, :1], s[:, :-1, -1:]), 1)                           # seq of the carried state
         decay_from_start = decay_from_start * (s == first_prev)[:, None].to(f32)
     y_off = torch.einsum("bclhn,bchpn,bhcl->bclhp", Cc, prev, decay_from_start)
     y = (y_diag + y_off).reshape(b, Lp, H, P)[:, :L]
-    return y.to(x.dtype), carried[-1]
+    return y.to(x.dtype), final_state
 
 
 class GatedRMSNorm(nn.Module):

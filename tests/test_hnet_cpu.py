@@ -4,6 +4,7 @@ steps from the config file."""
 
 import os
 
+import pytest
 import torch
 import torch.nn.functional as F
 
@@ -214,3 +215,34 @@ def test_ema_scan_matches_a_plain_loop_with_gradients():
     torch.testing.assert_close(out, ref.float(), rtol=1e-5, atol=1e-6)
     torch.testing.assert_close(xf.grad, x.grad.float(), rtol=1e-5, atol=1e-6)
     torch.testing.assert_close(pf.grad, p.grad.float(), rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("packed", [False, True])
+def test_ssd_scan_state_passing_by_recurrence_matches_the_chunk_loop(monkeypatch, packed):
+    """The chunk-to-chunk carry of `ssd_scan` as one linear recurrence over the chunk axis (the GPU
+    form, here on the PyTorch path of the scan op) against the per-chunk loop: output, final state
+    and every gradient."""
+    import halite_b200.models.models.mamba2 as m
+
+    b, L, H, P, G, N = 2, 192, 4, 8, 2, 16
+    seq = None
+    if packed:
+        seq = torch.zeros(b, L, dtype=torch.int32)
+        seq[:, 70:] = 1
+        seq[:, 130:] = 2
+        seq[1, 150:] = 3
+
+    def run(use_scan):
+        monkeypatch.setattr(m, "_scan_kernel_for", lambda x: use_scan)
+        torch.manual_seed(0)
+        ins = [torch.randn(b, L, H, P), torch.rand(b, L, H) * 0.5 + 0.01, -torch.rand(H) - 0.1,
+               torch.randn(b, L, G, N), torch.randn(b, L, G, N)]
+        ins = [t.requires_grad_() for t in ins]
+        y, state = m.ssd_scan(*ins, chunk_size=64, seq_idx=seq)
+        (y.square().sum() + state.square().sum()).backward()
+        return [y.detach(), state.detach()] + [t.grad for t in ins]
+
+    loop, scan = run(False), run(True)
+    assert loop[1].abs().max() > 0
+    for a, c in zip(loop, scan):
+        torch.testing.assert_close(c, a, rtol=1e-5, atol=1e-5)

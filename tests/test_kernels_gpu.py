@@ -558,3 +558,27 @@ def test_ema_scan_gradients_and_dechunk_match_the_chunked_formulation(monkeypatc
     torch.testing.assert_close(outs[0][0], outs[1][0], rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(outs[0][1], outs[1][1], rtol=5e-2, atol=5e-2)
     torch.testing.assert_close(outs[0][2], outs[1][2], rtol=5e-2, atol=5e-2)
+
+
+def test_ssd_scan_state_passing_on_the_recurrence_kernel(monkeypatch):
+    """Mamba-2 chunked scan on the GPU: the chunk-to-chunk carry on `linear_scan_kernel` against
+    the per-chunk loop (the forced reference path), packed sequences, values and gradients."""
+    from halite_b200.models.models.mamba2 import ssd_scan
+
+    b, L, H, P, G, N = 2, 512, 4, 32, 2, 32
+    seq = torch.zeros(b, L, dtype=torch.int32, device="cuda")
+    seq[:, 200:] = 1
+    seq[1, 300:] = 2
+    outs = []
+    for force in ("1", "0"):
+        monkeypatch.setenv("HALITE_B200_FORCE_REFERENCE", force)
+        torch.manual_seed(0)
+        ins = [torch.randn(b, L, H, P, device="cuda"), torch.rand(b, L, H, device="cuda") * 0.5 + 0.01,
+               -torch.rand(H, device="cuda") - 0.1, torch.randn(b, L, G, N, device="cuda"),
+               torch.randn(b, L, G, N, device="cuda")]
+        ins = [t.requires_grad_() for t in ins]
+        y, state = ssd_scan(*ins, chunk_size=64, seq_idx=seq)
+        (y.square().mean() + state.square().mean()).backward()
+        outs.append([y.detach(), state.detach()] + [t.grad for t in ins])
+    for ref, got in zip(*outs):
+        torch.testing.assert_close(got, ref, rtol=2e-3, atol=2e-3)
