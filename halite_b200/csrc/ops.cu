@@ -412,62 +412,83 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restri
 
 // 16-byte variant, optionally out of place (src and dst may have different token strides, e.g.
 // a contiguous gradient rotated into its slot of a packed qkv gradient). One thread per
-// (token, head, 8 elements); elements past rot_dim are copied when src != dst.
+// (token, group of `hpt` heads, 8 elements): the thread reads its slice of the token's cos/sin row
+// once and walks the heads of its group with it (hpt = 1: one thread per head; hpt = heads: the
+// tables are read once per token instead of once per head). Elements past rot_dim are copied when
+// src != dst.
 template <typename PosT, bool INTERLEAVED>
 __global__ void rope_vec_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst,
                                 const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                 const PosT* __restrict__ pos, int tokens, int heads, int head_dim,
-                                int rot_dim, long src_stride, long dst_stride, float sign, bool in_place) {
+                                int rot_dim, long src_stride, long dst_stride, float sign, bool in_place,
+                                int hpt) {
   const int half = rot_dim >> 1;
   const int vph = head_dim >> 3;
-  const long total = static_cast<long>(tokens) * heads * vph;
+  const int groups = (heads + hpt - 1) / hpt;
+  const long total = static_cast<long>(tokens) * groups * vph;
   for (long idx = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; idx < total;
        idx += static_cast<long>(gridDim.x) * blockDim.x) {
     const int j = idx % vph;
-    const long th = idx / vph;
-    const int hd = th % heads;
-    const long t = th / heads;
-    const __nv_bfloat16* s = src + t * src_stride + static_cast<long>(hd) * head_dim;
-    __nv_bfloat16* d = dst + t * dst_stride + static_cast<long>(hd) * head_dim;
+    const long tg = idx / vph;
+    const int h0 = (tg % groups) * hpt;
+    const int h1 = min(heads, h0 + hpt);
+    const long t = tg / groups;
+    const __nv_bfloat16* s = src + t * src_stride + 8 * j;
+    __nv_bfloat16* d = dst + t * dst_stride + 8 * j;
     if (INTERLEAVED) {
       if (8 * j < rot_dim) {
         const long p = static_cast<long>(pos[t]);
         const float4 c = *reinterpret_cast<const float4*>(cos_t + p * half + 4 * j);
         const float4 sn = *reinterpret_cast<const float4*>(sin_t + p * half + 4 * j);
-        float f[8], o[8];
-        unpack8(*reinterpret_cast<const bf16x8*>(s + 8 * j), f);
         const float cc[4] = {c.x, c.y, c.z, c.w};
         const float ss[4] = {sn.x * sign, sn.y * sign, sn.z * sign, sn.w * sign};
+#pragma unroll 4
+        for (int hd = h0; hd < h1; ++hd) {
+          float f[8], o[8];
+          unpack8(*reinterpret_cast<const bf16x8*>(s + static_cast<long>(hd) * head_dim), f);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          o[2 * k] = f[2 * k] * cc[k] - f[2 * k + 1] * ss[k];
-          o[2 * k + 1] = f[2 * k] * ss[k] + f[2 * k + 1] * cc[k];
+          for (int k = 0; k < 4; ++k) {
+            o[2 * k] = f[2 * k] * cc[k] - f[2 * k + 1] * ss[k];
+            o[2 * k + 1] = f[2 * k] * ss[k] + f[2 * k + 1] * cc[k];
+          }
+          *reinterpret_cast<bf16x8*>(d + static_cast<long>(hd) * head_dim) = pack8(o);
         }
-        *reinterpret_cast<bf16x8*>(d + 8 * j) = pack8(o);
       } else if (!in_place) {
-        *reinterpret_cast<bf16x8*>(d + 8 * j) = *reinterpret_cast<const bf16x8*>(s + 8 * j);
+#pragma unroll 4
+        for (int hd = h0; hd < h1; ++hd)
+          *reinterpret_cast<bf16x8*>(d + static_cast<long>(hd) * head_dim) =
+              *reinterpret_cast<const bf16x8*>(s + static_cast<long>(hd) * head_dim);
       }
     } else {
       const int hv = half >> 3;
       if (j < hv) {
         const long p = static_cast<long>(pos[t]);
-        float cc[8], ss[8], lo[8], hi[8], olo[8], ohi[8];
+        float cc[8], ss[8];
         *reinterpret_cast<float4*>(cc) = *reinterpret_cast<const float4*>(cos_t + p * half + 8 * j);
         *reinterpret_cast<float4*>(cc + 4) = *reinterpret_cast<const float4*>(cos_t + p * half + 8 * j + 4);
         *reinterpret_cast<float4*>(ss) = *reinterpret_cast<const float4*>(sin_t + p * half + 8 * j);
         *reinterpret_cast<float4*>(ss + 4) = *reinterpret_cast<const float4*>(sin_t + p * half + 8 * j + 4);
-        unpack8(*reinterpret_cast<const bf16x8*>(s + 8 * j), lo);
-        unpack8(*reinterpret_cast<const bf16x8*>(s + half + 8 * j), hi);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const float sk = ss[k] * sign;
-          olo[k] = lo[k] * cc[k] - hi[k] * sk;
-          ohi[k] = hi[k] * cc[k] + lo[k] * sk;
+        for (int k = 0; k < 8; ++k) ss[k] *= sign;
+#pragma unroll 2
+        for (int hd = h0; hd < h1; ++hd) {
+          const long off = static_cast<long>(hd) * head_dim;
+          float lo[8], hi[8], olo[8], ohi[8];
+          unpack8(*reinterpret_cast<const bf16x8*>(s + off), lo);
+          unpack8(*reinterpret_cast<const bf16x8*>(s + off + half), hi);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            olo[k] = lo[k] * cc[k] - hi[k] * ss[k];
+            ohi[k] = hi[k] * cc[k] + lo[k] * ss[k];
+          }
+          *reinterpret_cast<bf16x8*>(d + off) = pack8(olo);
+          *reinterpret_cast<bf16x8*>(d + off + half) = pack8(ohi);
         }
-        *reinterpret_cast<bf16x8*>(d + 8 * j) = pack8(olo);
-        *reinterpret_cast<bf16x8*>(d + half + 8 * j) = pack8(ohi);
       } else if (8 * j >= rot_dim && !in_place) {
-        *reinterpret_cast<bf16x8*>(d + 8 * j) = *reinterpret_cast<const bf16x8*>(s + 8 * j);
+#pragma unroll 4
+        for (int hd = h0; hd < h1; ++hd)
+          *reinterpret_cast<bf16x8*>(d + static_cast<long>(hd) * head_dim) =
+              *reinterpret_cast<const bf16x8*>(s + static_cast<long>(hd) * head_dim);
       }
     }
   }
@@ -989,11 +1010,15 @@ cudaError_t rope_apply(const void* src, void* dst, const float* cos, const float
   auto S = static_cast<const __nv_bfloat16*>(src);
   auto D = static_cast<__nv_bfloat16*>(dst);
   if (vec_ok) {
-    const long total = static_cast<long>(tokens) * heads * (head_dim / 8);
+    // enough tokens to fill the GPU with one thread per (token, 8 elements): that thread walks all
+    // heads with one read of the tables; otherwise one thread per head
+    const int hpt = static_cast<long>(tokens) * (head_dim / 8) >= (1L << 18) ? heads : 1;
+    const long total = static_cast<long>(tokens) * ((heads + hpt - 1) / hpt) * (head_dim / 8);
     const int grid = grid_for(total, 256);
 #define HB_ROPE_VEC(PT, IL)                                                                              \
   rope_vec_kernel<PT, IL><<<grid, 256, 0, stream>>>(S, D, cos, sin, static_cast<const PT*>(positions), tokens, \
-                                                    heads, head_dim, rot_dim, src_stride, dst_stride, sign, in_place)
+                                                    heads, head_dim, rot_dim, src_stride, dst_stride, sign,    \
+                                                    in_place, hpt)
     if (pos_is_i64) {
       if (interleaved) HB_ROPE_VEC(int64_t, true);
       else HB_ROPE_VEC(int64_t, false);

@@ -228,6 +228,10 @@ def test_rope_on_slices_of_a_fused_projection(C, interleaved):
     T, H, Hk, D, rot = 300, 6, 2, 64, 32
     _rope_on_slices(interleaved, T, H, Hk, D, rot)
     _rope_on_slices(interleaved, 77, 4, 4, 16, 8)        # narrow rotation: the 4-element kernel after a row copy
+    # enough tokens for the head-walking form (one thread per token and 8 elements, tables read once
+    # per token): partial and full rotation
+    _rope_on_slices(interleaved, 16400, 3, 2, 128, 64)
+    _rope_on_slices(interleaved, 16400, 2, 1, 128, 128)
 
 
 def _rope_on_slices(interleaved, T, H, Hk, D, rot):
