@@ -174,6 +174,7 @@ def test_shipped_experiment_configs_load_and_validate():
     root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "configs", "lm")
     expect = {"dense_662m.py": (0.55e9, 0.8e9), "dense_1.7b.py": (1.4e9, 2.0e9), "diff_transformer_383m.py": (0.3e9, 0.5e9),
               "moe_383m.py": (1.5e9, 5e9), "ngpt_383m.py": (0.3e9, 0.5e9), "scale_383m_soap.py": (0.3e9, 0.5e9),
+              "scale_383m_shampoo.py": (0.3e9, 0.5e9),
               "dense_scaling.py": (0.3e9, 0.5e9), "diff_transformer_large.py": (0.8e9, 1.1e9),
               "scaling/scale_383m.py": (0.3e9, 0.5e9), "scaling/scale_large.py": (0.8e9, 1.1e9),
               "scaling/moe.py": (1.5e9, 5e9), "stacking/base_900m.py": (0.2e9, 0.4e9),

@@ -1,4 +1,4 @@
-"""SOAP optimizer and the linear-layer Probe."""
+"""SOAP and Shampoo optimizers and the linear-layer Probe."""
 
 import json
 import os
@@ -47,6 +47,56 @@ def test_soap_beats_adam_on_an_ill_conditioned_quadratic():
     for q in opt.state[w]["basis"].Q:
         if q is not None:
             torch.testing.assert_close(q.t() @ q, torch.eye(q.shape[0]), rtol=1e-4, atol=1e-4)
+
+
+def test_shampoo_beats_adam_on_a_rotated_ill_conditioned_quadratic():
+    """A quadratic whose curvature is a Kronecker product of two ill-conditioned, non-diagonal
+    matrices: what Adam's diagonal scaling cannot see and Shampoo's two factors can. Both exponent
+    choices (classic -1/4 per factor, and the override to -1/2), 1-D parameters on the grafted
+    Adam step, decoupled weight decay, and a folded 4-D tensor."""
+    from halite_b200.optim.shampoo import AdamGraftingConfig, Shampoo, _inverse_root
+
+    torch.manual_seed(0)
+    A = torch.randn(32, 32)
+    A = A @ A.t() / 32 + 0.01 * torch.eye(32)
+    Q, _ = torch.linalg.qr(torch.randn(16, 16))
+    B = Q @ torch.diag(torch.logspace(-2, 1, 16)) @ Q.t()
+    target = torch.randn(32, 16)
+
+    def loss_fn(w):
+        return ((A @ (w - target) @ B) ** 2).mean()
+
+    def run(make):
+        w = torch.zeros(32, 16, requires_grad=True)
+        b = torch.zeros(16, requires_grad=True)
+        opt = make([w, b])
+        for _ in range(300):
+            (loss_fn(w) + 0.1 * (b - 1).square().sum()).backward()
+            opt.step()
+            opt.zero_grad()
+        assert (b - 1).abs().max() < 0.2
+        return loss_fn(w).item()
+
+    adam = run(lambda p: torch.optim.Adam(p, lr=3e-2, betas=(0.9, 0.95)))
+    graft = AdamGraftingConfig(beta2=0.95, epsilon=1e-8)
+    for root in (0, 2):
+        shampoo = run(lambda p: Shampoo(p, lr=3e-2, betas=(0.9, 0.95), precondition_frequency=5,
+                                        inv_root_override=root, grafting_config=graft))
+        assert shampoo < 0.4 * adam, (root, shampoo, adam)
+    # the inverse root itself
+    m = torch.randn(6, 6)
+    m = m @ m.t() + torch.eye(6)
+    r = _inverse_root(m, 2, 0.0)
+    torch.testing.assert_close(r @ m @ r, torch.eye(6), rtol=1e-4, atol=1e-4)
+    # decoupled weight decay shrinks a parameter that gets zero gradients; 4-D tensors fold
+    w = torch.ones(4, 3, 3, 3, requires_grad=True)
+    opt = Shampoo([w], lr=0.1, weight_decay=0.5, merge_dims=True, max_preconditioner_dim=30, precondition_frequency=2)
+    for _ in range(4):
+        (w * 0).sum().backward()
+        opt.step()
+        opt.zero_grad()
+    torch.testing.assert_close(w, torch.full_like(w, 0.95 ** 4))
+    assert [None if f is None else tuple(f.shape) for f in opt.state[w]["factors"]] == [(4, 4), (27, 27)]
 
 
 def test_probe_records_linear_statistics_and_gradients(tmp_path):
