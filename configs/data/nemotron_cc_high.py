@@ -1,0 +1,4 @@
+"""Nemotron-CC, the `high` quality tier alone (reference: configs/data/nemotron_cc_high.py, whose shard
+table is site data; here it comes from the `shards.json` index read by `nemotron_cc.py`)."""
+
+from .nemotron_cc import high as conf

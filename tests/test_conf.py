@@ -193,3 +193,10 @@ def test_shipped_experiment_configs_load_and_validate():
     assert instantiate(conf.output.name)(conf.hparams).startswith("202m@lr-0.00781_batch-32")
     small = load_config(os.path.join(root, "scaling", "scale_1.py"), schema=LMConfig)
     assert small.training.train_batch_size == 64
+    # data specs: one file per Nemotron-CC tier plus the 200B sample the MoE run trains on
+    data_root = os.path.join(os.path.dirname(root), "data")
+    tiers = {"high": "high", "medium_high": "medium-high", "medium": "medium", "medium_low": "medium-low", "low": "low"}
+    for stem, source in tiers.items():
+        assert dict(load_config(os.path.join(data_root, f"nemotron_cc_{stem}.py")).ratios) == {source: 1.0}
+    moe = load_config(os.path.join(root, "scaling", "moe.py"), schema=LMConfig)
+    assert dict(moe.data.train.ratios) == {"nemotron-cc": 1.0}
