@@ -10,7 +10,6 @@ step (a MAX all-reduce of a "finished" flag per step).
 from __future__ import annotations
 
 import copy
-import itertools
 import multiprocessing as mp
 import pickle
 import queue as queue_mod

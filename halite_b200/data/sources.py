@@ -11,9 +11,7 @@ from __future__ import annotations
 import bisect
 import dataclasses
 import itertools
-import json
 import mmap
-import os
 import struct
 
 _MAGIC = b"HBREC001"

@@ -21,7 +21,6 @@ from typing import Any
 import torch
 import torch.distributed as dist
 import torch.distributed.checkpoint as dcp
-from torch import nn
 
 from halite_b200.distributed.managers import LRSchedulerManager, ModelManager, OptimizerManager
 from halite_b200.logging import logger

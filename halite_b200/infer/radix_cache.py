@@ -11,7 +11,6 @@ from __future__ import annotations
 
 import heapq
 import time
-from collections import defaultdict
 
 
 class TreeNode:

@@ -9,9 +9,7 @@ steps ahead of the host (see `ModelRunner.decode_steps`).
 
 from __future__ import annotations
 
-import uuid
 
-import torch
 
 from halite_b200.infer.batch import Batch, ForwardMode, Request
 from halite_b200.infer.radix_cache import RadixCache, make_radix_cache  # noqa: F401

@@ -3,13 +3,11 @@ names equal the training decoder's, so a training state dict loads unchanged."""
 
 from __future__ import annotations
 
-import torch
 from torch import nn
 
 from halite_b200.infer.postprocessor import LogitsProcessor
 from halite_b200.models.container import ModuleDict
 from halite_b200.models.model import ModelMixin
-from halite_b200.models.position import RotaryTable
 
 
 class InferTransformerDecoder(nn.Module, ModelMixin):

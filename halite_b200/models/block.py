@@ -4,7 +4,6 @@ from __future__ import annotations
 
 from typing import Any
 
-import torch
 from torch import nn
 
 

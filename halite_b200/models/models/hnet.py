@@ -26,7 +26,7 @@ from ... import ops
 from ...nn.normalization import RMSNorm
 from ...ops.scan import ema_scan
 from ..feedforward import _project
-from ..block import ResidualBlock, TransformerEncoderBlock
+from ..block import TransformerEncoderBlock
 from ..generation import GenerationMixin
 from ..model import ModelMixin
 from ..types import TransformerDecoderOutput, UnpadParams

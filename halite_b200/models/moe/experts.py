@@ -19,7 +19,6 @@ import torch
 from torch import nn
 
 import halite_b200.ops as ops
-from halite_b200.models.initialize import init_weights
 from halite_b200.ops.linear import gemm
 
 

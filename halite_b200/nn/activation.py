@@ -3,13 +3,11 @@ whose last dimension holds the two halves side by side."""
 
 from __future__ import annotations
 
-import math
 
 import torch
 from torch import nn
 import torch.nn.functional as F
 
-from halite_b200 import ops
 from halite_b200.ops.activation import gated_act_packed
 
 

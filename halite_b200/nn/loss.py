@@ -3,7 +3,6 @@ z-loss, micro-averaging and a loss dictionary for logging."""
 
 from __future__ import annotations
 
-import torch
 from torch import nn
 
 from halite_b200 import ops

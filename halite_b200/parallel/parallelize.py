@@ -6,7 +6,6 @@ ignored: the hot path here is hand-written kernels, not a tracing compiler.
 
 from __future__ import annotations
 
-import torch
 
 from halite_b200.parallel.fsdp import apply_ddp, apply_fsdp
 from halite_b200.utils import get_torch_dtype

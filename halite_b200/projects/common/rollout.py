@@ -11,7 +11,6 @@ from __future__ import annotations
 
 import dataclasses
 import uuid
-from collections import defaultdict
 from dataclasses import dataclass, field
 from random import Random
 from typing import Any, Callable, NamedTuple

@@ -12,7 +12,6 @@ from __future__ import annotations
 
 from collections.abc import Mapping
 
-import torch
 
 from halite_b200.optim.sharded_adamw import clip_grad_norm_
 

@@ -16,7 +16,6 @@ import torch.distributed as dist
 from halite_b200.conf import instantiate, summarize
 from halite_b200.data.dataloader import DataLoader, DataManager
 from halite_b200.data.dataset import WeightedIterableDataset, build_dataset_from_spec
-from halite_b200.distributed import all_reduce_mean
 from halite_b200.distributed.checkpoint import CheckpointManager, load_checkpoint
 from halite_b200.logging import get_logger
 from halite_b200.optim import build_optimizer

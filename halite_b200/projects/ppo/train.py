@@ -13,7 +13,6 @@ sharded kernels; metrics stay on the device until a log step.
 from __future__ import annotations
 
 import gc
-import os
 
 import torch
 import torch.distributed as dist
@@ -23,7 +22,7 @@ from halite_b200.data.dataloader import DataLoader, DataManager
 from halite_b200.data.dataset import WeightedIterableDataset, build_dataset_from_spec
 from halite_b200.distributed.checkpoint import CheckpointManager, load_checkpoint
 from halite_b200.infer.engine import InferenceEngine
-from halite_b200.infer.types import ModelConfig, ServerConfig
+from halite_b200.infer.types import ModelConfig
 from halite_b200.logging import get_logger
 from halite_b200.optim import build_optimizer
 from halite_b200.optim.sharded_adamw import clip_grad_norm_

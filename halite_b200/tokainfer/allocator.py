@@ -11,7 +11,6 @@ token must be computed to produce the first logits.
 
 from __future__ import annotations
 
-import heapq
 import itertools
 
 

@@ -12,7 +12,6 @@ prompt. Results that arrive for finished or bumped sequences are dropped.
 
 from __future__ import annotations
 
-import time
 import uuid
 from collections import deque
 

@@ -11,7 +11,6 @@ from __future__ import annotations
 import statistics
 import subprocess
 import threading
-import time
 
 import torch
 import torch.distributed as dist
