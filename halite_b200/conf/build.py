@@ -4,7 +4,6 @@ from __future__ import annotations
 
 import copy
 import functools
-from typing import Any, Callable
 
 from .node import (ARGS, FILE, FN, META, PARTIAL, PATCH, TAG, TARGET, TUPLE, Field, Lazy, Ref,
                    is_target, locate, normalize, object_path, public_items, unwrap)

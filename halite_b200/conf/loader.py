@@ -22,7 +22,6 @@ import json
 import os
 import sys
 import types
-from typing import Any
 
 from . import node as _node
 from .node import Field, Lazy, from_plain, lazy_partial, normalize, resolve_refs, wrap_lazy

@@ -3,7 +3,7 @@ transformers/infer/types.py:9-154, engine/batch.py:20-76)."""
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, NamedTuple
 
 import torch

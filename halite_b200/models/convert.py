@@ -14,7 +14,6 @@ from dataclasses import dataclass
 from typing import Any, Callable
 
 import torch
-from pydantic import BaseModel
 
 from halite_b200.conf import instantiate
 

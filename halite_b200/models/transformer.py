@@ -6,7 +6,6 @@ transformers/transformer.py:21-418). Module and state-dict names match the refer
 
 from __future__ import annotations
 
-from typing import Any
 
 import torch
 from torch import nn, utils

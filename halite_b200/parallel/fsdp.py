@@ -25,7 +25,6 @@ with dp_shard == 1 (DDP) a unit's "shard" is the whole buffer.
 from __future__ import annotations
 
 import math
-from typing import Iterable
 
 import torch
 import torch.distributed as dist

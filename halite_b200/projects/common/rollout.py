@@ -13,7 +13,7 @@ import dataclasses
 import uuid
 from dataclasses import dataclass, field
 from random import Random
-from typing import Any, Callable, NamedTuple
+from typing import Any, NamedTuple
 
 import torch
 

@@ -15,7 +15,7 @@ import math
 import threading
 import time
 from collections import deque
-from typing import Any, NamedTuple
+from typing import NamedTuple
 
 import torch
 
