@@ -36,7 +36,9 @@ class ShardedParams(list):
 
 def build_optimizer(factory, model, weight_decay: float = 0.0):
     """`factory` is what a config holds (`partial(optim.AdamW, lr=..., betas=...)`). On a sharded
-    model an AdamW request becomes `ShardedAdamW` (fused kernel on fp32 master shards)."""
+    model an AdamW request becomes `ShardedAdamW` (fused kernel on fp32 master shards); any other
+    optimizer runs through `ReplicatedOptimizer` when the model is wrapped with
+    `data_parallel="ddp"` (whole parameters on every rank)."""
     import functools
 
     import torch
@@ -56,8 +58,13 @@ def build_optimizer(factory, model, weight_decay: float = 0.0):
             if fn is torch.optim.Adam:
                 weight_decay = 0.0
             return ShardedAdamW(model, weight_decay=weight_decay, **kw)
-        raise TypeError(f"{fn} cannot drive a sharded model; use AdamW or wrap the model with "
-                        "data_parallel='ddp' and reduce gradients with all_reduce_gradients()")
+        if all(u.ws == 1 for u in model._hb_fsdp.units):
+            # replicated data parallelism: whole parameters on every rank, any optimizer on fp32 masters
+            from .replicated import ReplicatedOptimizer
+
+            return ReplicatedOptimizer(model, factory, weight_decay)
+        raise TypeError(f"{fn} cannot drive a sharded model: it needs whole parameters. Use AdamW, or wrap the "
+                        "model with data_parallel='ddp'")
     return factory(params)
 
 

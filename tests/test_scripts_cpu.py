@@ -38,6 +38,23 @@ def test_lm_script_trains_checkpoints_and_resumes(tmp_path):
     assert steps and min(steps) >= 12
 
 
+def test_lm_script_with_shampoo_on_replicated_ranks(tmp_path):
+    """Pre-training with a whole-matrix optimizer: two replicated ranks, Shampoo on fp32 masters of
+    the flat buffers, checkpoints written and picked up again."""
+    data, out = str(tmp_path / "data"), str(tmp_path / "out")
+    _corpus(data)
+    env = {"HB_TEST_DATA": data, "HB_TEST_OUT": out}
+    script = os.path.join(ROOT, "scripts/lm.py")
+    conf = os.path.join(ROOT, "tests/configs/tiny_lm_shampoo.py")
+    logs = " ".join(run_ranks(script, 2, args=["--conf", conf], timeout=900, env_extra=env)[0].split())
+    losses = [float(x) for x in re.findall(r"global \d+; loss: ([0-9.]+)", logs)]
+    assert len(losses) == 4 and losses[-1] < losses[0] - 0.4, logs[-3000:]
+    assert sorted(os.listdir(out)) == ["step-12", "step-6"]
+    logs = " ".join(run_ranks(script, 2, args=["--conf", conf, "training.max_iter=15"], timeout=900,
+                              env_extra=env)[0].split())
+    assert "resumed at step 12" in logs, logs[-3000:]
+
+
 def test_ppo_script_runs_grpo_iterations_and_checkpoints(tmp_path):
     data, out = str(tmp_path / "data"), str(tmp_path / "out")
     os.makedirs(os.path.join(data, "a"))
