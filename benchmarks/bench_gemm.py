@@ -1,5 +1,5 @@
 """Micro-benchmark of the tcgen05 GEMM against cuBLAS (torch.matmul) on the shapes of a
-transformer step: `python -m halite_b200.ops.bench_gemm [--tokens 32768] [--dim 3072] ...`.
+transformer step: `python -m benchmarks.bench_gemm [--tokens 32768] [--dim 3072] ...`.
 
 Each case is timed with CUDA events over `--iters` launches after warm-up, with a buffer larger
 than L2 rewritten between launches so operands start cold. Prints one JSON line per case.

@@ -1,6 +1,6 @@
 """Achieved memory bandwidth of the memory-bound training kernels at transformer-step sizes:
 
-    python -m halite_b200.ops.bench_memory_bound [--tokens 32768] [--dim 3072] [--ff 8192]
+    python -m benchmarks.bench_memory_bound [--tokens 32768] [--dim 3072] [--ff 8192]
 
 Each op is timed with CUDA events over `--iters` launches after warm-up, a buffer larger than L2
 rewritten between launches; bytes are the op's algorithmic traffic (every operand read once,

@@ -1,7 +1,7 @@
 """Time of one PPO iteration with four models (actor, critic, reference policy, reward model):
 
-    python -m halite_b200.projects.ppo.bench_iter [--prompts 64] [--prompt-len 256] [--new-tokens 512]
-    torchrun --nproc-per-node N -m halite_b200.projects.ppo.bench_iter ...      (FSDP over N ranks)
+    python -m benchmarks.bench_ppo_iter [--prompts 64] [--prompt-len 256] [--new-tokens 512]
+    torchrun --nproc-per-node N -m benchmarks.bench_ppo_iter ...      (FSDP over N ranks)
 
 Per iteration and rank: push the actor's weights into the in-process paged engine, sample
 `--new-tokens` tokens for `--prompts` random prompts, score them with the reward model (scalar

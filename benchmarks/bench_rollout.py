@@ -1,6 +1,6 @@
 """Rollout throughput of one engine replica:
 
-    python -m halite_b200.infer.bench_rollout [--requests 128] [--new-tokens 512] [--engine paged|tokainfer]
+    python -m benchmarks.bench_rollout [--requests 128] [--new-tokens 512] [--engine paged|tokainfer]
 
 Llama-3.2-3B architecture with random bf16 weights; prompt lengths uniform in [min, max] with
 uniform-random token ids, a share of the requests starting with one common 512-token prefix

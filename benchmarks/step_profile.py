@@ -1,6 +1,6 @@
 """Per-kernel time breakdown of one training step of the benchmark model:
 
-    python -m halite_b200.utils.step_profile [--layers 8] [--batch 8] [--seq 4096] [--rows 30]
+    python -m benchmarks.step_profile [--layers 8] [--batch 8] [--seq 4096] [--rows 30]
 
 Runs a few warm-up steps, then one step under `torch.profiler` (CUPTI kernel timestamps) and
 prints device time per kernel name, largest first, with each kernel's share. Use it to decide

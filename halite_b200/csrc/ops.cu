@@ -962,7 +962,7 @@ cudaError_t rmsnorm_bwd(const void* dy, const void* h, const void* w, const floa
   auto W = static_cast<const __nv_bfloat16*>(w);
   auto DR = static_cast<const __nv_bfloat16*>(dres);
   auto DX = static_cast<__nv_bfloat16*>(dx);
-  const int grid_dx = (rows + 7) / 8;
+  const int grid_dx = static_cast<int>((static_cast<long long>(rows) + 7) / 8);   // rows may be near 2^31
   const int vpt = (dim / 8 + kRowThreads - 1) / kRowThreads;
 #define HB_NORM_BWD(V)                                                                                          \
   do {                                                                                                          \

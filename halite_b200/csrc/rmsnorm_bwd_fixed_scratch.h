@@ -1,10 +1,12 @@
 // RMSNorm backward that performs no memory allocation of any kind.
 //
-// This entry point has no counterpart in the reference project; it exists for hosts that must
-// not allocate while they run: a C or C++ program that links this library without torch and
-// so has no caching allocator to ask; a callback that runs while some other component holds
-// the allocator's lock; and a latency-critical loop that cannot afford the implicit device
-// synchronisation that cudaMalloc / cudaFree bring. The regular entry point
+// This entry point has no counterpart in the reference project; it exists for callers that must
+// not allocate while they run: native (C / C++ / ctypes) code that reaches this symbol directly
+// and has no business inside torch's caching allocator; a callback that runs while some other
+// component holds the allocator's lock; and a latency-critical loop that cannot afford the
+// implicit device synchronisation that cudaMalloc / cudaFree bring. The symbol is exported from
+// the framework's extension library (`halite_b200/_C.so`), which itself links against torch: the
+// process must be able to load torch's libraries, but this function never calls into them. The regular entry point
 // (`rmsnorm_bwd` of the Python extension) asks torch for its outputs and for a scratch tensor
 // on every call; this one gets inputs and outputs from the caller and keeps its scratch in a
 // fixed array inside the library's device image.
@@ -16,7 +18,8 @@
 //
 // Limits: dim is a multiple of 8 and at most HB_RMSNORM_BWD_FIXED_MAX_DIM (8192). The scratch
 // is HB_RMSNORM_BWD_FIXED_SLICES (64) x HB_RMSNORM_BWD_FIXED_MAX_DIM floats = 2 MiB per device,
-// whatever the call's size. `rows` is unlimited. A size outside these limits is rejected with
+// whatever the call's size. `rows` is between 0 and 2^31 - 1 (the kernels index rows with 32-bit
+// integers); rows == 0 only clears dw. A size outside these limits is rejected with
 // HB_FIXED_ERR_SIZE and a message on stderr; nothing is launched.
 //
 // Set-up: the first call on each device looks up the scratch array's device address (one
@@ -37,7 +40,7 @@
 #define HB_RMSNORM_BWD_FIXED_MAX_DIM 8192
 #define HB_RMSNORM_BWD_FIXED_SLICES 64
 
-#define HB_FIXED_ERR_SIZE (-1)      // dim not a multiple of 8, dim > max, or rows < 0
+#define HB_FIXED_ERR_SIZE (-1)      // dim <= 0, not a multiple of 8 or > max; rows < 0 or > 2^31 - 1
 #define HB_FIXED_ERR_POINTER (-2)   // a required pointer is NULL or not 16-byte aligned
 
 #ifdef __cplusplus

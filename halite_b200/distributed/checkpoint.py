@@ -49,6 +49,7 @@ class CheckpointManager:
                  model_weights_only: bool = False, export_dtype: str = "float32", async_mode: str = "disabled"):
         self.enable_checkpoint = enable_checkpoint
         self.keep_latest_k = keep_latest_k
+        self.pre_save = None      # optional callable run right before a save that is going to happen
         if not enable_checkpoint:
             return
         self.states = dict(states or {})
@@ -118,6 +119,8 @@ class CheckpointManager:
     def save(self, step: int, force: bool = False, last: bool = False):
         if not self._should_save(step, force):
             return False
+        if self.pre_save is not None:
+            self.pre_save()
         self._wait()
         path = self._id(step)
         if last and self.model_weights_only:
@@ -225,6 +228,13 @@ class CheckpointManager:
         keys = ["model"] if step == 0 else list(self.states.keys())
         sd = {k: (self.states[k].state_dict() if hasattr(self.states[k], "state_dict") else self.states[k])
               for k in keys}
+        # state that a fresh object has not created yet (lazily built optimizer state) is asked
+        # for by the checkpoint's own key list, not by the fresh object's
+        saved_meta = dcp.FileSystemReader(path).read_metadata().state_dict_metadata
+        for k in keys:
+            if hasattr(self.states[k], "extend_load_template") and isinstance(sd[k], dict):
+                self.states[k].extend_load_template(
+                    sd[k], {key[len(k) + 1:]: md for key, md in saved_meta.items() if key.startswith(k + ".")})
         fixups = self._adapt_to_saved_sizes(sd, path)
         dcp.load(sd, checkpoint_id=path)
         for group, key, original, full in fixups:

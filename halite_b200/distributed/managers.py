@@ -98,6 +98,33 @@ class OptimizerManager(Stateful):
                 out[prefix + "param_groups"] = sd["param_groups"]
         return out
 
+    def extend_load_template(self, template, saved):
+        """Add to `template` (this manager's `state_dict()` of a FRESH optimizer) every entry the
+        checkpoint holds and the fresh optimizer has not created yet. A torch optimizer builds its
+        per-parameter state (moments, preconditioner factors, step counts) lazily in its first
+        `step()`, so the fresh template has none of those keys and a load that only asks for the
+        template's keys would silently restart them from zero. `saved` maps this group's saved
+        keys to their checkpoint metadata (tensor entries carry `size` and `properties.dtype`)."""
+        for i, opt in enumerate(self.optimizers):
+            if hasattr(opt, "fsdp"):
+                continue
+            prefix = "" if len(self.optimizers) == 1 else f"{i}."
+            device = torch.device("cpu")
+            for g in opt.param_groups:
+                if g["params"]:
+                    device = g["params"][0].device
+                    break
+            for key, md in saved.items():
+                if not key.startswith(prefix + "state.") or key in template:
+                    continue
+                if hasattr(md, "size") and hasattr(md, "properties"):
+                    size = tuple(md.size)
+                    # scalar entries (step counters) stay on the host, where torch keeps them
+                    where = device if len(size) > 0 and md.size.numel() > 1 else torch.device("cpu")
+                    template[key] = torch.empty(size, dtype=md.properties.dtype, device=where)
+                else:
+                    template[key] = None       # a pickled object: the loader replaces the value
+
     def load_state_dict(self, state_dict):
         for i, opt in enumerate(self.optimizers):
             prefix = "" if len(self.optimizers) == 1 else f"{i}."
@@ -112,11 +139,28 @@ class OptimizerManager(Stateful):
                 opt.load_state_dict(flat)
             else:
                 sd = opt.state_dict()
-                for pid, st in sd["state"].items():
-                    for name in st:
-                        key = f"{prefix}state.{pid}.{name}"
-                        if key in state_dict:
-                            st[name] = state_dict[key]
+                state = {pid: dict(st) for pid, st in sd["state"].items()}
+                head = prefix + "state."
+                for key, val in state_dict.items():
+                    if not key.startswith(head):
+                        continue
+                    pid, _, name = key[len(head):].partition(".")
+                    state.setdefault(int(pid), {})[name] = val
+                # list-valued entries (one preconditioner factor per dimension) are stored element
+                # by element under `name.index`: put them back together
+                for st in state.values():
+                    parts = {}
+                    for name in [n for n in st if "." in n and n.rpartition(".")[2].isdigit()]:
+                        base, _, idx = name.rpartition(".")
+                        parts.setdefault(base, {})[int(idx)] = st.pop(name)
+                    for base, items in parts.items():
+                        st[base] = [items[j] for j in sorted(items)]
+                sd["state"] = state
+                if prefix + "param_groups" in state_dict:
+                    saved_groups = state_dict[prefix + "param_groups"]
+                    if len(saved_groups) == len(sd["param_groups"]):
+                        for cur, old in zip(sd["param_groups"], saved_groups):
+                            cur.update({k: v for k, v in old.items() if k != "params"})
                 opt.load_state_dict(sd)
 
 

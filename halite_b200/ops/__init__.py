@@ -3,9 +3,10 @@
 * `sm100`: the hand-written CUDA kernels in `halite_b200/csrc` (bf16 tensors on a CUDA device);
 * `reference`: plain PyTorch in fp32, used on CPU and as the oracle in tests.
 
-There is no silent fallback on a GPU: a bf16 CUDA tensor either runs the sm_100a kernel or
-raises. Set `HALITE_B200_FORCE_REFERENCE=1` to run the PyTorch path on purpose (tests do, to
-compare the two).
+On a GPU a bf16 tensor runs the sm_100a kernel, and a missing extension raises. The one
+exception is a matrix product with a dimension that is not a multiple of 8 (TMA needs 16-byte
+rows): it goes to the library GEMM and `ops/linear.py` logs that once per shape. Set
+`HALITE_B200_FORCE_REFERENCE=1` to run the PyTorch path on purpose (tests do, to compare the two).
 """
 
 from __future__ import annotations

@@ -17,6 +17,21 @@ import torch.nn.functional as F
 import halite_b200.ops as ops
 from halite_b200.utils import probe as _probe
 
+_noted = set()
+
+
+def _note_library_path(kind, shape):
+    """Log, once per (kind, shape), that a bf16 CUDA product left the tcgen05 kernel for a library
+    routine because a dimension is not a multiple of 8 (16-byte rows are what TMA needs)."""
+    key = (kind, tuple(shape))
+    if key in _noted:
+        return
+    _noted.add(key)
+    from halite_b200.logging import logger
+
+    logger.warning(f"{kind}: shape {tuple(shape)} has a dimension that is not a multiple of 8; "
+                   "this product runs on the library GEMM, not on the sm_100a kernel")
+
 
 def gemm(a, b, out=None, a_mn=False, b_mn=False, accumulate=False, out_dtype=None, block_n=0,
          max_ctas=0, gather=None, scatter=None, group=None):
@@ -31,6 +46,8 @@ def gemm(a, b, out=None, a_mn=False, b_mn=False, accumulate=False, out_dtype=Non
         out = torch.empty(M, N, device=a.device, dtype=out_dtype or torch.bfloat16)
     if gather is None and scatter is None and group is None and not (_tma_ready(a) and _tma_ready(b)):
         # rows that are not 16-byte multiples (a vocabulary of 260, say): the library computes it
+        if a.is_cuda:
+            _note_library_path("gemm", (M, N))
         prod = torch.matmul((a.t() if a_mn else a).float(), (b if b_mn else b.t()).float())
         if accumulate:
             out += prod.to(out.dtype)
@@ -109,6 +126,8 @@ def linear(x, weight, bias=None):
             and weight.shape[1] % 8 == 0 and x.dtype == torch.bfloat16:
         out = _LinearFn.apply(x, weight, bias)
     else:
+        if x.is_cuda and x.dtype == torch.bfloat16 and not ops.force_reference():
+            _note_library_path("linear", weight.shape)
         out = F.linear(x, weight, bias)
     if _probe.active_probe() is not None:
         _probe.active_probe().on_linear(x, weight, out)

@@ -94,6 +94,8 @@ class FlatUnit:
         self._reduce_work = None
         self._gather_work = None
         self._backward_done = False
+        self._needs_reduce = False
+        self.defer_reduce = False  # set by `ShardedModel.no_sync()`: backward passes only accumulate
         self.fused = None         # FusedGather state once `enable_fused_gather` has run
         self.fused_reduce = None  # FusedReduce state once `enable_fused_reduce` has run
         self._adopt_params()
@@ -188,6 +190,10 @@ class FlatUnit:
 
     def pre_forward(self):
         self.wait_gather()
+        # the backward pass that follows writes gradients: an earlier micro-batch's reduction of
+        # this unit must have finished with the buffer (the wait is queued on the stream now, the
+        # reduction itself is long done by the time backward reaches the unit)
+        self.wait_reduce_before_write()
         if self.fused is not None and self.fused.pending:
             # nobody carried this unit's gather (first block, or the carrying GEMM did not run)
             self.fused.run_standalone()
@@ -206,6 +212,9 @@ class FlatUnit:
         if self._backward_done:
             return
         self._backward_done = True
+        # a reduction of an earlier pass may still be reading (or, when the shard is the whole
+        # buffer, rewriting) the gradient buffer this pass has just added to
+        self.wait_reduce_before_write()
         for m, n, _, off, numel in self.entries:
             p = m._parameters[n]
             if p.grad is not None:
@@ -227,9 +236,18 @@ class FlatUnit:
             tp = getattr(p, "_hb_tp_replicated", None)
             if tp is not None and tp.size > 1:
                 dist.all_reduce(p._hb_grad, group=tp.group)
-        self.start_reduce()
+        if self.defer_reduce:
+            self._needs_reduce = True
+        else:
+            self.start_reduce()
+
+    def wait_reduce_before_write(self):
+        """Order the current stream after a reduction of this unit that is still in flight."""
+        if self._reduce_event is not None:
+            torch.cuda.current_stream().wait_event(self._reduce_event)
 
     def start_reduce(self):
+        self._needs_reduce = False
         if self.ws == 1 and self.replicate_group is None:
             return
         if self.fused_reduce is not None:
@@ -525,6 +543,33 @@ class ShardedModel:
         self.gather_heap = None
         self.reduce_heap = None
 
+    def wait_parameters(self):
+        """Make the current stream see whole, current parameters in every unit: waits for the
+        collective gathers in flight and launches the carried gathers nobody has carried yet.
+        Anything that reads or writes parameters outside the model's own forward (state_dict,
+        checkpoint staging, weight export to an engine, in-place re-normalisation) calls this."""
+        for u in self.units:
+            u.wait_gather()
+        self.flush_gathers()
+
+    def no_sync(self):
+        """Context manager for gradient accumulation: backward passes inside it only add into the
+        flat gradient buffers; the reduce-scatter / all-reduce of each unit is started by the
+        first backward pass outside it (or by `finish_backward`), once per optimizer step."""
+        state = self
+
+        class _NoSync:
+            def __enter__(self_inner):
+                for u in state.units:
+                    u.defer_reduce = True
+
+            def __exit__(self_inner, *exc):
+                for u in state.units:
+                    u.defer_reduce = False
+                return False
+
+        return _NoSync()
+
     def flush_gathers(self):
         """Launch every gather that is still waiting for its carrier (before anything other than
         the model's own forward reads the parameters: state_dict, weight export, evaluation of a
@@ -538,6 +583,8 @@ class ShardedModel:
         not fire, e.g. one whose input needed no gradient)."""
         for u in self.units:
             u.post_backward()
+            if u._needs_reduce:
+                u.start_reduce()
 
     def wait_reductions(self):
         for u in self.units:
@@ -692,13 +739,14 @@ def apply_fsdp(model, mesh=None, param_dtype=torch.bfloat16, reduce_dtype=torch.
         return tuple(_to_param_dtype(a) for a in args), {k: _to_param_dtype(v) for k, v in kwargs.items()}
 
     model.register_forward_pre_hook(root_pre_forward, with_kwargs=True)
+    # state_dict() hands out views of the flat buffers: they must be whole and current first
+    model.register_state_dict_pre_hook(lambda module, prefix, keep_vars: state.wait_parameters())
     if fused_all_gather is None:
         import os
 
         fused_all_gather = os.environ.get("HB_FSDP_FUSED_GATHER", "0") == "1"
     if fused_all_gather and shard_group is not None and device.type == "cuda" and calls_block_hooks:
-        if enable_fused_gather(state):
-            model.register_state_dict_pre_hook(lambda module, prefix, keep_vars: state.flush_gathers())
+        enable_fused_gather(state)
     if fused_reduce_scatter is None:
         import os
 

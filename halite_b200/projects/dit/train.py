@@ -225,6 +225,10 @@ class DiTLoop:
                     val /= self.pdims.dp
                 lr = self.optimizer.param_groups[0]["lr"]
                 self.losses.append(val.item())
+                if self.device.type == "cuda":
+                    from halite_b200 import ops
+
+                    ops.check_status(self.device)       # a bounded wait that ran out raises here
                 log.info(f"epoch {epoch}; {step}/{n_iter}; global {self.global_step}; loss: {val.item():.5f}; lr: {lr:.7f}")
                 if self.pdims.is_primary and wandb is not None and wandb.run is not None:
                     wandb.log({"train/loss": val.item(), "train/lr": lr}, step=self.global_step)

@@ -21,6 +21,8 @@ from halite_b200.logging import get_logger
 from halite_b200.optim import build_optimizer
 from halite_b200.optim.sharded_adamw import clip_grad_norm_
 from halite_b200.parallel import ParallelDims
+from halite_b200.utils import nvtx
+from halite_b200.utils.throughput import ThroughputMeter, model_flops_per_token
 
 try:  # experiment tracking is optional
     import wandb
@@ -95,9 +97,11 @@ def _fmt(loss_dict):
 
 
 class LMTrainer:
-    def __init__(self, conf, device=None, sft=False, num_workers=2):
+    def __init__(self, conf, device=None, sft=False, num_workers=2, profile_steps=None):
         self.conf = conf
         self.sft = sft
+        self.profile_steps = nvtx.parse_step_window(profile_steps) if isinstance(profile_steps, str) \
+            else profile_steps
         t = conf.training
         self.pdims = ParallelDims(dp_replicate=t.data_parallel_replicate, dp_shard=t.data_parallel_shard,
                                   tp=t.tensor_parallel, pp=t.pipeline_parallel)
@@ -186,6 +190,7 @@ class LMTrainer:
         self.checkpoint = CheckpointManager(self.model, self.optimizer, self.scheduler, self.train_loader,
                                             model_config=self.conf.model, directory=out.output_dir or "checkpoint",
                                             interval=out.save_step or 0, enable_checkpoint=enabled)
+        self.checkpoint.pre_save = self._check_kernels      # never write a state a timed-out kernel produced
         if enabled and self.checkpoint.load(-1):
             self.global_step = int(getattr(self.optimizer, "_step", 0))
             self.logger.info(f"resumed at step {self.global_step}")
@@ -193,6 +198,17 @@ class LMTrainer:
     # ------------------------------------------------------------------ loops
     def _dp_group(self):
         return self.pdims.group("dp") if self.pdims.dp > 1 else None
+
+    def _meter(self):
+        return ThroughputMeter(None, self.pdims.dp, self.device)
+
+    def _check_kernels(self):
+        """Raise if a kernel of this process gave up a bounded wait (a peer that never signalled, a
+        barrier that never completed): called where the loop reads from the device anyway."""
+        if self.device.type == "cuda":
+            from halite_b200 import ops
+
+            ops.check_status(self.device)
 
     def train_epoch(self, epoch):
         conf, log, model = self.conf, self.logger, self.model
@@ -203,29 +219,49 @@ class LMTrainer:
         batches = DevicePrefetcher(DataManager(self.train_loader, self._dp_group(), device=self.device), self.device)
         step = 0
         fsdp = getattr(model, "_hb_fsdp", None)
+        meter = self._meter()
+        profiler = nvtx.StepWindowProfiler(self.profile_steps, conf.output.output_dir, log, self.pdims.rank)
         for batch in batches:
-            loss, loss_dict = _forward_loss(conf, model, self.criterion, batch, self.train_step_fn)
-            loss.backward()
-            loss = loss.detach()
-            if fsdp is not None:
-                fsdp.finish_backward()
-            grad_norm = None
-            if conf.training.clip_grad_norm is not None:
-                grad_norm = clip_grad_norm_(model, conf.training.clip_grad_norm, self.optimizer)
-            self.scheduler.step()
-            self.optimizer.step()
-            self.optimizer.zero_grad(set_to_none=True)
-            if self.postprocess is not None:
-                self.postprocess(model)
+            profiler.step_begin(self.global_step)
+            with nvtx.phase(f"step {self.global_step}"):
+                with nvtx.phase("forward"):
+                    loss, loss_dict = _forward_loss(conf, model, self.criterion, batch, self.train_step_fn)
+                with nvtx.phase("backward"):
+                    loss.backward()
+                    loss = loss.detach()
+                    if fsdp is not None:
+                        fsdp.finish_backward()
+                grad_norm = None
+                with nvtx.phase("optimizer"):
+                    if conf.training.clip_grad_norm is not None:
+                        grad_norm = clip_grad_norm_(model, conf.training.clip_grad_norm, self.optimizer)
+                    self.scheduler.step()
+                    self.optimizer.step()
+                    self.optimizer.zero_grad(set_to_none=True)
+                    if self.postprocess is not None:
+                        self.postprocess(model)
+            profiler.step_end(self.global_step)
+            inputs = batch["input"] if "input" in batch else None
+            if isinstance(inputs, torch.Tensor):
+                if meter.flops_per_token is None:
+                    meter.flops_per_token = model_flops_per_token(model, inputs.shape[-1])
+                meter.add(inputs.numel())
             if self.global_step % conf.output.log_step == 0:
                 lr = self.optimizer.param_groups[0]["lr"]
+                loss_val = float(loss)                     # the loop's one device -> host read
+                self._check_kernels()
+                speed = meter.lap()
                 gn = "" if grad_norm is None else f" grad norm: {float(grad_norm):.3f};"
-                log.info(f"epoch {epoch}; {step}/{n_iter}; global {self.global_step}; loss: {float(loss):.5f}; "
-                         f"{_fmt(loss_dict)};{gn} lr: {lr:.7f}")
+                sp = "" if not speed else (f" tokens/s: {speed['tokens_per_s']:.0f}; "
+                                           f"mfu: {100 * speed.get('mfu', 0.0):.1f}%;")
+                log.info(f"epoch {epoch}; {step}/{n_iter}; global {self.global_step}; loss: {loss_val:.5f}; "
+                         f"{_fmt(loss_dict)};{gn}{sp} lr: {lr:.7f}")
+                self.last_speed = speed or getattr(self, "last_speed", {})
                 if self.pdims.is_primary and wandb is not None and wandb.run is not None:
-                    report = {"train/loss": float(loss), "train/lr": lr}
+                    report = {"train/loss": loss_val, "train/lr": lr}
                     report.update({f"train/{k}": float(v) for k, v in loss_dict.items()
                                    if k not in ("loss_vals",)})
+                    report.update({f"perf/{k}": v for k, v in speed.items()})
                     if grad_norm is not None:
                         report["train/grad_norm"] = float(grad_norm)
                     wandb.log(report, step=self.global_step)

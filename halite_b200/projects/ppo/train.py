@@ -12,6 +12,8 @@ sharded kernels; metrics stay on the device until a log step.
 
 from __future__ import annotations
 
+import contextlib
+
 import gc
 
 import torch
@@ -209,9 +211,12 @@ class PPOLoop:
                 self.optimizer.zero_grad(set_to_none=True)
                 micro = mb.split(t.ppo_microbatch_size) if t.ppo_microbatch_size is not None else [mb]
                 n_micro = len(micro)
-                for m in micro:
-                    res = self.trainer.compute_actor_loss(m)
-                    (res.loss / n_micro).backward()
+                for i, m in enumerate(micro):
+                    # only the last micro-batch's backward starts the gradient reductions
+                    hold = fsdp.no_sync() if fsdp is not None and i < n_micro - 1 else contextlib.nullcontext()
+                    with hold:
+                        res = self.trainer.compute_actor_loss(m)
+                        (res.loss / n_micro).backward()
                     d = {k: (v.detach() if isinstance(v, torch.Tensor) else v) for k, v in res.metric_dict().items()}
                     d["sample/response_len/mean"] = m.batch.response_len.float().mean()
                     metrics.append(d)
@@ -221,6 +226,12 @@ class PPOLoop:
                     grad_norm = clip_grad_norm_(self.actor, t.clip_grad_norm, self.optimizer)
                 self.optimizer.step()
         self.n_minibatches, self.n_microbatches = len(minibatches), n_micro
+        if self.device.type == "cuda":
+            from halite_b200 import ops
+
+            # `reduce_metrics` reads from the device right after this: a kernel that gave up a
+            # bounded wait during the update raises here instead of training on
+            ops.check_status(self.device)
         return rollout, metrics, grad_norm
 
     def reduce_metrics(self, metrics):

@@ -5,7 +5,12 @@
     torchrun --nproc-per-node N scripts/sft.py --conf <experiment config.py> [key=value ...]
 """
 
+import os
+import sys
+
 import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 from halite_b200.conf import load_arg_config
 from halite_b200.projects.lm.config import LMConfig
@@ -13,8 +18,11 @@ from halite_b200.projects.lm.train import LMTrainer
 
 
 def main():
+    from scripts.lm import pop_profile_steps
+
+    window = pop_profile_steps(sys.argv)
     conf = load_arg_config(LMConfig)
-    LMTrainer(conf, sft=True, num_workers=4).run()
+    LMTrainer(conf, sft=True, num_workers=4, profile_steps=window).run()
 
 
 if __name__ == "__main__":

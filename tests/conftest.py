@@ -36,7 +36,7 @@ def zoo():
 
 
 def tiny_llama_conf(zoo, **over):
-    """Config 1 of the baseline table: dim 256, 4 layers, 4/2 heads, SwiGLU 688, vocab 1024."""
+    """Tiny Llama-style decoder: dim 256, 4 layers, 4 query / 2 KV heads, SwiGLU 688, vocab 1024."""
     from functools import partial
 
     import torch

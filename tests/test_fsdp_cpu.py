@@ -1,5 +1,5 @@
 """Sharded data parallelism on CPU / Gloo: the tiny-Llama loss curve and parameters must match a
-plain single-process AdamW run (config 1 of the baseline table, training half)."""
+plain single-process AdamW run (tiny Llama: dim 256, 4 layers, 20 AdamW steps)."""
 
 import os
 

@@ -1,4 +1,4 @@
-"""Paged-KV engine on CPU (config 1 of the baseline table, inference half): greedy decode through
+"""Paged-KV engine on CPU (tiny Llama, page size 16, 8 prompts of 16 tokens): greedy decode through
 the paged cache must reproduce the dense forward (tokens equal, log-probs within 1e-4), the
 prefix cache must be hit by shared prefixes, and no page or request slot may leak."""
 

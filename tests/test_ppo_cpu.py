@@ -221,7 +221,7 @@ def test_ppo_iteration_benchmark_runs_four_models():
     """Actor, critic, reference and reward model through one timed iteration (tiny widths)."""
     import os
 
-    from halite_b200.projects.ppo import bench_iter
+    from benchmarks import bench_ppo_iter as bench_iter
 
     conf = os.path.join(os.path.dirname(os.path.abspath(__file__)), "configs/tiny_ppo_models.py")
     out = bench_iter.main(["--conf", conf, "--prompts", "8", "--prompt-len", "12", "--new-tokens", "10",

@@ -72,6 +72,39 @@ def test_matches_regular_entry_point_twice_in_a_row(rows, dim, with_dres):
         torch.testing.assert_close(dx.float(), ref_dx, rtol=2e-2, atol=2e-2)
 
 
+def test_zero_rows_clears_dw_and_dims_may_change_between_calls():
+    """rows == 0 takes the memset path; then the largest dim followed by the smallest one, so the
+    second call runs on a scratch that the first left full of unrelated values."""
+    import halite_b200.ops as ops
+
+    fn = _lib()
+    ext = ops.ext()
+    dw = torch.full((64,), float("nan"), device="cuda")
+    empty = torch.empty(0, 64, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(64, device="cuda", dtype=torch.bfloat16)
+    rstd = torch.empty(0, device="cuda")
+    # zero rows: pointers of empty tensors may be NULL, so hand over valid ones
+    buf = torch.empty(8, 64, device="cuda", dtype=torch.bfloat16)
+    rc = fn(buf.data_ptr(), buf.data_ptr(), w.data_ptr(), dw.data_ptr(), None, buf.data_ptr(), dw.data_ptr(),
+            0, 64, 0.0, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert float(dw.abs().sum()) == 0.0
+    del empty, rstd
+    for rows, dim in ((333, MAX_DIM), (5, 64)):
+        dy, h, w, rstd, dres = _inputs(rows, dim, 7)
+        want_dx, want_dw = ext.rmsnorm_bwd(dy, h, w, rstd, dres, 0.0)
+        dx = torch.empty(rows, dim, device="cuda", dtype=torch.bfloat16)
+        dw = torch.full((dim,), float("nan"), device="cuda")
+        assert _call(fn, dy, h, w, rstd, dres, dx, dw) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(dx, want_dx)
+        torch.testing.assert_close(dw, want_dw, rtol=2e-3, atol=2e-2 * (rows ** 0.5) / 64)
+    # rows beyond 31 bits are refused before anything is launched
+    assert fn(buf.data_ptr(), buf.data_ptr(), w.data_ptr(), dw.data_ptr(), None, buf.data_ptr(), dw.data_ptr(),
+              2 ** 31, 64, 0.0, None) == -1
+
+
 def test_rejects_sizes_beyond_the_fixed_scratch():
     fn = _lib()
     dim = MAX_DIM + 8
