@@ -150,6 +150,8 @@ class TransformerDecoder(nn.Module, ModelMixin, GenerationMixin):
             out, residual, _, _ = block(out, residual, None, None, pos_emb=pos_emb, use_cache=False)
             if hooks is not None:
                 out = hooks[1](i, out)
+        if hooks is not None:
+            out = hooks[0](len(self.blocks), out)
         if self.post_blocks is not None:
             out = self.post_blocks(out)
         hidden = TP.gather_rows(out.reshape(-1, out.shape[-1]), tp)          # [B*S, dim]
@@ -251,6 +253,8 @@ class TransformerDecoder(nn.Module, ModelMixin, GenerationMixin):
             if use_cache and hasattr(cache, "update"):
                 next_caches = cache
 
+        if hooks is not None:
+            out = hooks[0](n_blocks, out)      # announces the output side (final norm + head)
         if self.post_blocks is not None:
             out = self.post_blocks(out, residual) if residual is not None else self.post_blocks(out)
         if output_hidden_states:

@@ -3,7 +3,7 @@
 One fused kernel per unit range reads the reduced fp32 gradient shard, applies the (deferred)
 clipping coefficient from a device scalar, updates master / moments and writes the bf16
 working shard in place inside the unit's gathered parameter buffer; then the per-unit
-all-gathers are queued in forward order. Nothing in `step()` synchronises with the host.
+all-gathers are queued unit by unit in forward order. Nothing in `step()` synchronises with the host.
 
 Replaces `torch.optim.AdamW(foreach)` + `clip_grad_norm_(foreach)` on DTensor shards in the
 reference's loop (scripts/lm.py:94-100).
@@ -69,16 +69,22 @@ class ShardedAdamW(torch.optim.Optimizer):
                 u.fused.wait_readers()     # peers still copying last step's shard finish first
             if u.fused_reduce is not None:
                 u.fused_reduce.wait_readers()   # ... and peers still summing this step's gradients
-        for u, lo, hi, gi in self._slots:
-            g = self.param_groups[self._gidx[gi]]
-            ops.fused_adamw_step(
-                u.master[lo:hi], self.exp_avg[id(u)][lo:hi], self.exp_avg_sq[id(u)][lo:hi],
-                u.grad_shard[lo:hi], u.param_shard()[lo:hi], g["lr"], g["betas"], g["eps"],
-                g["weight_decay"], self._step, 1.0, self.clip_coef)
-        self.clip_coef = None
+        # unit by unit in the order the next forward uses them: a unit's gather starts on the
+        # communication stream as soon as its own update is done and runs under the next units'
+        # updates, and the forward only ever waits for the unit it is about to use
+        by_unit = {}
+        for slot in self._slots:
+            by_unit.setdefault(id(slot[0]), []).append(slot)
         for u in self.units:
+            for _, lo, hi, gi in by_unit.get(id(u), ()):
+                g = self.param_groups[self._gidx[gi]]
+                ops.fused_adamw_step(
+                    u.master[lo:hi], self.exp_avg[id(u)][lo:hi], self.exp_avg_sq[id(u)][lo:hi],
+                    u.grad_shard[lo:hi], u.param_shard()[lo:hi], g["lr"], g["betas"], g["eps"],
+                    g["weight_decay"], self._step, 1.0, self.clip_coef)
             u._written.clear()          # the next backward pass starts a new sum
             u.start_gather(epoch=self._step)
+        self.clip_coef = None
 
     # ------------------------------------------------------------------ checkpoint
     def state_dict(self):

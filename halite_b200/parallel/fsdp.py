@@ -1,7 +1,8 @@
 """Sharded data parallelism on flat per-block buffers (the job FSDP2 does in the reference,
 parallel/fsdp.py:8-60), laid out for a 180 GB GPU.
 
-Each unit (one transformer block, or the root remainder: embedding, final norm, head) owns
+Each unit (one transformer block; the head unit: final norm + head; the root remainder: the
+embedding and anything else) owns
 
 * `full_param`  low-precision (bf16) flat buffer holding every parameter of the unit; the
                 module's `nn.Parameter`s are views into it, so linears that read the same
@@ -15,8 +16,9 @@ the moment the unit's backward ends and overlaps the next unit's backward; after
 AdamW has rewritten the rank's bf16 shard inside `full_param`, one all-gather per unit is
 issued in forward order and each forward waits only for its own unit. Parameters stay
 gathered between forward and backward (no second all-gather): 2 bytes / parameter of HBM
-buys one collective per step instead of two. `reshard_after_forward=True` restores the
-memory-lean schedule.
+buys one collective per step instead of two. The AdamW kernels and the gathers are issued unit
+by unit in the order the next forward uses the units, so that forward waits for the embedding's
+gather only and every other gather hides under compute.
 
 With dp_replicate > 1 (HSDP) gradient shards are additionally all-reduced across replicas;
 with dp_shard == 1 (DDP) a unit's "shard" is the whole buffer.
@@ -476,7 +478,7 @@ def enable_fused_reduce(state):
     The root unit keeps the collective."""
     from halite_b200.parallel.symm import SymmetricHeap
 
-    units = [u for u in state.units if u is not state.root_unit and u.ws > 1]
+    units = [u for u in state.units if u is not state.root_unit and u is not state.head_unit and u.ws > 1]
     if not units or units[0].device.type != "cuda" or state.replicate_group is not None \
             or units[0].reduce_dtype != torch.float32:
         return False
@@ -506,7 +508,7 @@ def enable_fused_gather(state, carried=True):
     it is launched on its own right before the block runs."""
     from halite_b200.parallel.symm import SymmetricHeap
 
-    units = [u for u in state.units if u is not state.root_unit and u.ws > 1]
+    units = [u for u in state.units if u is not state.root_unit and u is not state.head_unit and u.ws > 1]
     if not units or units[0].device.type != "cuda":
         return False
     elem = units[0].full_param.element_size()
@@ -533,10 +535,11 @@ def enable_fused_gather(state, carried=True):
 class ShardedModel:
     """Book-keeping object attached to a wrapped model as `model._hb_fsdp`."""
 
-    def __init__(self, model, units, root_unit, shard_group, replicate_group, comm_stream):
+    def __init__(self, model, units, root_unit, shard_group, replicate_group, comm_stream, head_unit=None):
         self.model = model
-        self.units: list[FlatUnit] = units        # forward order; root unit last
-        self.root_unit = root_unit
+        self.units: list[FlatUnit] = units        # order of use in a forward pass: root, blocks, head
+        self.root_unit = root_unit                # embedding and whatever no other unit took
+        self.head_unit = head_unit                # final norm + head (None: they live in the root unit)
         self.shard_group = shard_group
         self.replicate_group = replicate_group
         self.comm_stream = comm_stream
@@ -636,7 +639,8 @@ def _unit_params(module: nn.Module, exclude: set[int]):
 
 def apply_fsdp(model, mesh=None, param_dtype=torch.bfloat16, reduce_dtype=torch.float32,
                reshard_after_forward=False, device=None, blocks_attr="blocks", force_fsdp=False,
-               block_iterator=None, fused_all_gather=None, fused_reduce_scatter=None):
+               block_iterator=None, fused_all_gather=None, fused_reduce_scatter=None,
+               tail_attrs=("post_blocks", "head")):
     """Shard `model` over the mesh's data-parallel dimensions. Returns the same module, with
     parameters re-homed into flat unit buffers and `model._hb_fsdp` set.
 
@@ -644,6 +648,8 @@ def apply_fsdp(model, mesh=None, param_dtype=torch.bfloat16, reduce_dtype=torch.
     `block_iterator(model)` may yield `(key, block, container)` for models whose blocks live in
     more than one container (an encoder's blocks followed by the model's own); each yielded block
     becomes a unit. Without it the units are the entries of `model.<blocks_attr>`.
+    `tail_attrs` names the modules that run after the last block; when the model's forward calls
+    the pre-block hook with index == number of blocks before them, they form the "head" unit.
     `fused_all_gather` (default: the HB_FSDP_FUSED_GATHER environment variable) replaces the block
     units' parameter all-gather collective by copies carried inside GEMM launches (`FusedGather`);
     `fused_reduce_scatter` (HB_FSDP_FUSED_REDUCE) does the same for the gradient reduce-scatter
@@ -689,12 +695,35 @@ def apply_fsdp(model, mesh=None, param_dtype=torch.bfloat16, reduce_dtype=torch.
         if index is not None:
             block_units[index] = u
         taken.update(id(p) for p in u.params())   # the re-homed Parameter objects
+    # The output side of the model (final norm + head) becomes a unit of its own when the model's
+    # forward announces it (hook index == number of blocks): its gradients are the first ones of
+    # the backward pass, so their reduction starts at the top of backward and hides under all the
+    # blocks, instead of waiting in the root unit until the pass is over; and its parameters are
+    # the last ones the next forward needs, so its gather is queued last.
+    head_unit = None
+    tail_mods = [getattr(model, a, None) for a in tail_attrs]
+    tied = getattr(model, "tie_embeds", False)
+    if calls_block_hooks and block_units and not tied and tail_mods and tail_mods[-1] is not None:
+        ps = []
+        for mod in tail_mods:
+            if mod is not None:
+                got = _unit_params(mod, taken)
+                taken.update(id(p) for _, _, p in got)
+                ps.extend(got)
+        if ps:
+            head_unit = FlatUnit("head", ps, shard_group, replicate_group, param_dtype, reduce_dtype, device,
+                                 comm_stream)
+            taken.update(id(p) for p in head_unit.params())
+            block_units[len(listed)] = head_unit
     # tied head/embedding weights are one parameter: `_unit_params` de-duplicates by identity
     root_ps = _unit_params(model, taken)
     root = FlatUnit("root", root_ps, shard_group, replicate_group, param_dtype, reduce_dtype, device,
                     comm_stream)
-    units.append(root)
-    if getattr(model, "tie_embeds", False) and getattr(model, "head", None) is not None:
+    # order of use in a forward pass: root (embedding), the blocks, the head
+    units.insert(0, root)
+    if head_unit is not None:
+        units.append(head_unit)
+    if tied and getattr(model, "head", None) is not None:
         model.head.tie_weight(model.embedding.embed_weight)
 
     # move remaining buffers
@@ -704,7 +733,7 @@ def apply_fsdp(model, mesh=None, param_dtype=torch.bfloat16, reduce_dtype=torch.
                 mod._buffers[n] = torch.empty_like(b, device=device) if b.device.type == "meta" \
                     else b.to(device)
 
-    state = ShardedModel(model, units, root, shard_group, replicate_group, comm_stream)
+    state = ShardedModel(model, units, root, shard_group, replicate_group, comm_stream, head_unit)
     model._hb_fsdp = state
     _install_fused_views(model, units)
 

@@ -16,6 +16,12 @@ from halite_b200.parallel import ParallelDims, parallelize
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 mode = sys.argv[1] if len(sys.argv) > 1 else "fsdp"
+# "<mode>_micro": every step's batch goes through in two micro-batches, the first one inside
+# `no_sync()` (gradients only accumulate; one reduction per step); "<mode>_micro_sync" does the
+# same without `no_sync()` (a reduction per micro-batch, which must still give the right sum)
+micro = "_micro" in mode
+hold_back = micro and not mode.endswith("_sync")
+mode = mode.split("_")[0]
 
 
 def build():
@@ -39,7 +45,7 @@ else:
     pd = ParallelDims(dp_shard=ws)
 pd.build_mesh("cpu")
 rank = pd.rank
-steps = 20 if mode == "fsdp" else 6
+steps = 20 if mode == "fsdp" and not micro else 6
 g = torch.Generator().manual_seed(0)
 data = torch.randint(0, 1024, (ws, steps, 4, 257), generator=g)
 model, ref = build(), build()
@@ -49,8 +55,20 @@ ropt = torch.optim.AdamW(group_parameters(ref, 0.1), lr=3e-4, betas=(0.9, 0.95))
 worst = 0.0
 for step in range(steps):
     x = data[rank, step]
-    loss = torch.nn.functional.cross_entropy(model(x[:, :-1]).logits.flatten(0, 1), x[:, 1:].flatten())
-    loss.backward()
+    if micro:
+        import contextlib
+
+        loss = 0.0
+        for i, xm in enumerate(x.chunk(2)):
+            hold = model._hb_fsdp.no_sync() if hold_back and i == 0 else contextlib.nullcontext()
+            with hold:
+                lm = torch.nn.functional.cross_entropy(model(xm[:, :-1]).logits.flatten(0, 1),
+                                                       xm[:, 1:].flatten()) / 2
+                lm.backward()
+            loss = loss + lm.detach()
+    else:
+        loss = torch.nn.functional.cross_entropy(model(x[:, :-1]).logits.flatten(0, 1), x[:, 1:].flatten())
+        loss.backward()
     n = clip_grad_norm_(model, 1.0, opt)
     opt.step()
     opt.zero_grad()

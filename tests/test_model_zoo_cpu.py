@@ -196,5 +196,5 @@ def test_encoder_jit_on_a_small_vision_encoder_and_its_unit_layout():
     model = parallelize(model, param_dtype="float32", reduce_dtype="float32", device="cpu",
                         block_iterator=encoder_jit_block_iterator)
     names = [u.name for u in model._hb_fsdp.units]
-    assert names == ["encoder.blocks.0", "encoder.blocks.1", "blocks.0", "blocks.1", "blocks.2", "root"]
+    assert names == ["root", "encoder.blocks.0", "encoder.blocks.1", "blocks.0", "blocks.1", "blocks.2"]
     assert model(x, torch.rand(2), lab).shape == x.shape
