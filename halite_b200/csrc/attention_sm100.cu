@@ -1,0 +1,1073 @@
+// Training attention for sm_100a: softmax(mask(scale * Q K^T)) V and its gradients on tcgen05
+// tensor cores with the score / probability tiles held in tensor memory.
+//
+// Forward (`attn_fwd_kernel`): one CTA per 256 query rows of one head, 384 threads:
+//   warp 0 (one lane)   TMA producer: the two 128-row Q tiles once, then K_j, V_j tiles through
+//                       a shared-memory ring (cp.async.bulk.tensor, 128B swizzle, no multicast)
+//   warp 1 (one lane)   MMA issuer: S_t = Q_t K_j^T into TMEM, O_t += P_t V_j with P_t read from
+//                       TMEM (it overwrites the first half of S_t's columns as bf16)
+//   warp 2              TMEM allocation (all 512 columns: S_0 S_1 O_0 O_1)
+//   warps 4-7 / 8-11    softmax of tile 0 / tile 1: one thread per query row, online softmax
+//                       with deferred rescaling (O_t is only rescaled when a row's maximum grew
+//                       by more than 2^8), P_t written back to TMEM with tcgen05.st
+// While one tile's rows are in the softmax, the tensor cores work on the other tile.
+//
+// Backward (`attn_bwd_kernel`): one CTA per 128 key/value rows of one KV head; it walks the query
+// tiles (of every query head of the group) that can see those rows and keeps dK, dV in TMEM:
+//   S^T = K Q^T, dP^T = V dO^T         (TMEM; one thread per key row reads them)
+//   P^T = exp2(S^T c - lse)            -> TMEM (bf16, over S^T), A operand of dV += P^T dO
+//   dS^T = P^T (dP^T - delta) scale    -> shared memory, read K-major by dK += dS^T Q and
+//                                         MN-major by dQ = dS K
+//   dQ tile                            -> TMEM (over dP^T) -> fp32 atomic adds into dq_accum
+//
+// Masks (causal, sliding window, segment bounds for packed sequences / documents, soft-capping)
+// are evaluated from per-token bounds on the device; nothing depends on host-side lengths.
+//
+// Replaces the FlashAttention-2 / SDPA / FlexAttention calls of the reference
+// (transformers/attention.py:505-558, 600-643).
+#include "attention.h"
+
+#include <math.h>
+#include <stdio.h>
+
+#include <algorithm>
+
+#include "sm100.cuh"
+
+namespace hb {
+
+namespace {
+
+constexpr int kTile = 128;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleThreshold = 8.f;   // in log2 units: P values stay below 2^8
+
+struct AttnParams {
+  int total;
+  int n_heads, n_kv_heads;
+  int seq_len;
+  const int* seg_start;
+  const int* seg_end;
+  int causal;
+  int window;
+  float scale;
+  float softcap;
+  int* status;
+};
+
+// ---------------------------------------------------------------- extra tcgen05 forms
+// D[tmem] (+)= A[tmem] * B[smem]: A is a 128-lane x K tile of packed bf16 pairs in tensor memory.
+__device__ __forceinline__ void umma_bf16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+      "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+      "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+      "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+      "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// Segment of token t: [s0, s1).
+__device__ __forceinline__ void segment_of(const AttnParams& p, int t, int& s0, int& s1) {
+  if (p.seg_start) {
+    s0 = p.seg_start[t];
+    s1 = p.seg_end[t];
+  } else {
+    s0 = (t / p.seq_len) * p.seq_len;
+    s1 = min(s0 + p.seq_len, p.total);
+  }
+}
+// Keys that query row q may attend: [lo, hi] (empty when hi < lo).
+__device__ __forceinline__ void query_bounds(const AttnParams& p, int q, int& lo, int& hi) {
+  if (q >= p.total) {
+    lo = 0;
+    hi = -1;
+    return;
+  }
+  int s0, s1;
+  segment_of(p, q, s0, s1);
+  lo = s0;
+  hi = p.causal ? q : s1 - 1;
+  if (p.window > 0) {
+    lo = max(lo, q - p.window + 1);
+    if (!p.causal) hi = min(hi, q + p.window - 1);
+  }
+}
+// Queries that may attend key row k: [lo, hi].
+__device__ __forceinline__ void key_bounds(const AttnParams& p, int k, int& lo, int& hi) {
+  if (k >= p.total) {
+    lo = 0;
+    hi = -1;
+    return;
+  }
+  int s0, s1;
+  segment_of(p, k, s0, s1);
+  lo = p.causal ? k : s0;
+  hi = s1 - 1;
+  if (p.window > 0) {
+    hi = min(hi, k + p.window - 1);
+    if (!p.causal) lo = max(lo, k - p.window + 1);
+  }
+}
+
+// ================================================================== forward
+template <int D>
+struct FwdCfg {
+  static constexpr int kChunks = D / 64;                 // 64-element (128-byte) column chunks
+  static constexpr int kChunkBytes = kTile * 128;        // 128 rows x 128 bytes
+  static constexpr int kTileBytes = kChunks * kChunkBytes;
+  static constexpr int kStages = (D == 128) ? 4 : 6;
+  static constexpr int kSmemBytes = (2 + kStages) * kTileBytes + 1024;
+  static constexpr int kThreads = 384;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kOCol = 256;                       // O_t at kOCol + t * D
+};
+
+template <int D, bool kSoftcap>
+__global__ void __launch_bounds__(384, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, __nv_bfloat16* __restrict__ out,
+                float* __restrict__ lse, const __grid_constant__ AttnParams p) {
+  using C = FwdCfg<D>;
+  constexpr int kStages = C::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_q_full[2];
+  __shared__ __align__(8) uint64_t bar_kv_full[kStages];
+  __shared__ __align__(8) uint64_t bar_kv_empty[kStages];
+  __shared__ __align__(8) uint64_t bar_s_full[2];
+  __shared__ __align__(8) uint64_t bar_p_ready[2];
+  __shared__ __align__(8) uint64_t bar_o_full[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t q_smem[2] = {smem_base, smem_base + C::kTileBytes};
+  const uint32_t ring = smem_base + 2 * C::kTileBytes;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // ---- which 256 query rows, which head (heaviest blocks first)
+  const int H = p.n_heads;
+  int qb, head;
+  {
+    const int id = blockIdx.x;
+    if (!p.seg_start && p.seq_len % 256 == 0 && p.total % p.seq_len == 0) {
+      const int per_seq = p.seq_len / 256, nseq = p.total / p.seq_len;
+      const int pos = per_seq - 1 - id / (nseq * H);
+      const int rem = id % (nseq * H);
+      qb = (rem / H) * per_seq + pos;
+      head = rem % H;
+    } else {
+      const int nqb = (p.total + 255) / 256;
+      qb = nqb - 1 - id / H;
+      head = id % H;
+    }
+  }
+  const int kv_head = head / (H / p.n_kv_heads);
+  // ---- key tile range of each query tile
+  int jb[2], je[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int r0 = qb * 256 + t * kTile;
+    if (r0 >= p.total) {
+      jb[t] = je[t] = 0;
+      continue;
+    }
+    int lo, hi, lo2, hi2;
+    query_bounds(p, r0, lo, hi2);
+    query_bounds(p, min(r0 + kTile - 1, p.total - 1), lo2, hi);
+    jb[t] = lo / kTile;
+    je[t] = hi / kTile + 1;
+  }
+  const bool act1 = je[1] > jb[1];
+  const int J0 = act1 ? min(jb[0], jb[1]) : jb[0];
+  const int J1 = act1 ? max(je[0], je[1]) : je[0];
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(smem_u32(&bar_q_full[t]), 1);
+      mbar_init(smem_u32(&bar_s_full[t]), 1);
+      mbar_init(smem_u32(&bar_p_ready[t]), 4);
+      mbar_init(smem_u32(&bar_o_full[t]), 1);
+    }
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&bar_kv_full[s]), 1);
+      mbar_init(smem_u32(&bar_kv_empty[s]), 1);
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32(&tmem_slot), C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ------------------------------------------------------------ producer
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      if (je[t] <= jb[t]) continue;
+      const uint32_t full = smem_u32(&bar_q_full[t]);
+      mbar_expect_tx(full, C::kTileBytes);
+#pragma unroll
+      for (int c = 0; c < C::kChunks; ++c)
+        tma_load_3d(q_smem[t] + c * C::kChunkBytes, &tm_q, full, c * 64, head, qb * 256 + t * kTile);
+    }
+    int e = 0;
+    bool ok = true;
+    for (int j = J0; j < J1 && ok; ++j) {
+#pragma unroll
+      for (int which = 0; which < 2; ++which, ++e) {
+        const int stage = e % kStages;
+        const uint32_t phase = (e / kStages) & 1;
+        ok = mbar_wait(smem_u32(&bar_kv_empty[stage]), phase ^ 1, &abort_flag, p.status, kTimeoutEmpty);
+        if (!ok) break;
+        const uint32_t full = smem_u32(&bar_kv_full[stage]);
+        mbar_expect_tx(full, C::kTileBytes);
+        const uint32_t dst = ring + stage * C::kTileBytes;
+#pragma unroll
+        for (int c = 0; c < C::kChunks; ++c)
+          tma_load_3d(dst + c * C::kChunkBytes, which == 0 ? &tm_k : &tm_v, full, c * 64, kv_head, j * kTile);
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc_qk = make_idesc_bf16(kTile, kTile, false, false);
+    constexpr uint32_t idesc_pv = make_idesc_bf16(kTile, D, false, true);
+    bool ok = true;
+    auto issue_s = [&](int t, uint32_t k_addr) {
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const uint32_t off = (ks >> 2) * C::kChunkBytes + (ks & 3) * 32;
+        umma_bf16(tmem_base + t * kTile, make_smem_desc(q_smem[t] + off, 0, 1024),
+                  make_smem_desc(k_addr + off, 0, 1024), idesc_qk, ks != 0);
+      }
+      umma_commit(smem_u32(&bar_s_full[t]));
+    };
+    auto issue_pv = [&](int t, uint32_t v_addr, bool acc) {
+#pragma unroll
+      for (int ks = 0; ks < kTile / 16; ++ks)
+        umma_bf16_ta(tmem_base + C::kOCol + t * D, tmem_base + t * kTile + ks * 8,
+                     make_smem_desc(v_addr + ks * 2048, C::kChunkBytes, 1024), idesc_pv, acc || ks != 0);
+    };
+    auto wait_entry = [&](int e) -> bool {
+      return mbar_wait(smem_u32(&bar_kv_full[e % kStages]), (e / kStages) & 1, &abort_flag, p.status,
+                       kTimeoutFull);
+    };
+    auto entry_addr = [&](int e) -> uint32_t { return ring + (e % kStages) * C::kTileBytes; };
+    for (int t = 0; t < 2 && ok; ++t)
+      if (je[t] > jb[t]) ok = mbar_wait(smem_u32(&bar_q_full[t]), 0, &abort_flag, p.status, kTimeoutFull);
+    uint32_t n_p[2] = {0, 0};
+    if (ok && J1 > J0) {
+      ok = wait_entry(0);
+      if (ok) {
+        tc_fence_after();
+        for (int t = 0; t < 2; ++t)
+          if (jb[t] <= J0 && J0 < je[t]) issue_s(t, entry_addr(0));
+        umma_commit(smem_u32(&bar_kv_empty[0]));
+      }
+    }
+    for (int j = J0; j < J1 && ok; ++j) {
+      const int e_v = 2 * (j - J0) + 1, e_kn = e_v + 1;
+      const bool next = j + 1 < J1;
+      ok = wait_entry(e_v);
+      if (!ok) break;
+      bool have_next = false;
+      for (int t = 0; t < 2 && ok; ++t) {
+        if (jb[t] <= j && j < je[t]) {
+          ok = mbar_wait(smem_u32(&bar_p_ready[t]), n_p[t] & 1, &abort_flag, p.status, kTimeoutTmemEmpty);
+          if (!ok) break;
+          ++n_p[t];
+          tc_fence_after();
+          issue_pv(t, entry_addr(e_v), j > jb[t]);
+          if (j == je[t] - 1) umma_commit(smem_u32(&bar_o_full[t]));
+        }
+        if (next && jb[t] <= j + 1 && j + 1 < je[t]) {
+          if (!have_next) {
+            ok = wait_entry(e_kn);
+            if (!ok) break;
+            have_next = true;
+            tc_fence_after();
+          }
+          issue_s(t, entry_addr(e_kn));
+        }
+      }
+      if (!ok) break;
+      umma_commit(smem_u32(&bar_kv_empty[e_v % kStages]));
+      if (next) {
+        if (!have_next) ok = wait_entry(e_kn);
+        if (ok) umma_commit(smem_u32(&bar_kv_empty[e_kn % kStages]));
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------ softmax + epilogue
+    const int t = (warp - 4) >> 2;
+    const int wq = warp & 3;
+    if (je[t] > jb[t]) {
+      const int row = qb * 256 + t * kTile + wq * 32 + lane;
+      int lo, hi;
+      query_bounds(p, row, lo, hi);
+      const uint32_t lane_addr = static_cast<uint32_t>(wq * 32) << 16;
+      const uint32_t s_addr = tmem_base + t * kTile + lane_addr;
+      const uint32_t o_addr = tmem_base + C::kOCol + t * D + lane_addr;
+      const float c2 = kSoftcap ? kLog2e : p.scale * kLog2e;   // multiplies a (capped) score into log2 units
+      const float cap_in = kSoftcap ? p.scale / p.softcap : 0.f;
+      float m_used = -INFINITY, l = 0.f;
+      bool ok = true;
+      int k = 0;
+      for (int j = jb[t]; j < je[t]; ++j, ++k) {
+        ok = mbar_wait(smem_u32(&bar_s_full[t]), k & 1, &abort_flag, p.status, kTimeoutTmemFull);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        const int kv0 = j * kTile;
+        const bool mask_tile = __any_sync(0xffffffffu, kv0 < lo || kv0 + kTile - 1 > hi);
+        // ---- pass 1: row maximum of this tile (soft-capped scores are written back)
+        float mt = -INFINITY;
+#pragma unroll 1
+        for (int c = 0; c < kTile / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(s_addr + c * 32, v);
+          tmem_ld_wait();
+          if (kSoftcap) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              v[i] = __float_as_uint(p.softcap * tanh_fast(__uint_as_float(v[i]) * cap_in));
+            tmem_st_32x32(s_addr + c * 32, v);
+          }
+          if (mask_tile) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int kv = kv0 + c * 32 + i;
+              if (kv >= lo && kv <= hi) mt = fmaxf(mt, __uint_as_float(v[i]));
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mt = fmaxf(mt, __uint_as_float(v[i]));
+          }
+        }
+        if (kSoftcap) tmem_st_wait();
+        // ---- deferred rescaling of the running output
+        const float m_new = fmaxf(m_used, mt);
+        float m_next = m_used;
+        if (k == 0 || (m_new - m_used) * c2 > kRescaleThreshold) m_next = m_new;
+        const bool rescale = k != 0 && m_next != m_used;
+        if (__any_sync(0xffffffffu, rescale)) {
+          const float alpha = (m_next == m_used) ? 1.f : exp2f((m_used - m_next) * c2);
+          l *= alpha;
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld_32x32(o_addr + c * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_st_32x32(o_addr + c * 32, v);
+          }
+          tmem_st_wait();
+        }
+        m_used = m_next;
+        const float mc = (m_used == -INFINITY) ? 0.f : m_used * c2;
+        // ---- pass 2: P = exp2(S c2 - m c2) as bf16 pairs over the first half of S's columns
+#pragma unroll 1
+        for (int c = 0; c < kTile / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(s_addr + c * 32, v);
+          tmem_ld_wait();
+          float pr[32];
+          if (mask_tile) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int kv = kv0 + c * 32 + i;
+              const float e = exp2f(fmaf(__uint_as_float(v[i]), c2, -mc));
+              pr[i] = (kv >= lo && kv <= hi) ? e : 0.f;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) pr[i] = exp2f(fmaf(__uint_as_float(v[i]), c2, -mc));
+          }
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            l += pr[2 * i] + pr[2 * i + 1];
+            pk[i] = pack_bf16x2(pr[2 * i], pr[2 * i + 1]);
+          }
+          tmem_st_32x16(s_addr + c * 16, pk);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_p_ready[t]));
+      }
+      if (ok) {
+        ok = mbar_wait(smem_u32(&bar_o_full[t]), 0, &abort_flag, p.status, kTimeoutTmemFull);
+        ok = __all_sync(0xffffffffu, ok);
+      }
+      if (ok) {
+        tc_fence_after();
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        const bool live = row < p.total;
+        __nv_bfloat16* dst = out + (static_cast<size_t>(row) * H + head) * D;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(o_addr + c * 32, v);
+          tmem_ld_wait();
+          if (live) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(v[8 * g]) * inv, __uint_as_float(v[8 * g + 1]) * inv);
+              o.y = pack_bf16x2(__uint_as_float(v[8 * g + 2]) * inv, __uint_as_float(v[8 * g + 3]) * inv);
+              o.z = pack_bf16x2(__uint_as_float(v[8 * g + 4]) * inv, __uint_as_float(v[8 * g + 5]) * inv);
+              o.w = pack_bf16x2(__uint_as_float(v[8 * g + 6]) * inv, __uint_as_float(v[8 * g + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = o;
+            }
+          }
+        }
+        if (live) {
+          const float m_nat = (m_used == -INFINITY) ? 0.f : m_used * (kSoftcap ? 1.f : p.scale);
+          lse[static_cast<size_t>(head) * p.total + row] = l > 0.f ? m_nat + __logf(l) : 0.f;
+        }
+      }
+    }
+  }
+
+  if (abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);   // let copies in flight land
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ================================================================== backward
+template <int D>
+struct BwdCfg {
+  static constexpr int kChunks = D / 64;
+  static constexpr int kChunkBytes = kTile * 128;
+  static constexpr int kTileBytes = kChunks * kChunkBytes;
+  static constexpr int kRing = 3;                               // Q_i, dO_i, Q_{i+1}
+  static constexpr int kDsBytes = 2 * kChunkBytes;              // dS^T: 128 key rows x 128 query columns
+  static constexpr int kVecBytes = 2 * 2 * kTile * 4;           // lse, delta: two buffers each
+  static constexpr int kSmemBytes = (2 + kRing) * kTileBytes + kDsBytes + kVecBytes + 1024;
+  static constexpr int kThreads = 256;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kDpCol = 128;                            // dP^T, later the dQ tile
+  static constexpr int kDkCol = 256;
+  static constexpr int kDvCol = 256 + D;
+};
+
+// delta[h, t] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (token, head)
+template <int D>
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                                  float* __restrict__ delta, int total, int heads) {
+  const long n = static_cast<long>(total) * heads;
+  const int lane = threadIdx.x & 31;
+  for (long w = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; w < n;
+       w += (static_cast<long>(gridDim.x) * blockDim.x) >> 5) {
+    const __nv_bfloat16* a = o + w * D;
+    const __nv_bfloat16* b = d_o + w * D;
+    float acc = 0.f;
+    // D / 32 consecutive elements per lane
+    constexpr int kPer = D / 32;
+    const __nv_bfloat16* pa = a + lane * kPer;
+    const __nv_bfloat16* pb = b + lane * kPer;
+#pragma unroll
+    for (int i = 0; i < kPer; i += 2) {
+      const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(pa + i));
+      const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(pb + i));
+      acc = fmaf(x.x, y.x, acc);
+      acc = fmaf(x.y, y.y, acc);
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+    if (lane == 0) {
+      const long tok = w / heads;
+      const int h = static_cast<int>(w - tok * heads);
+      delta[static_cast<size_t>(h) * total + tok] = acc;
+    }
+  }
+}
+
+__global__ void attn_dq_convert_kernel(const float4* __restrict__ src, uint2* __restrict__ dst, long n4) {
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const float4 v = src[i];
+    uint2 o;
+    o.x = pack_bf16x2(v.x, v.y);
+    o.y = pack_bf16x2(v.z, v.w);
+    dst[i] = o;
+  }
+}
+
+template <int D, bool kSoftcap>
+__global__ void __launch_bounds__(256, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                const float* __restrict__ lse, const float* __restrict__ delta,
+                float* __restrict__ dq_accum, __nv_bfloat16* __restrict__ dk, long dk_stride,
+                __nv_bfloat16* __restrict__ dv, long dv_stride, const __grid_constant__ AttnParams p) {
+  using C = BwdCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_kv_full;
+  __shared__ __align__(8) uint64_t bar_ring_full[C::kRing];
+  __shared__ __align__(8) uint64_t bar_ring_empty[C::kRing];
+  __shared__ __align__(8) uint64_t bar_s_full, bar_dp_full, bar_p_ready, bar_ds_ready, bar_dq_full, bar_dq_free,
+      bar_dkv_full;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t k_smem = smem_base;
+  const uint32_t v_smem = smem_base + C::kTileBytes;
+  const uint32_t ring = smem_base + 2 * C::kTileBytes;
+  const uint32_t ds_smem = ring + C::kRing * C::kTileBytes;
+  float* vec = reinterpret_cast<float*>(smem_raw + (ds_smem + C::kDsBytes - smem_u32(smem_raw)));
+  // vec layout: [buffer][lse2 | delta][128]
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int Hk = p.n_kv_heads, G = p.n_heads / Hk;
+  int jk, hk;
+  {
+    const int id = blockIdx.x;
+    if (!p.seg_start && p.seq_len % kTile == 0 && p.total % p.seq_len == 0) {
+      const int per_seq = p.seq_len / kTile, nseq = p.total / p.seq_len;
+      const int pos = id / (nseq * Hk);          // early key tiles are seen by the most queries: first
+      const int rem = id % (nseq * Hk);
+      jk = (rem / Hk) * per_seq + pos;
+      hk = rem % Hk;
+    } else {
+      jk = id / Hk;
+      hk = id % Hk;
+    }
+  }
+  const int k0 = jk * kTile;
+  int ib, ie;
+  {
+    int lo, hi, lo2, hi2;
+    key_bounds(p, k0, lo, hi2);
+    key_bounds(p, min(k0 + kTile - 1, p.total - 1), lo2, hi);
+    ib = lo / kTile;
+    ie = hi / kTile + 1;
+    if (ie < ib) ie = ib;
+  }
+  const int n_i = ie - ib;
+  const int n_it = n_i * G;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar_kv_full), 1);
+    for (int s = 0; s < C::kRing; ++s) {
+      mbar_init(smem_u32(&bar_ring_full[s]), 1);
+      mbar_init(smem_u32(&bar_ring_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&bar_s_full), 1);
+    mbar_init(smem_u32(&bar_dp_full), 1);
+    mbar_init(smem_u32(&bar_p_ready), 4);
+    mbar_init(smem_u32(&bar_ds_ready), 4);
+    mbar_init(smem_u32(&bar_dq_full), 1);
+    mbar_init(smem_u32(&bar_dq_free), 4);
+    mbar_init(smem_u32(&bar_dkv_full), 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+    tma_prefetch_desc(&tm_do);
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32(&tmem_slot), C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ------------------------------------------------------------ producer
+    {
+      const uint32_t full = smem_u32(&bar_kv_full);
+      mbar_expect_tx(full, 2 * C::kTileBytes);
+#pragma unroll
+      for (int c = 0; c < C::kChunks; ++c) {
+        tma_load_3d(k_smem + c * C::kChunkBytes, &tm_k, full, c * 64, hk, k0);
+        tma_load_3d(v_smem + c * C::kChunkBytes, &tm_v, full, c * 64, hk, k0);
+      }
+    }
+    bool ok = true;
+    int e = 0;
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int h = hk * G + it / n_i;
+      const int q0 = (ib + it % n_i) * kTile;
+#pragma unroll
+      for (int which = 0; which < 2; ++which, ++e) {
+        const int stage = e % C::kRing;
+        const uint32_t phase = (e / C::kRing) & 1;
+        ok = mbar_wait(smem_u32(&bar_ring_empty[stage]), phase ^ 1, &abort_flag, p.status, kTimeoutEmpty);
+        if (!ok) break;
+        const uint32_t full = smem_u32(&bar_ring_full[stage]);
+        mbar_expect_tx(full, C::kTileBytes);
+        const uint32_t dst = ring + stage * C::kTileBytes;
+#pragma unroll
+        for (int c = 0; c < C::kChunks; ++c)
+          tma_load_3d(dst + c * C::kChunkBytes, which == 0 ? &tm_q : &tm_do, full, c * 64, h, q0);
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc_kk = make_idesc_bf16(kTile, kTile, false, false);   // S^T, dP^T
+    constexpr uint32_t idesc_acc = make_idesc_bf16(kTile, D, false, true);       // dV, dK
+    constexpr uint32_t idesc_dq = make_idesc_bf16(kTile, D, true, true);         // dQ
+    bool ok = mbar_wait(smem_u32(&bar_kv_full), 0, &abort_flag, p.status, kTimeoutFull);
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int e_q = 2 * it, e_o = 2 * it + 1;
+      const uint32_t q_addr = ring + (e_q % C::kRing) * C::kTileBytes;
+      const uint32_t o_addr = ring + (e_o % C::kRing) * C::kTileBytes;
+      const uint32_t par = it & 1;
+      // S^T = K Q^T
+      ok = mbar_wait(smem_u32(&bar_ring_full[e_q % C::kRing]), (e_q / C::kRing) & 1, &abort_flag, p.status,
+                     kTimeoutFull);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const uint32_t off = (ks >> 2) * C::kChunkBytes + (ks & 3) * 32;
+        umma_bf16(tmem_base, make_smem_desc(k_smem + off, 0, 1024), make_smem_desc(q_addr + off, 0, 1024),
+                  idesc_kk, ks != 0);
+      }
+      umma_commit(smem_u32(&bar_s_full));
+      // dP^T = V dO^T (its columns held the previous dQ tile until the drain finished)
+      ok = mbar_wait(smem_u32(&bar_ring_full[e_o % C::kRing]), (e_o / C::kRing) & 1, &abort_flag, p.status,
+                     kTimeoutFull);
+      if (ok && it > 0)
+        ok = mbar_wait(smem_u32(&bar_dq_free), (it - 1) & 1, &abort_flag, p.status, kTimeoutTmemEmpty);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const uint32_t off = (ks >> 2) * C::kChunkBytes + (ks & 3) * 32;
+        umma_bf16(tmem_base + C::kDpCol, make_smem_desc(v_smem + off, 0, 1024),
+                  make_smem_desc(o_addr + off, 0, 1024), idesc_kk, ks != 0);
+      }
+      umma_commit(smem_u32(&bar_dp_full));
+      // dV += P^T dO
+      ok = mbar_wait(smem_u32(&bar_p_ready), par, &abort_flag, p.status, kTimeoutTmemEmpty);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int ks = 0; ks < kTile / 16; ++ks)
+        umma_bf16_ta(tmem_base + C::kDvCol, tmem_base + ks * 8,
+                     make_smem_desc(o_addr + ks * 2048, C::kChunkBytes, 1024), idesc_acc, it > 0 || ks != 0);
+      umma_commit(smem_u32(&bar_ring_empty[e_o % C::kRing]));
+      // dK += dS^T Q, dQ = dS K
+      ok = mbar_wait(smem_u32(&bar_ds_ready), par, &abort_flag, p.status, kTimeoutTmemEmpty);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int ks = 0; ks < kTile / 16; ++ks) {
+        const uint32_t a_off = (ks >> 2) * C::kChunkBytes + (ks & 3) * 32;
+        umma_bf16(tmem_base + C::kDkCol, make_smem_desc(ds_smem + a_off, 0, 1024),
+                  make_smem_desc(q_addr + ks * 2048, C::kChunkBytes, 1024), idesc_acc, it > 0 || ks != 0);
+      }
+#pragma unroll
+      for (int ks = 0; ks < kTile / 16; ++ks)
+        umma_bf16(tmem_base + C::kDpCol, make_smem_desc(ds_smem + ks * 2048, C::kChunkBytes, 1024),
+                  make_smem_desc(k_smem + ks * 2048, C::kChunkBytes, 1024), idesc_dq, ks != 0);
+      umma_commit(smem_u32(&bar_dq_full));
+      umma_commit(smem_u32(&bar_ring_empty[e_q % C::kRing]));
+    }
+    if (ok) umma_commit(smem_u32(&bar_dkv_full));
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------ elementwise + drains
+    const int wq = warp & 3;
+    const int r = wq * 32 + lane;              // key row in the first two phases, query row in the drain
+    const int kpos = k0 + r;
+    int qlo, qhi;
+    key_bounds(p, kpos, qlo, qhi);
+    const uint32_t lane_addr = static_cast<uint32_t>(wq * 32) << 16;
+    const uint32_t s_addr = tmem_base + lane_addr;
+    const uint32_t dp_addr = tmem_base + C::kDpCol + lane_addr;
+    const float c2 = kSoftcap ? kLog2e : p.scale * kLog2e;
+    const float cap_in = kSoftcap ? p.scale / p.softcap : 0.f;
+    const uint32_t ds_row = ds_smem + r * 128;
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      const int h = hk * G + it / n_i;
+      const int q0 = (ib + it % n_i) * kTile;
+      const uint32_t par = it & 1;
+      float* lse2 = vec + (it & 1) * 2 * kTile;
+      float* dlt = lse2 + kTile;
+      {
+        const int q = q0 + r;
+        const bool live = q < p.total;
+        lse2[r] = live ? lse[static_cast<size_t>(h) * p.total + q] * kLog2e : INFINITY;
+        dlt[r] = live ? delta[static_cast<size_t>(h) * p.total + q] : 0.f;
+      }
+      named_barrier_sync(1, 128);
+      const bool mask_tile = __any_sync(0xffffffffu, q0 < qlo || q0 + kTile - 1 > qhi);
+      // ---- P^T
+      ok = mbar_wait(smem_u32(&bar_s_full), par, &abort_flag, p.status, kTimeoutTmemFull);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t pk[kTile / 2];
+#pragma unroll
+      for (int c = 0; c < kTile / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(s_addr + c * 32, v);
+        tmem_ld_wait();
+        float pr[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = __uint_as_float(v[i]);
+          if (kSoftcap) {
+            const float th = tanh_fast(s * cap_in);
+            s = p.softcap * th;
+            v[i] = __float_as_uint(1.f - th * th);
+          }
+          const int q = q0 + c * 32 + i;
+          const float e = exp2f(fmaf(s, c2, -lse2[c * 32 + i]));
+          pr[i] = (!mask_tile || (q >= qlo && q <= qhi)) ? e : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) pk[c * 16 + i] = pack_bf16x2(pr[2 * i], pr[2 * i + 1]);
+        if (kSoftcap) {
+          // park d(capped score)/d(score) in this row's slot of the dS buffer until dP arrives
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const uint32_t u = static_cast<uint32_t>((c & 1) * 4 + g);
+            st_shared_v4(ds_row + (c >> 1) * C::kChunkBytes + ((u ^ (r & 7)) << 4),
+                         pack_bf16x2(__uint_as_float(v[8 * g]), __uint_as_float(v[8 * g + 1])),
+                         pack_bf16x2(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3])),
+                         pack_bf16x2(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5])),
+                         pack_bf16x2(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7])));
+          }
+        }
+        uint32_t pc[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) pc[i] = pk[c * 16 + i];
+        tmem_st_32x16(s_addr + c * 16, pc);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_p_ready));
+      // ---- dS^T
+      ok = mbar_wait(smem_u32(&bar_dp_full), par, &abort_flag, p.status, kTimeoutTmemFull);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < kTile / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(dp_addr + c * 32, v);
+        tmem_ld_wait();
+        float ds[32];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float2 pp = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk[c * 16 + i]));
+          ds[2 * i] = pp.x * (__uint_as_float(v[2 * i]) - dlt[c * 32 + 2 * i]) * p.scale;
+          ds[2 * i + 1] = pp.y * (__uint_as_float(v[2 * i + 1]) - dlt[c * 32 + 2 * i + 1]) * p.scale;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const uint32_t u = static_cast<uint32_t>((c & 1) * 4 + g);
+          const uint32_t addr = ds_row + (c >> 1) * C::kChunkBytes + ((u ^ (r & 7)) << 4);
+          if (kSoftcap) {
+            const uint4 gq = ld_shared_v4(addr);
+            const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gq);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 gg = __bfloat1622float2(g2[i]);
+              ds[8 * g + 2 * i] *= gg.x;
+              ds[8 * g + 2 * i + 1] *= gg.y;
+            }
+          }
+          st_shared_v4(addr, pack_bf16x2(ds[8 * g], ds[8 * g + 1]), pack_bf16x2(ds[8 * g + 2], ds[8 * g + 3]),
+                       pack_bf16x2(ds[8 * g + 4], ds[8 * g + 5]), pack_bf16x2(ds[8 * g + 6], ds[8 * g + 7]));
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();      // the tensor cores read dS^T through the async proxy
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_ds_ready));
+      // ---- dQ tile: this thread now owns query row q0 + r
+      ok = mbar_wait(smem_u32(&bar_dq_full), par, &abort_flag, p.status, kTimeoutTmemFull);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      {
+        const int q = q0 + r;
+        float* dst = dq_accum + (static_cast<size_t>(q) * p.n_heads + h) * D;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(dp_addr + c * 32, v);
+          tmem_ld_wait();
+          if (q < p.total) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              atomicAdd(reinterpret_cast<float4*>(dst + c * 32 + g * 4),
+                        make_float4(__uint_as_float(v[4 * g]), __uint_as_float(v[4 * g + 1]),
+                                    __uint_as_float(v[4 * g + 2]), __uint_as_float(v[4 * g + 3])));
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_dq_free));
+    }
+    // ---- dK, dV of this key tile
+    if (ok && n_it > 0) {
+      ok = mbar_wait(smem_u32(&bar_dkv_full), 0, &abort_flag, p.status, kTimeoutTmemFull);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok && kpos < p.total) {
+      if (n_it > 0) tc_fence_after();
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t addr = tmem_base + (which == 0 ? C::kDkCol : C::kDvCol) + lane_addr;
+        __nv_bfloat16* dst = which == 0 ? dk + static_cast<size_t>(kpos) * dk_stride + hk * D
+                                        : dv + static_cast<size_t>(kpos) * dv_stride + hk * D;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t v[32];
+          if (n_it > 0) {
+            tmem_ld_32x32(addr + c * 32, v);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0u;       // no query sees these keys
+          }
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(v[8 * g]), __uint_as_float(v[8 * g + 1]));
+            o.y = pack_bf16x2(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3]));
+            o.z = pack_bf16x2(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5]));
+            o.w = pack_bf16x2(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7]));
+            *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = o;
+          }
+        }
+      }
+    }
+  }
+
+  if (abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ================================================================== host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* ptr = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  return fn;
+}
+
+// [tokens, heads, head_dim] bf16 with `tok_stride` elements between tokens; box = 128 tokens of
+// one head, 64 elements wide, 128-byte swizzle, zeros beyond the last token.
+bool make_tmap_heads(CUtensorMap* map, const void* base, int tokens, int heads, int head_dim, long tok_stride) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    // the encode call is a driver entry point: bind the primary context in threads that have not
+    // made a runtime call yet (autograd's backward workers)
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) return false;
+    (void)cudaFree(nullptr);
+    ctx_bound = true;
+  }
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(heads),
+                        static_cast<cuuint64_t>(tokens)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(head_dim) * 2, static_cast<cuuint64_t>(tok_stride) * 2};
+  cuuint32_t box[3] = {64, 1, kTile};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    fprintf(stderr, "halite_b200: attention tensor map failed (%d): tokens=%d heads=%d dim=%d stride=%ld base=%p\n",
+            static_cast<int>(r), tokens, heads, head_dim, tok_stride, base);
+  return r == CUDA_SUCCESS;
+}
+
+cudaError_t check_args(const AttnArgs& a) {
+  if (a.total <= 0) return cudaSuccess;
+  if ((a.head_dim != 64 && a.head_dim != 128) || a.n_heads <= 0 || a.n_kv_heads <= 0 ||
+      a.n_heads % a.n_kv_heads != 0)
+    return cudaErrorInvalidValue;
+  if (!a.seg_start && a.seq_len <= 0) return cudaErrorInvalidValue;
+  if ((a.seg_start == nullptr) != (a.seg_end == nullptr)) return cudaErrorInvalidValue;
+  if (a.q_tok_stride % 8 || a.k_tok_stride % 8 || a.v_tok_stride % 8) return cudaErrorInvalidValue;
+  if ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) | reinterpret_cast<uintptr_t>(a.v)) & 15)
+    return cudaErrorInvalidValue;
+  return cudaSuccess;
+}
+
+AttnParams to_params(const AttnArgs& a) {
+  AttnParams p;
+  p.total = a.total;
+  p.n_heads = a.n_heads;
+  p.n_kv_heads = a.n_kv_heads;
+  p.seq_len = a.seq_len > 0 ? a.seq_len : a.total;
+  p.seg_start = a.seg_start;
+  p.seg_end = a.seg_end;
+  p.causal = a.causal ? 1 : 0;
+  p.window = a.window;
+  p.scale = a.scale;
+  p.softcap = a.softcap;
+  p.status = a.status;
+  return p;
+}
+
+template <int D, bool SC>
+cudaError_t launch_fwd(const AttnArgs& a, void* out, float* lse) {
+  using C = FwdCfg<D>;
+  CUtensorMap tq, tk, tv;
+  if (!make_tmap_heads(&tq, a.q, a.total, a.n_heads, D, a.q_tok_stride) ||
+      !make_tmap_heads(&tk, a.k, a.total, a.n_kv_heads, D, a.k_tok_stride) ||
+      !make_tmap_heads(&tv, a.v, a.total, a.n_kv_heads, D, a.v_tok_stride))
+    return cudaErrorInvalidValue;
+  auto kern = attn_fwd_kernel<D, SC>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const int nqb = (a.total + 255) / 256;
+  kern<<<nqb * a.n_heads, C::kThreads, C::kSmemBytes, a.stream>>>(tq, tk, tv, static_cast<__nv_bfloat16*>(out), lse,
+                                                                  to_params(a));
+  return cudaGetLastError();
+}
+
+template <int D, bool SC>
+cudaError_t launch_bwd(const AttnArgs& a, const void* o, const void* d_o, const float* lse, float* delta,
+                       float* dq_accum, void* dq, void* dk, long dk_stride, void* dv, long dv_stride) {
+  using C = BwdCfg<D>;
+  CUtensorMap tq, tk, tv, tdo;
+  if (!make_tmap_heads(&tq, a.q, a.total, a.n_heads, D, a.q_tok_stride) ||
+      !make_tmap_heads(&tk, a.k, a.total, a.n_kv_heads, D, a.k_tok_stride) ||
+      !make_tmap_heads(&tv, a.v, a.total, a.n_kv_heads, D, a.v_tok_stride) ||
+      !make_tmap_heads(&tdo, d_o, a.total, a.n_heads, D, static_cast<long>(a.n_heads) * D))
+    return cudaErrorInvalidValue;
+  auto kern = attn_bwd_kernel<D, SC>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const size_t n = static_cast<size_t>(a.total) * a.n_heads * D;
+  cudaError_t e = cudaMemsetAsync(dq_accum, 0, n * sizeof(float), a.stream);
+  if (e != cudaSuccess) return e;
+  {
+    const long warps = static_cast<long>(a.total) * a.n_heads;
+    const int grid = static_cast<int>(std::min<long>((warps + 7) / 8, 148L * 16));
+    attn_delta_kernel<D><<<grid, 256, 0, a.stream>>>(static_cast<const __nv_bfloat16*>(o),
+                                                      static_cast<const __nv_bfloat16*>(d_o), delta, a.total,
+                                                      a.n_heads);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
+  const int nkt = (a.total + kTile - 1) / kTile;
+  kern<<<nkt * a.n_kv_heads, C::kThreads, C::kSmemBytes, a.stream>>>(
+      tq, tk, tv, tdo, lse, delta, dq_accum, static_cast<__nv_bfloat16*>(dk), dk_stride,
+      static_cast<__nv_bfloat16*>(dv), dv_stride, to_params(a));
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  {
+    const long n4 = static_cast<long>(n / 4);
+    const int grid = static_cast<int>(std::min<long>((n4 + 255) / 256, 148L * 16));
+    attn_dq_convert_kernel<<<grid, 256, 0, a.stream>>>(reinterpret_cast<const float4*>(dq_accum),
+                                                       reinterpret_cast<uint2*>(dq), n4);
+    e = cudaGetLastError();
+  }
+  return e;
+}
+
+}  // namespace
+
+cudaError_t attention_fwd(const AttnArgs& a, void* out, float* lse) {
+  cudaError_t e = check_args(a);
+  if (e != cudaSuccess || a.total <= 0) return e;
+  const bool sc = a.softcap > 0.f;
+  if (a.head_dim == 128) return sc ? launch_fwd<128, true>(a, out, lse) : launch_fwd<128, false>(a, out, lse);
+  return sc ? launch_fwd<64, true>(a, out, lse) : launch_fwd<64, false>(a, out, lse);
+}
+
+cudaError_t attention_bwd(const AttnArgs& a, const void* o, const void* d_o, const float* lse, float* delta,
+                          float* dq_accum, void* dq, void* dk, long dk_tok_stride, void* dv, long dv_tok_stride) {
+  cudaError_t e = check_args(a);
+  if (e != cudaSuccess || a.total <= 0) return e;
+  if (dk_tok_stride % 8 || dv_tok_stride % 8) return cudaErrorInvalidValue;
+  const bool sc = a.softcap > 0.f;
+  if (a.head_dim == 128)
+    return sc ? launch_bwd<128, true>(a, o, d_o, lse, delta, dq_accum, dq, dk, dk_tok_stride, dv, dv_tok_stride)
+              : launch_bwd<128, false>(a, o, d_o, lse, delta, dq_accum, dq, dk, dk_tok_stride, dv, dv_tok_stride);
+  return sc ? launch_bwd<64, true>(a, o, d_o, lse, delta, dq_accum, dq, dk, dk_tok_stride, dv, dv_tok_stride)
+            : launch_bwd<64, false>(a, o, d_o, lse, delta, dq_accum, dq, dk, dk_tok_stride, dv, dv_tok_stride);
+}
+
+}  // namespace hb

@@ -176,6 +176,7 @@ void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& out, bool a_mn, 
 
 void register_elementwise(pybind11::module_& m);  // ops_bindings.cpp
 void register_infer(pybind11::module_& m);        // infer_bindings.cpp
+void register_attention(pybind11::module_& m);    // attention_bindings.cpp
 
 void register_runtime(py::module_& m);
 
@@ -194,5 +195,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("reset_launch_count", []() { hb::launch_counter().store(0); });
   register_elementwise(m);
   register_infer(m);
+  register_attention(m);
   register_runtime(m);
 }

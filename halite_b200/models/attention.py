@@ -128,7 +128,10 @@ class Attention(nn.Module):
                                       max_seqlen=unpad_params.max_length_q, **kwargs)
         mask = attention_mask
         if mask is not None and hasattr(mask, "to_attention_kwargs"):
-            kwargs.update(mask.to_attention_kwargs(query.shape[1], key.shape[1], query.device))
+            resolved = mask.to_attention_kwargs(query.shape[1], key.shape[1], query.device)
+            if resolved.get("window") is None:
+                resolved.pop("window", None)         # the module's own window stays in force
+            kwargs.update(resolved)
             mask = kwargs.pop("mask", None)
         if self.processor == "native" or attention_bias is not None or mask is not None:
             if mask is not None and mask.dtype != torch.bool:

@@ -4,9 +4,10 @@ Each mask class keeps the reference's calling convention: called with its declar
 returns a `mask_mod(b, h, q_idx, kv_idx) -> bool` (True = may attend). On top of that every
 class carries a structured description (`MaskSpec`): whether it is causal, its window, and the
 per-batch document offsets. `FlexAttentionProcessor` returns a `ResolvedMask` that the
-attention dispatcher turns either into kernel arguments (causal flag, window, per-document
-varlen) or, for arbitrary programs, into a dense boolean mask evaluated once per batch and
-cached according to the update mode.
+attention dispatcher turns either into kernel arguments (causal flag, window, per-row document
+offsets, which become per-token segment bounds on the device) or, for arbitrary programs and
+score modifiers, into a dense boolean mask evaluated once per batch and cached according to the
+update mode.
 """
 
 from __future__ import annotations
@@ -62,8 +63,13 @@ class ResolvedMask:
 
     def to_attention_kwargs(self, q_len, kv_len, device):
         s = self.spec
-        if not s.opaque and s.document_offsets is None and self.score_mod is None:
-            return {"causal": s.causal, "window": s.window}
+        if not s.opaque and self.score_mod is None:
+            # causal flag, window and per-row document offsets are arguments of the attention
+            # kernel; only programs that cannot be described that way are evaluated densely
+            out = {"causal": s.causal, "window": s.window}
+            if s.document_offsets is not None:
+                out["document_offsets"] = s.document_offsets
+            return out
         return {"causal": False, "window": None, "mask": self.dense(device)}
 
 
