@@ -4,7 +4,7 @@
 // sequence of a [batch, seq] tensor, a document of a packed batch). Token q may attend token k
 // when both lie in the same segment and
 //     causal:      k <= q            (else k anywhere in the segment)
-//     window > 0:  q - k < window    (and k - q < window when not causal)
+//     window > 0:  q - k < window    (how far back a query looks; keys after q are not limited)
 // Segments are either equal-length (`seq_len`, token t belongs to segment t / seq_len) or given
 // per token by `seg_start[t]` / `seg_end[t]` (first token of t's segment, one past its last):
 // that one form covers fixed batches, `cu_seqlens` packing and document masks, and keeps every

@@ -93,9 +93,6 @@ __device__ __forceinline__ float tanh_fast(float x) {
   asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
 
 // Segment of token t: [s0, s1).
 __device__ __forceinline__ void segment_of(const AttnParams& p, int t, int& s0, int& s1) {
@@ -118,10 +115,7 @@ __device__ __forceinline__ void query_bounds(const AttnParams& p, int q, int& lo
   segment_of(p, q, s0, s1);
   lo = s0;
   hi = p.causal ? q : s1 - 1;
-  if (p.window > 0) {
-    lo = max(lo, q - p.window + 1);
-    if (!p.causal) hi = min(hi, q + p.window - 1);
-  }
+  if (p.window > 0) lo = max(lo, q - p.window + 1);     // the window limits how far back a query looks
 }
 // Queries that may attend key row k: [lo, hi].
 __device__ __forceinline__ void key_bounds(const AttnParams& p, int k, int& lo, int& hi) {
@@ -134,10 +128,7 @@ __device__ __forceinline__ void key_bounds(const AttnParams& p, int k, int& lo, 
   segment_of(p, k, s0, s1);
   lo = p.causal ? k : s0;
   hi = s1 - 1;
-  if (p.window > 0) {
-    hi = min(hi, k + p.window - 1);
-    if (!p.causal) lo = max(lo, k - p.window + 1);
-  }
+  if (p.window > 0) hi = min(hi, k + p.window - 1);
 }
 
 // ================================================================== forward
@@ -169,6 +160,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   __shared__ __align__(8) uint64_t bar_o_full[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+
+  // a launch whose status word already reports a failed wait does nothing: a protocol error then
+  // costs one wait budget, not one per CTA
+  if (threadIdx.x == 0) abort_flag = p.status ? *reinterpret_cast<volatile int*>(p.status) : 0;
+  __syncthreads();
+  if (abort_flag) return;
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t q_smem[2] = {smem_base, smem_base + C::kTileBytes};
@@ -489,7 +486,7 @@ struct BwdCfg {
   static constexpr int kTileBytes = kChunks * kChunkBytes;
   static constexpr int kRing = 3;                               // Q_i, dO_i, Q_{i+1}
   static constexpr int kDsBytes = 2 * kChunkBytes;              // dS^T: 128 key rows x 128 query columns
-  static constexpr int kVecBytes = 2 * 2 * kTile * 4;           // lse, delta: two buffers each
+  static constexpr int kVecBytes = 4 * 2 * kTile * 4;           // lse, delta of the current query tile, one copy per warp
   static constexpr int kSmemBytes = (2 + kRing) * kTileBytes + kDsBytes + kVecBytes + 1024;
   static constexpr int kThreads = 256;
   static constexpr int kTmemCols = 512;
@@ -558,13 +555,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
+  if (threadIdx.x == 0) abort_flag = p.status ? *reinterpret_cast<volatile int*>(p.status) : 0;
+  __syncthreads();
+  if (abort_flag) return;
+
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t k_smem = smem_base;
   const uint32_t v_smem = smem_base + C::kTileBytes;
   const uint32_t ring = smem_base + 2 * C::kTileBytes;
   const uint32_t ds_smem = ring + C::kRing * C::kTileBytes;
   float* vec = reinterpret_cast<float*>(smem_raw + (ds_smem + C::kDsBytes - smem_u32(smem_raw)));
-  // vec layout: [buffer][lse2 | delta][128]
+  // vec layout: [warp][lse2 | delta][128]: each elementwise warp stages its own copy, so the
+  // four warps never wait for one another
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
@@ -737,15 +739,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int h = hk * G + it / n_i;
       const int q0 = (ib + it % n_i) * kTile;
       const uint32_t par = it & 1;
-      float* lse2 = vec + (it & 1) * 2 * kTile;
+      float* lse2 = vec + wq * 2 * kTile;
       float* dlt = lse2 + kTile;
-      {
-        const int q = q0 + r;
+      __syncwarp();                 // every lane is done with the previous tile's values
+#pragma unroll
+      for (int x = lane; x < kTile; x += 32) {
+        const int q = q0 + x;
         const bool live = q < p.total;
-        lse2[r] = live ? lse[static_cast<size_t>(h) * p.total + q] * kLog2e : INFINITY;
-        dlt[r] = live ? delta[static_cast<size_t>(h) * p.total + q] : 0.f;
+        lse2[x] = live ? lse[static_cast<size_t>(h) * p.total + q] * kLog2e : INFINITY;
+        dlt[x] = live ? delta[static_cast<size_t>(h) * p.total + q] : 0.f;
       }
-      named_barrier_sync(1, 128);
+      __syncwarp();
       const bool mask_tile = __any_sync(0xffffffffu, q0 < qlo || q0 + kTile - 1 > qhi);
       // ---- P^T
       ok = mbar_wait(smem_u32(&bar_s_full), par, &abort_flag, p.status, kTimeoutTmemFull);
@@ -864,7 +868,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       ok = mbar_wait(smem_u32(&bar_dkv_full), 0, &abort_flag, p.status, kTimeoutTmemFull);
       ok = __all_sync(0xffffffffu, ok);
     }
-    if (ok && kpos < p.total) {
+    if (ok) {
+      // (all 32 lanes stay together here: tcgen05.ld is a warp-wide instruction; only the stores
+      // below depend on whether this lane's key row exists)
+      const bool live = kpos < p.total;
       if (n_it > 0) tc_fence_after();
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
@@ -881,14 +888,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = 0u;       // no query sees these keys
           }
+          if (live) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 o;
-            o.x = pack_bf16x2(__uint_as_float(v[8 * g]), __uint_as_float(v[8 * g + 1]));
-            o.y = pack_bf16x2(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3]));
-            o.z = pack_bf16x2(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5]));
-            o.w = pack_bf16x2(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7]));
-            *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = o;
+            for (int g = 0; g < 4; ++g) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(v[8 * g]), __uint_as_float(v[8 * g + 1]));
+              o.y = pack_bf16x2(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3]));
+              o.z = pack_bf16x2(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5]));
+              o.w = pack_bf16x2(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7]));
+              *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = o;
+            }
           }
         }
       }
