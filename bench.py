@@ -164,7 +164,7 @@ def run_ours(args):
                        "global_batch": seqs * world, "seq_len": S,
                        "parallelism": f"fsdp{world}", "optimizer": "AdamW fp32 master, clip 1.0",
                        "l2": "inputs larger than L2 (activations of 32768 tokens/GPU)",
-                       "attention": "torch SDPA core inside packed-QKV op",
+                       "attention": "own tcgen05 kernels (forward + backward) inside the packed-QKV op",
                        "fsdp_all_gather": gather_mode},
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": e2e_ms / K,
                     "h2d_bytes_per_step": seqs * (S + 1) * 8, "d2h_bytes_per_step": 4},

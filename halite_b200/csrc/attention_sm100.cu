@@ -1,13 +1,13 @@
 // Training attention for sm_100a: softmax(mask(scale * Q K^T)) V and its gradients on tcgen05
 // tensor cores with the score / probability tiles held in tensor memory.
 //
-// Forward (`attn_fwd_kernel`): one CTA per 256 query rows of one head, 384 threads:
+// Forward (`attn_fwd_kernel`): one CTA per 256 query rows of one head, 320 threads:
 //   warp 0 (one lane)   TMA producer: the two 128-row Q tiles once, then K_j, V_j tiles through
 //                       a shared-memory ring (cp.async.bulk.tensor, 128B swizzle, no multicast)
 //   warp 1 (one lane)   MMA issuer: S_t = Q_t K_j^T into TMEM, O_t += P_t V_j with P_t read from
 //                       TMEM (it overwrites the first half of S_t's columns as bf16)
-//   warp 2              TMEM allocation (all 512 columns: S_0 S_1 O_0 O_1)
-//   warps 4-7 / 8-11    softmax of tile 0 / tile 1: one thread per query row, online softmax
+//   warp 0 (all lanes)  TMEM allocation (all 512 columns: S_0 S_1 O_0 O_1)
+//   warps 2-5 / 6-9     softmax of tile 0 / tile 1: one thread per query row, online softmax
 //                       with deferred rescaling (O_t is only rescaled when a row's maximum grew
 //                       by more than 2^8), P_t written back to TMEM with tcgen05.st
 // While one tile's rows are in the softmax, the tensor cores work on the other tile.
@@ -15,10 +15,11 @@
 // Backward (`attn_bwd_kernel`): one CTA per 128 key/value rows of one KV head; it walks the query
 // tiles (of every query head of the group) that can see those rows and keeps dK, dV in TMEM:
 //   S^T = K Q^T, dP^T = V dO^T         (TMEM; one thread per key row reads them)
-//   P^T = exp2(S^T c - lse)            -> TMEM (bf16, over S^T), A operand of dV += P^T dO
+//   P^T = exp2(S^T c - lse)            -> TMEM (bf16, inside S^T's columns), A operand of dV += P^T dO
 //   dS^T = P^T (dP^T - delta) scale    -> shared memory, read K-major by dK += dS^T Q and
 //                                         MN-major by dQ = dS K
-//   dQ tile                            -> TMEM (over dP^T) -> fp32 atomic adds into dq_accum
+//   dQ tile                            -> TMEM (over dP^T) -> shared memory -> bulk tensor reductions
+//                                         (fp32 add, whole 128-byte lines) into dq_accum
 //
 // Masks (causal, sliding window, segment bounds for packed sequences / documents, soft-capping)
 // are evaluated from per-token bounds on the device; nothing depends on host-side lengths.
@@ -94,6 +95,11 @@ __device__ __forceinline__ float tanh_fast(float x) {
   return y;
 }
 
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 // Segment of token t: [s0, s1).
 __device__ __forceinline__ void segment_of(const AttnParams& p, int t, int& s0, int& s1) {
   if (p.seg_start) {
@@ -139,13 +145,13 @@ struct FwdCfg {
   static constexpr int kTileBytes = kChunks * kChunkBytes;
   static constexpr int kStages = (D == 128) ? 4 : 6;
   static constexpr int kSmemBytes = (2 + kStages) * kTileBytes + 1024;
-  static constexpr int kThreads = 384;
+  static constexpr int kThreads = 320;
   static constexpr int kTmemCols = 512;
   static constexpr int kOCol = 256;                       // O_t at kOCol + t * D
 };
 
 template <int D, bool kSoftcap>
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(320, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, __nv_bfloat16* __restrict__ out,
                 float* __restrict__ lse, const __grid_constant__ AttnParams p) {
@@ -227,7 +233,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
   }
-  if (warp == 2) {
+  if (warp == 0) {
     tmem_alloc(smem_u32(&tmem_slot), C::kTmemCols);
     tmem_relinquish();
   }
@@ -333,9 +339,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (ok) umma_commit(smem_u32(&bar_kv_empty[e_kn % kStages]));
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp >= 2) {
     // ------------------------------------------------------------ softmax + epilogue
-    const int t = (warp - 4) >> 2;
+    // warps 2-5 own query tile 0, warps 6-9 tile 1; a warp reads the TMEM lane quarter warp % 4
+    const int t = (warp - 2) >> 2;
     const int wq = warp & 3;
     if (je[t] > jb[t]) {
       const int row = qb * 256 + t * kTile + wq * 32 + lane;
@@ -356,31 +363,37 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tc_fence_after();
         const int kv0 = j * kTile;
         const bool mask_tile = __any_sync(0xffffffffu, kv0 < lo || kv0 + kTile - 1 > hi);
-        // ---- pass 1: row maximum of this tile (soft-capped scores are written back)
-        float mt = -INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < kTile / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(s_addr + c * 32, v);
-          tmem_ld_wait();
-          if (kSoftcap) {
+        // ---- the whole score row into registers
+        uint32_t v[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld_32x32(s_addr + c * 32, v[c]);
+        tmem_ld_wait();
+        if (kSoftcap) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
 #pragma unroll
             for (int i = 0; i < 32; ++i)
-              v[i] = __float_as_uint(p.softcap * tanh_fast(__uint_as_float(v[i]) * cap_in));
-            tmem_st_32x32(s_addr + c * 32, v);
-          }
-          if (mask_tile) {
+              v[c][i] = __float_as_uint(p.softcap * tanh_fast(__uint_as_float(v[c][i]) * cap_in));
+        }
+        if (mask_tile) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const int kv = kv0 + c * 32 + i;
-              if (kv >= lo && kv <= hi) mt = fmaxf(mt, __uint_as_float(v[i]));
+              if (kv < lo || kv > hi) v[c][i] = __float_as_uint(-INFINITY);
             }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) mt = fmaxf(mt, __uint_as_float(v[i]));
-          }
         }
-        if (kSoftcap) tmem_st_wait();
+        // ---- row maximum (eight independent chains)
+        float mx[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) mx[u] = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx[i & 7] = fmaxf(mx[i & 7], __uint_as_float(v[c][i]));
+        const float mt = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
+                               fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
         // ---- deferred rescaling of the running output
         const float m_new = fmaxf(m_used, mt);
         float m_next = m_used;
@@ -391,43 +404,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           l *= alpha;
 #pragma unroll 1
           for (int c = 0; c < D / 32; ++c) {
-            uint32_t v[32];
-            tmem_ld_32x32(o_addr + c * 32, v);
+            uint32_t o[32];
+            tmem_ld_32x32(o_addr + c * 32, o);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-            tmem_st_32x32(o_addr + c * 32, v);
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32(o_addr + c * 32, o);
           }
           tmem_st_wait();
         }
         m_used = m_next;
         const float mc = (m_used == -INFINITY) ? 0.f : m_used * c2;
-        // ---- pass 2: P = exp2(S c2 - m c2) as bf16 pairs over the first half of S's columns
-#pragma unroll 1
-        for (int c = 0; c < kTile / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(s_addr + c * 32, v);
-          tmem_ld_wait();
-          float pr[32];
-          if (mask_tile) {
+        // ---- P = exp2(S c2 - m c2) as bf16 pairs over the first half of S's columns
+        float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int kv = kv0 + c * 32 + i;
-              const float e = exp2f(fmaf(__uint_as_float(v[i]), c2, -mc));
-              pr[i] = (kv >= lo && kv <= hi) ? e : 0.f;
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) pr[i] = exp2f(fmaf(__uint_as_float(v[i]), c2, -mc));
-          }
+        for (int c = 0; c < 4; ++c) {
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            l += pr[2 * i] + pr[2 * i + 1];
-            pk[i] = pack_bf16x2(pr[2 * i], pr[2 * i + 1]);
+            const float e0 = ex2_fast(fmaf(__uint_as_float(v[c][2 * i]), c2, -mc));
+            const float e1 = ex2_fast(fmaf(__uint_as_float(v[c][2 * i + 1]), c2, -mc));
+            ls[i & 3] += e0 + e1;
+            pk[i] = pack_bf16x2(e0, e1);
           }
           tmem_st_32x16(s_addr + c * 16, pk);
         }
+        l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
@@ -472,7 +474,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 2) {
+  if (warp == 0) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::kTmemCols);
   }
@@ -486,10 +488,12 @@ struct BwdCfg {
   static constexpr int kTileBytes = kChunks * kChunkBytes;
   static constexpr int kRing = 3;                               // Q_i, dO_i, Q_{i+1}
   static constexpr int kDsBytes = 2 * kChunkBytes;              // dS^T: 128 key rows x 128 query columns
-  static constexpr int kVecBytes = 4 * 2 * kTile * 4;           // lse, delta of the current query tile, one copy per warp
+  static constexpr int kVecBytes = 8 * 2 * 64 * 4;              // lse, delta of a warp's 64 query columns, one copy per warp
   static constexpr int kSmemBytes = (2 + kRing) * kTileBytes + kDsBytes + kVecBytes + 1024;
-  static constexpr int kThreads = 256;
+  static constexpr int kThreads = 384;
   static constexpr int kTmemCols = 512;
+  static constexpr int kPCol = 32;                              // P^T (64 columns of bf16 pairs) inside S^T's columns:
+                                                                // each warpgroup overwrites only columns it has read itself
   static constexpr int kDpCol = 128;                            // dP^T, later the dQ tile
   static constexpr int kDkCol = 256;
   static constexpr int kDvCol = 256 + D;
@@ -539,11 +543,11 @@ __global__ void attn_dq_convert_kernel(const float4* __restrict__ src, uint2* __
 }
 
 template <int D, bool kSoftcap>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(384, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-                const float* __restrict__ lse, const float* __restrict__ delta,
-                float* __restrict__ dq_accum, __nv_bfloat16* __restrict__ dk, long dk_stride,
+                const __grid_constant__ CUtensorMap tm_dq, const float* __restrict__ lse,
+                const float* __restrict__ delta, __nv_bfloat16* __restrict__ dk, long dk_stride,
                 __nv_bfloat16* __restrict__ dv, long dv_stride, const __grid_constant__ AttnParams p) {
   using C = BwdCfg<D>;
   extern __shared__ uint8_t smem_raw[];
@@ -565,8 +569,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t ring = smem_base + 2 * C::kTileBytes;
   const uint32_t ds_smem = ring + C::kRing * C::kTileBytes;
   float* vec = reinterpret_cast<float*>(smem_raw + (ds_smem + C::kDsBytes - smem_u32(smem_raw)));
-  // vec layout: [warp][lse2 | delta][128]: each elementwise warp stages its own copy, so the
-  // four warps never wait for one another
+  // vec layout: [warp][lse2 | delta][64]: each elementwise warp stages its own copy, so the
+  // eight warps never wait for one another
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
@@ -607,16 +611,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     mbar_init(smem_u32(&bar_s_full), 1);
     mbar_init(smem_u32(&bar_dp_full), 1);
-    mbar_init(smem_u32(&bar_p_ready), 4);
-    mbar_init(smem_u32(&bar_ds_ready), 4);
+    mbar_init(smem_u32(&bar_p_ready), 8);
+    mbar_init(smem_u32(&bar_ds_ready), 8);
     mbar_init(smem_u32(&bar_dq_full), 1);
-    mbar_init(smem_u32(&bar_dq_free), 4);
+    mbar_init(smem_u32(&bar_dq_free), 8);
     mbar_init(smem_u32(&bar_dkv_full), 1);
     fence_barrier_init();
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
     tma_prefetch_desc(&tm_do);
+    tma_prefetch_desc(&tm_dq);
   }
   if (warp == 2) {
     tmem_alloc(smem_u32(&tmem_slot), C::kTmemCols);
@@ -659,20 +664,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
   } else if (warp == 1 && lane == 0) {
     // ------------------------------------------------------------ MMA issuer
+    // Order per query tile: dP(it), dV(it), S(it + 1), dK(it), dQ(it). S of the next tile is issued
+    // as soon as dV has consumed P, so the elementwise warps can turn it into P(it + 1) while the
+    // tensor cores run dK(it) and dQ(it).
     constexpr uint32_t idesc_kk = make_idesc_bf16(kTile, kTile, false, false);   // S^T, dP^T
     constexpr uint32_t idesc_acc = make_idesc_bf16(kTile, D, false, true);       // dV, dK
     constexpr uint32_t idesc_dq = make_idesc_bf16(kTile, D, true, true);         // dQ
     bool ok = mbar_wait(smem_u32(&bar_kv_full), 0, &abort_flag, p.status, kTimeoutFull);
-    for (int it = 0; it < n_it && ok; ++it) {
-      const int e_q = 2 * it, e_o = 2 * it + 1;
-      const uint32_t q_addr = ring + (e_q % C::kRing) * C::kTileBytes;
-      const uint32_t o_addr = ring + (e_o % C::kRing) * C::kTileBytes;
-      const uint32_t par = it & 1;
-      // S^T = K Q^T
-      ok = mbar_wait(smem_u32(&bar_ring_full[e_q % C::kRing]), (e_q / C::kRing) & 1, &abort_flag, p.status,
-                     kTimeoutFull);
-      if (!ok) break;
+    auto issue_s = [&](int it) -> bool {
+      const int e_q = 2 * it;
+      if (!mbar_wait(smem_u32(&bar_ring_full[e_q % C::kRing]), (e_q / C::kRing) & 1, &abort_flag, p.status,
+                     kTimeoutFull))
+        return false;
       tc_fence_after();
+      const uint32_t q_addr = ring + (e_q % C::kRing) * C::kTileBytes;
 #pragma unroll
       for (int ks = 0; ks < D / 16; ++ks) {
         const uint32_t off = (ks >> 2) * C::kChunkBytes + (ks & 3) * 32;
@@ -680,6 +685,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                   idesc_kk, ks != 0);
       }
       umma_commit(smem_u32(&bar_s_full));
+      return true;
+    };
+    if (ok && n_it > 0) ok = issue_s(0);
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int e_q = 2 * it, e_o = 2 * it + 1;
+      const uint32_t q_addr = ring + (e_q % C::kRing) * C::kTileBytes;
+      const uint32_t o_addr = ring + (e_o % C::kRing) * C::kTileBytes;
+      const uint32_t par = it & 1;
       // dP^T = V dO^T (its columns held the previous dQ tile until the drain finished)
       ok = mbar_wait(smem_u32(&bar_ring_full[e_o % C::kRing]), (e_o / C::kRing) & 1, &abort_flag, p.status,
                      kTimeoutFull);
@@ -700,9 +713,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tc_fence_after();
 #pragma unroll
       for (int ks = 0; ks < kTile / 16; ++ks)
-        umma_bf16_ta(tmem_base + C::kDvCol, tmem_base + ks * 8,
+        umma_bf16_ta(tmem_base + C::kDvCol, tmem_base + C::kPCol + ks * 8,
                      make_smem_desc(o_addr + ks * 2048, C::kChunkBytes, 1024), idesc_acc, it > 0 || ks != 0);
       umma_commit(smem_u32(&bar_ring_empty[e_o % C::kRing]));
+      // S^T of the next tile, over the P that dV has just been issued on (the tensor cores run
+      // one CTA's instructions in issue order)
+      if (it + 1 < n_it) {
+        ok = issue_s(it + 1);
+        if (!ok) break;
+      }
       // dK += dS^T Q, dQ = dS K
       ok = mbar_wait(smem_u32(&bar_ds_ready), par, &abort_flag, p.status, kTimeoutTmemEmpty);
       if (!ok) break;
@@ -723,57 +742,103 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (ok) umma_commit(smem_u32(&bar_dkv_full));
   } else if (warp >= 4) {
     // ------------------------------------------------------------ elementwise + drains
+    // Two warpgroups share every 128 x 128 tile: warps 4-7 take query columns 0-63 of each key
+    // row, warps 8-11 columns 64-127 (a warp reads the TMEM lane quarter warp % 4). Per query
+    // tile: P (step 1), dS (step 2), drain of the dQ tile (step 3). Step 1 of the next tile runs
+    // before step 3 of this one, under the dK / dQ products. With soft-capping the plain order is
+    // kept, because step 1 then parks a factor in the dS buffer.
+    const int wg = (warp - 4) >> 2;            // which half of the columns
     const int wq = warp & 3;
-    const int r = wq * 32 + lane;              // key row in the first two phases, query row in the drain
+    const int r = wq * 32 + lane;              // key row in steps 1 and 2, query row in the drain
     const int kpos = k0 + r;
     int qlo, qhi;
     key_bounds(p, kpos, qlo, qhi);
     const uint32_t lane_addr = static_cast<uint32_t>(wq * 32) << 16;
-    const uint32_t s_addr = tmem_base + lane_addr;
-    const uint32_t dp_addr = tmem_base + C::kDpCol + lane_addr;
+    const uint32_t s_addr = tmem_base + lane_addr + wg * 64;                 // this half of S^T
+    const uint32_t p_addr = tmem_base + lane_addr + C::kPCol + wg * 32;      // this half of P^T (bf16 pairs)
+    const uint32_t dp_addr = tmem_base + C::kDpCol + lane_addr + wg * 64;    // this half of dP^T
+    const uint32_t dq_addr = tmem_base + C::kDpCol + lane_addr + wg * (D / 2);   // this half of the dQ tile
     const float c2 = kSoftcap ? kLog2e : p.scale * kLog2e;
     const float cap_in = kSoftcap ? p.scale / p.softcap : 0.f;
-    const uint32_t ds_row = ds_smem + r * 128;
+    // this thread's 64 columns of dS^T are one 128-byte row of the buffer's half `wg`; the warp's
+    // 32 such rows double as its staging piece for the dQ drain
+    const uint32_t ds_row = ds_smem + wg * C::kChunkBytes + r * 128;
+    const uint32_t piece = ds_smem + wg * C::kChunkBytes + wq * 4096;
+    float* lse2 = vec + (warp - 4) * 2 * 64;
+    float* dlt = lse2 + 64;
+    uint32_t pk[32];
     bool ok = true;
-    for (int it = 0; it < n_it; ++it) {
+    bool reduce_in_flight = false;
+    float pre[4];
+
+    // lse / delta of this warp's 64 query columns: fetched early into registers, parked in shared
+    // memory right before use
+    auto fetch_vectors = [&](int it) {
       const int h = hk * G + it / n_i;
-      const int q0 = (ib + it % n_i) * kTile;
-      const uint32_t par = it & 1;
-      float* lse2 = vec + wq * 2 * kTile;
-      float* dlt = lse2 + kTile;
+      const int q0 = (ib + it % n_i) * kTile + wg * 64;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int q = q0 + lane + 32 * u;
+        const bool live = q < p.total;
+        pre[u] = live ? lse[static_cast<size_t>(h) * p.total + q] * kLog2e : INFINITY;
+        pre[2 + u] = live ? delta[static_cast<size_t>(h) * p.total + q] : 0.f;
+      }
+    };
+    auto park_vectors = [&]() {
       __syncwarp();                 // every lane is done with the previous tile's values
 #pragma unroll
-      for (int x = lane; x < kTile; x += 32) {
-        const int q = q0 + x;
-        const bool live = q < p.total;
-        lse2[x] = live ? lse[static_cast<size_t>(h) * p.total + q] * kLog2e : INFINITY;
-        dlt[x] = live ? delta[static_cast<size_t>(h) * p.total + q] : 0.f;
+      for (int u = 0; u < 2; ++u) {
+        lse2[lane + 32 * u] = pre[u];
+        dlt[lane + 32 * u] = pre[2 + u];
       }
       __syncwarp();
-      const bool mask_tile = __any_sync(0xffffffffu, q0 < qlo || q0 + kTile - 1 > qhi);
-      // ---- P^T
-      ok = mbar_wait(smem_u32(&bar_s_full), par, &abort_flag, p.status, kTimeoutTmemFull);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+    };
+    // the staging piece / dS rows may only be rewritten once the reductions that read them are done
+    auto wait_reduce_reads = [&]() {
+      if (reduce_in_flight) {
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        __syncwarp();
+        reduce_in_flight = false;
+      }
+    };
+    // ---- step 1: P^T = exp2(S^T c2 - lse) as bf16 pairs, into TMEM and into `pk`
+    auto step1 = [&](int it) -> bool {
+      const int q0 = (ib + it % n_i) * kTile + wg * 64;
+      const bool mask_tile = __any_sync(0xffffffffu, q0 < qlo || q0 + 63 > qhi);
+      bool good = mbar_wait(smem_u32(&bar_s_full), it & 1, &abort_flag, p.status, kTimeoutTmemFull);
+      good = __all_sync(0xffffffffu, good);
+      if (!good) return false;
       tc_fence_after();
-      uint32_t pk[kTile / 2];
+      if (kSoftcap) wait_reduce_reads();
+      uint32_t v[2][32];
+      tmem_ld_32x32(s_addr, v[0]);
+      tmem_ld_32x32(s_addr + 32, v[1]);
+      tmem_ld_wait();
 #pragma unroll
-      for (int c = 0; c < kTile / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(s_addr + c * 32, v);
-        tmem_ld_wait();
+      for (int c = 0; c < 2; ++c) {
         float pr[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(v[i]);
-          if (kSoftcap) {
-            const float th = tanh_fast(s * cap_in);
-            s = p.softcap * th;
-            v[i] = __float_as_uint(1.f - th * th);
+        for (int i4 = 0; i4 < 8; ++i4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(lse2 + c * 32 + i4 * 4);
+          const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int i = i4 * 4 + u;
+            float s = __uint_as_float(v[c][i]);
+            if (kSoftcap) {
+              const float th = tanh_fast(s * cap_in);
+              s = p.softcap * th;
+              v[c][i] = __float_as_uint(1.f - th * th);
+            }
+            pr[i] = ex2_fast(fmaf(s, c2, -ls[u]));
           }
-          const int q = q0 + c * 32 + i;
-          const float e = exp2f(fmaf(s, c2, -lse2[c * 32 + i]));
-          pr[i] = (!mask_tile || (q >= qlo && q <= qhi)) ? e : 0.f;
+        }
+        if (mask_tile) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int q = q0 + c * 32 + i;
+            if (q < qlo || q > qhi) pr[i] = 0.f;
+          }
         }
 #pragma unroll
         for (int i = 0; i < 16; ++i) pk[c * 16 + i] = pack_bf16x2(pr[2 * i], pr[2 * i + 1]);
@@ -781,44 +846,51 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           // park d(capped score)/d(score) in this row's slot of the dS buffer until dP arrives
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            const uint32_t u = static_cast<uint32_t>((c & 1) * 4 + g);
-            st_shared_v4(ds_row + (c >> 1) * C::kChunkBytes + ((u ^ (r & 7)) << 4),
-                         pack_bf16x2(__uint_as_float(v[8 * g]), __uint_as_float(v[8 * g + 1])),
-                         pack_bf16x2(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3])),
-                         pack_bf16x2(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5])),
-                         pack_bf16x2(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7])));
+            const uint32_t u = static_cast<uint32_t>(c * 4 + g);
+            st_shared_v4(ds_row + ((u ^ (r & 7)) << 4),
+                         pack_bf16x2(__uint_as_float(v[c][8 * g]), __uint_as_float(v[c][8 * g + 1])),
+                         pack_bf16x2(__uint_as_float(v[c][8 * g + 2]), __uint_as_float(v[c][8 * g + 3])),
+                         pack_bf16x2(__uint_as_float(v[c][8 * g + 4]), __uint_as_float(v[c][8 * g + 5])),
+                         pack_bf16x2(__uint_as_float(v[c][8 * g + 6]), __uint_as_float(v[c][8 * g + 7])));
           }
         }
-        uint32_t pc[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) pc[i] = pk[c * 16 + i];
-        tmem_st_32x16(s_addr + c * 16, pc);
       }
+      // both of this thread's S chunks are in registers: P may now overwrite S's columns
+      tmem_st_32x32(p_addr, pk);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_p_ready));
-      // ---- dS^T
-      ok = mbar_wait(smem_u32(&bar_dp_full), par, &abort_flag, p.status, kTimeoutTmemFull);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      return true;
+    };
+    // ---- step 2: dS^T = P^T (dP^T - delta) scale, bf16, into shared memory
+    auto step2 = [&](int it) -> bool {
+      bool good = mbar_wait(smem_u32(&bar_dp_full), it & 1, &abort_flag, p.status, kTimeoutTmemFull);
+      good = __all_sync(0xffffffffu, good);
+      if (!good) return false;
       tc_fence_after();
+      uint32_t v[2][32];
+      tmem_ld_32x32(dp_addr, v[0]);
+      tmem_ld_32x32(dp_addr + 32, v[1]);
+      wait_reduce_reads();
+      tmem_ld_wait();
 #pragma unroll
-      for (int c = 0; c < kTile / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(dp_addr + c * 32, v);
-        tmem_ld_wait();
+      for (int c = 0; c < 2; ++c) {
         float ds[32];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float2 pp = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk[c * 16 + i]));
-          ds[2 * i] = pp.x * (__uint_as_float(v[2 * i]) - dlt[c * 32 + 2 * i]) * p.scale;
-          ds[2 * i + 1] = pp.y * (__uint_as_float(v[2 * i + 1]) - dlt[c * 32 + 2 * i + 1]) * p.scale;
+        for (int i4 = 0; i4 < 8; ++i4) {
+          const float4 d4 = *reinterpret_cast<const float4*>(dlt + c * 32 + i4 * 4);
+          const float2 p0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk[c * 16 + i4 * 2]));
+          const float2 p1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk[c * 16 + i4 * 2 + 1]));
+          ds[i4 * 4] = p0.x * p.scale * (__uint_as_float(v[c][i4 * 4]) - d4.x);
+          ds[i4 * 4 + 1] = p0.y * p.scale * (__uint_as_float(v[c][i4 * 4 + 1]) - d4.y);
+          ds[i4 * 4 + 2] = p1.x * p.scale * (__uint_as_float(v[c][i4 * 4 + 2]) - d4.z);
+          ds[i4 * 4 + 3] = p1.y * p.scale * (__uint_as_float(v[c][i4 * 4 + 3]) - d4.w);
         }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          const uint32_t u = static_cast<uint32_t>((c & 1) * 4 + g);
-          const uint32_t addr = ds_row + (c >> 1) * C::kChunkBytes + ((u ^ (r & 7)) << 4);
+          const uint32_t u = static_cast<uint32_t>(c * 4 + g);
+          const uint32_t addr = ds_row + ((u ^ (r & 7)) << 4);
           if (kSoftcap) {
             const uint4 gq = ld_shared_v4(addr);
             const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gq);
@@ -837,33 +909,76 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       fence_proxy_async_smem();      // the tensor cores read dS^T through the async proxy
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_ds_ready));
-      // ---- dQ tile: this thread now owns query row q0 + r
-      ok = mbar_wait(smem_u32(&bar_dq_full), par, &abort_flag, p.status, kTimeoutTmemFull);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      return true;
+    };
+    // ---- step 3: this warp's part of the dQ tile (32 query rows x D / 2 columns) leaves through
+    // its staging piece, 32 columns at a time, as bulk tensor reductions (fp32 add) into dq_accum
+    auto step3 = [&](int it) -> bool {
+      const int h = hk * G + it / n_i;
+      const int q0 = (ib + it % n_i) * kTile;
+      bool good = mbar_wait(smem_u32(&bar_dq_full), it & 1, &abort_flag, p.status, kTimeoutTmemFull);
+      good = __all_sync(0xffffffffu, good);
+      if (!good) return false;
       tc_fence_after();
-      {
-        const int q = q0 + r;
-        float* dst = dq_accum + (static_cast<size_t>(q) * p.n_heads + h) * D;
-#pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(dp_addr + c * 32, v);
-          tmem_ld_wait();
-          if (q < p.total) {
+      uint32_t v[D / 64][32];
 #pragma unroll
-            for (int g = 0; g < 8; ++g)
-              atomicAdd(reinterpret_cast<float4*>(dst + c * 32 + g * 4),
-                        make_float4(__uint_as_float(v[4 * g]), __uint_as_float(v[4 * g + 1]),
-                                    __uint_as_float(v[4 * g + 2]), __uint_as_float(v[4 * g + 3])));
-          }
-        }
-      }
+      for (int c = 0; c < D / 64; ++c) tmem_ld_32x32(dq_addr + c * 32, v[c]);
+      tmem_ld_wait();
+      // the tile is in registers: its TMEM columns can take the next dP^T already
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_dq_free));
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        if (c > 0) {
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          __syncwarp();
+        }
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+          st_shared_v4(piece + lane * 128 + ((static_cast<uint32_t>(g) ^ (lane & 7)) << 4), v[c][4 * g],
+                       v[c][4 * g + 1], v[c][4 * g + 2], v[c][4 * g + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          asm volatile(
+              "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                  reinterpret_cast<uint64_t>(&tm_dq)),
+              "r"(piece), "r"(wg * (D / 2) + c * 32), "r"(h), "r"(q0 + wq * 32)
+              : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+      }
+      reduce_in_flight = true;
+      return true;
+    };
+
+    if (n_it > 0) {
+      fetch_vectors(0);
+      park_vectors();
+      ok = step1(0);
     }
-    // ---- dK, dV of this key tile
+    for (int it = 0; it < n_it && ok; ++it) {
+      const bool more = it + 1 < n_it;
+      if (more) fetch_vectors(it + 1);
+      ok = step2(it);
+      if (!ok) break;
+      if (!kSoftcap && more) {
+        park_vectors();
+        ok = step1(it + 1);
+        if (!ok) break;
+      }
+      ok = step3(it);
+      if (!ok) break;
+      if (kSoftcap && more) {
+        park_vectors();
+        ok = step1(it + 1);
+      }
+    }
+    // every reduction this lane issued has to land before the CTA's shared memory goes away
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    __syncwarp();
+    // ---- dK, dV of this key tile: the first warpgroup writes dK, the second dV
     if (ok && n_it > 0) {
       ok = mbar_wait(smem_u32(&bar_dkv_full), 0, &abort_flag, p.status, kTimeoutTmemFull);
       ok = __all_sync(0xffffffffu, ok);
@@ -873,31 +988,28 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // below depend on whether this lane's key row exists)
       const bool live = kpos < p.total;
       if (n_it > 0) tc_fence_after();
+      const uint32_t addr = tmem_base + (wg == 0 ? C::kDkCol : C::kDvCol) + lane_addr;
+      __nv_bfloat16* dst = wg == 0 ? dk + static_cast<size_t>(kpos) * dk_stride + hk * D
+                                   : dv + static_cast<size_t>(kpos) * dv_stride + hk * D;
 #pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
-        const uint32_t addr = tmem_base + (which == 0 ? C::kDkCol : C::kDvCol) + lane_addr;
-        __nv_bfloat16* dst = which == 0 ? dk + static_cast<size_t>(kpos) * dk_stride + hk * D
-                                        : dv + static_cast<size_t>(kpos) * dv_stride + hk * D;
-#pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t v[32];
-          if (n_it > 0) {
-            tmem_ld_32x32(addr + c * 32, v);
-            tmem_ld_wait();
-          } else {
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        if (n_it > 0) {
+          tmem_ld_32x32(addr + c * 32, v);
+          tmem_ld_wait();
+        } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = 0u;       // no query sees these keys
-          }
-          if (live) {
+          for (int i = 0; i < 32; ++i) v[i] = 0u;       // no query sees these keys
+        }
+        if (live) {
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              uint4 o;
-              o.x = pack_bf16x2(__uint_as_float(v[8 * g]), __uint_as_float(v[8 * g + 1]));
-              o.y = pack_bf16x2(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3]));
-              o.z = pack_bf16x2(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5]));
-              o.w = pack_bf16x2(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7]));
-              *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = o;
-            }
+          for (int g = 0; g < 4; ++g) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(v[8 * g]), __uint_as_float(v[8 * g + 1]));
+            o.y = pack_bf16x2(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3]));
+            o.z = pack_bf16x2(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5]));
+            o.w = pack_bf16x2(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7]));
+            *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = o;
           }
         }
       }
@@ -961,6 +1073,25 @@ bool make_tmap_heads(CUtensorMap* map, const void* base, int tokens, int heads, 
   return r == CUDA_SUCCESS;
 }
 
+// fp32 [tokens, heads, head_dim] contiguous; box = 32 tokens of one head, 32 columns (128 bytes),
+// 128-byte swizzle: the destination of the dQ reductions.
+bool make_tmap_dq(CUtensorMap* map, void* base, int tokens, int heads, int head_dim) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(heads),
+                        static_cast<cuuint64_t>(tokens)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(head_dim) * 4, static_cast<cuuint64_t>(heads) * head_dim * 4};
+  cuuint32_t box[3] = {32, 1, 32};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    fprintf(stderr, "halite_b200: dq tensor map failed (%d): tokens=%d heads=%d dim=%d base=%p\n",
+            static_cast<int>(r), tokens, heads, head_dim, base);
+  return r == CUDA_SUCCESS;
+}
+
 cudaError_t check_args(const AttnArgs& a) {
   if (a.total <= 0) return cudaSuccess;
   if ((a.head_dim != 64 && a.head_dim != 128) || a.n_heads <= 0 || a.n_kv_heads <= 0 ||
@@ -1015,12 +1146,14 @@ template <int D, bool SC>
 cudaError_t launch_bwd(const AttnArgs& a, const void* o, const void* d_o, const float* lse, float* delta,
                        float* dq_accum, void* dq, void* dk, long dk_stride, void* dv, long dv_stride) {
   using C = BwdCfg<D>;
-  CUtensorMap tq, tk, tv, tdo;
+  CUtensorMap tq, tk, tv, tdo, tdq;
   if (!make_tmap_heads(&tq, a.q, a.total, a.n_heads, D, a.q_tok_stride) ||
       !make_tmap_heads(&tk, a.k, a.total, a.n_kv_heads, D, a.k_tok_stride) ||
       !make_tmap_heads(&tv, a.v, a.total, a.n_kv_heads, D, a.v_tok_stride) ||
-      !make_tmap_heads(&tdo, d_o, a.total, a.n_heads, D, static_cast<long>(a.n_heads) * D))
+      !make_tmap_heads(&tdo, d_o, a.total, a.n_heads, D, static_cast<long>(a.n_heads) * D) ||
+      !make_tmap_dq(&tdq, dq_accum, a.total, a.n_heads, D))
     return cudaErrorInvalidValue;
+  if (reinterpret_cast<uintptr_t>(dq_accum) & 15) return cudaErrorInvalidValue;
   auto kern = attn_bwd_kernel<D, SC>;
   static bool configured = false;
   if (!configured) {
@@ -1042,7 +1175,7 @@ cudaError_t launch_bwd(const AttnArgs& a, const void* o, const void* d_o, const 
   }
   const int nkt = (a.total + kTile - 1) / kTile;
   kern<<<nkt * a.n_kv_heads, C::kThreads, C::kSmemBytes, a.stream>>>(
-      tq, tk, tv, tdo, lse, delta, dq_accum, static_cast<__nv_bfloat16*>(dk), dk_stride,
+      tq, tk, tv, tdo, tdq, lse, delta, static_cast<__nv_bfloat16*>(dk), dk_stride,
       static_cast<__nv_bfloat16*>(dv), dv_stride, to_params(a));
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
