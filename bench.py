@@ -35,6 +35,12 @@ def parse():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--metric", default="train", choices=["train", "rollout", "ppo"],
+                    help="train: Llama-3.2-3B step (the headline); rollout: paged-KV decode tokens/s, one engine "
+                         "replica per GPU; ppo: seconds per PPO iteration with four Llama-3.2-1B-style models")
+    ap.add_argument("--requests-per-gpu", type=int, default=128, help="rollout: 1024 requests per 8-GPU box")
+    ap.add_argument("--new-tokens", type=int, default=512)
+    ap.add_argument("--prompts-per-gpu", type=int, default=64, help="ppo: 512 prompts per 8-GPU box")
     ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
     ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (marks the run invalid)")
@@ -69,6 +75,117 @@ def make_batches(n, seqs, seq_len, rank, pinned=True):
         t = torch.randint(0, VOCAB, (seqs, seq_len + 1), generator=g, dtype=torch.int64)
         out.append(t.pin_memory() if pinned else t)
     return out
+
+
+def rollout_requests(args, rank, tag, warmup=False):
+    """[(id, token ids, sampling params)] of one rank's share of a rollout batch: prompt lengths
+    uniform in [128, 1024], uniform-random token ids, a quarter of the requests starting with one
+    common 512-token prefix (the same on every rank), `--new-tokens` sampled tokens each at
+    temperature 1.0 with EOS ignored. Warm-up batches are small (8 requests, 16 tokens)."""
+    import random
+
+    shared = random.Random(99).choices(range(VOCAB), k=512)
+    rng = random.Random(hash((rank, tag)) & 0xffffffff)
+    n_req = 8 if warmup else args.requests_per_gpu
+    n_new = 16 if warmup else args.new_tokens
+    out = []
+    for i in range(n_req):
+        n = rng.randint(128, 1024)
+        ids = rng.choices(range(VOCAB), k=n)
+        if rng.random() < 0.25:
+            ids = shared + ids[: max(n - 512, 1)]
+        out.append((f"{tag}-{rank}-{i}", ids,
+                    {"max_new_tokens": n_new, "temperature": 1.0, "top_p": 1.0, "ignore_eos": True}))
+    return out
+
+
+def rollout_config(args, world):
+    return {"model": MODEL_NAME, "requests": args.requests_per_gpu * world, "new_tokens": args.new_tokens,
+            "prompt_len": "uniform [128, 1024], 25% share a 512-token prefix", "page_size": 16,
+            "parallelism": f"dp{world} (one engine replica per GPU)", "sampling": "temperature 1.0, top-p 1.0, EOS ignored",
+            "l2": "weights (6.4 GB) and KV pages are larger than L2"}
+
+
+def run_rollout_ours(args):
+    """Rollout decode throughput through the in-process paged-KV engine (`halite_b200.infer`)."""
+    import torch
+    import torch.distributed as dist
+
+    rank, world, local = init_dist(args.gpus)
+    dev = torch.device("cuda", local)
+
+    from halite_b200 import ops
+    from halite_b200.conf import instantiate, load_config
+    from halite_b200.infer import InferenceEngine, InferenceRequest, ModelConfig, ServerConfig
+    from halite_b200.utils.timing import ClockSampler, DeviceTimer
+
+    C = ops.ext()
+    conf = load_config(os.path.join(ROOT, "configs/models/llama/llama3_2_3b.py"))
+    mc = conf.model_conf
+    with torch.device("meta"):
+        infer = instantiate(conf.model_infer)
+        if callable(infer) and not isinstance(infer, torch.nn.Module):
+            infer = instantiate(infer(conf.model))
+    infer = infer.to(dtype=torch.bfloat16)
+    infer.to_empty(device=dev)
+    torch.manual_seed(0)
+    infer.init_weights(dev)
+    engine = InferenceEngine(
+        infer, None,
+        ModelConfig(n_heads=mc.n_heads, n_key_value_heads=mc.n_key_value_heads, head_dim=mc.head_dim,
+                    n_layers=mc.n_layers, context_len=min(mc.context_len, 4096), device="cuda",
+                    kv_cache_dtype=torch.bfloat16, vocab_size=mc.vocab_size, memory_fraction_static=0.8),
+        ServerConfig(decode_steps_ahead=8, use_cudagraph=True))
+
+    def to_requests(specs):
+        return [InferenceRequest(i, ids, params) for i, ids, params in specs]
+
+    W, K = args.warmup, args.steps
+    for w in range(W):
+        engine.infer_batch(to_requests(rollout_requests(args, rank, f"w{w}", warmup=True)))
+    batches = [rollout_requests(args, rank, f"t{k}") for k in range(K)]
+    e2e_batches = [rollout_requests(args, rank, f"e{k}") for k in range(K)]
+    torch.cuda.synchronize()
+    ops.check_status()
+    new = e2e_new = h2d = d2h = 0
+    C.reset_launch_count()
+    with ClockSampler(local) as clocks:
+        with DeviceTimer() as t:
+            for specs in batches:
+                for r in engine.infer_batch(to_requests(specs)):
+                    new += len(r.output_ids[0])
+        launches = C.launch_count()
+        ms = t.max_ms()
+        # end to end: prompts start in pinned host memory, results are read back as host lists
+        with DeviceTimer() as te:
+            for specs in e2e_batches:
+                pinned = [torch.tensor(ids, dtype=torch.int64).pin_memory() for _, ids, _ in specs]
+                reqs = [InferenceRequest(i, p.tolist(), params) for (i, _, params), p in zip(specs, pinned)]
+                h2d += sum(p.numel() * 8 for p in pinned)
+                for r in engine.infer_batch(reqs):
+                    e2e_new += len(r.output_ids[0])
+                    d2h += len(r.output_ids[0]) * 8
+        e2e_ms = te.max_ms()
+    ops.check_status()
+    totals = torch.tensor([new, e2e_new], dtype=torch.float64, device=dev)
+    if dist.is_initialized():
+        dist.all_reduce(totals)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "rollout decode tokens/s (Llama-3.2-3B, paged KV, one replica per GPU)",
+            "value": float(totals[0]) / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic uniform-random prompts, random-init weights", "impl": "ours",
+            "config": rollout_config(args, world),
+            "e2e": {"value": float(totals[1]) / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / K,
+                    "h2d_bytes_per_step": h2d // K, "d2h_bytes_per_step": d2h // K},
+            "gpu_launches": int(launches), "clocks": clocks.summary(),
+            "stack": "halite_b200.infer engine: paged prefill / decode kernels, tcgen05 GEMMs, CUDA-graph decode",
+            "peak_mem_gib": torch.cuda.max_memory_allocated() / 2 ** 30,
+        }), flush=True)
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def run_ours(args):
@@ -189,6 +306,19 @@ def run_ours(args):
 
 def main():
     args = parse()
+    if args.metric == "rollout":
+        if args.impl == "reference":
+            from baseline import reference_rollout
+
+            reference_rollout.run(args)
+        else:
+            run_rollout_ours(args)
+        return
+    if args.metric == "ppo":
+        from benchmarks import ppo_iteration
+
+        ppo_iteration.run(args)
+        return
     if args.impl == "reference":
         from baseline import reference_bench
 

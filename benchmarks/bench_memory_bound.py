@@ -54,7 +54,7 @@ def main(argv=None):
     C = ops.ext()
     flush = torch.zeros(192 << 20, dtype=torch.uint8, device=dev)
     peak = None
-    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     try:
         with open(os.path.join(root, "MEASURED_PEAKS.json")) as f:
             peak = float(json.load(f)["hbm_gbs"])

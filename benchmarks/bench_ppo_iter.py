@@ -101,6 +101,8 @@ def main(argv=None):
                     help="keep the engine's weights, KV pool and CUDA graphs on the device between rollouts "
                          "instead of freeing them for the training phases")
     ap.add_argument("--device", default=None)
+    ap.add_argument("--quiet", action="store_true", help="return the result without printing it")
+    ap.add_argument("--keep-group", action="store_true", help="leave the process group up for another call")
     args = ap.parse_args(argv)
 
     from halite_b200.conf import load_config
@@ -125,7 +127,7 @@ def main(argv=None):
         torch.cuda.set_device(device)
     pdims.build_mesh(dev_type)
 
-    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     conf = load_config(args.conf or os.path.join(root, "configs/models/llama/llama3_2_1b.py"))
     mc = conf.model_conf
     if args.layers:
@@ -273,11 +275,17 @@ def main(argv=None):
         pass
     if dev_type == "cuda":
         out["peak_mem_gib"] = round(torch.cuda.max_memory_allocated() / 2 ** 30, 2)
-    if rank == 0:
+    if dev_type == "cuda":
+        from halite_b200 import ops
+
+        out["gpu_launches"] = int(ops.ext().launch_count())
+        ops.check_status()
+    if rank == 0 and not args.quiet:
         print(json.dumps(out))
     if world > 1:
         dist.barrier()
-        dist.destroy_process_group()
+        if not args.keep_group:
+            dist.destroy_process_group()
     return out
 
 

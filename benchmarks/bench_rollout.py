@@ -39,7 +39,7 @@ def main(argv=None):
     from halite_b200.conf import instantiate, load_config
     from halite_b200.infer import InferenceRequest, ModelConfig
 
-    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     conf = load_config(args.conf or os.path.join(root, "configs/models/llama/llama3_2_3b.py"))
     mc = conf.model_conf
     model_conf = conf.model

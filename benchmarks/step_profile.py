@@ -32,7 +32,7 @@ def main(argv=None):
     from halite_b200.parallel import ParallelDims, parallelize
     from halite_b200.projects.common.train_fn import optimization_step
 
-    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     conf = load_config(args.conf or os.path.join(root, "configs/models/llama/llama3_2_3b_bench.py"))
     if args.layers:
         conf.model.blocks = conf.model.blocks[: args.layers]

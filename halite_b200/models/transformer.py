@@ -43,7 +43,7 @@ class TransformerDecoder(nn.Module, ModelMixin, GenerationMixin):
         self.adapters = None
         self.cache_manager = None
         self.config = config
-        self.block_hooks = None   # set by the FSDP layer: (pre_block(i, x), post_block(i, x))
+        self.block_hooks = None   # set by the FSDP layer: (pre_block(i, x) -> x, post_block(i, x, residual) -> (x, residual))
 
     # ------------------------------------------------------------------ state
     def state_dict(self, *args, **kwargs):
@@ -149,7 +149,7 @@ class TransformerDecoder(nn.Module, ModelMixin, GenerationMixin):
                 out = hooks[0](i, out)
             out, residual, _, _ = block(out, residual, None, None, pos_emb=pos_emb, use_cache=False)
             if hooks is not None:
-                out = hooks[1](i, out)
+                out, residual = hooks[1](i, out, residual)
         if hooks is not None:
             out = hooks[0](len(self.blocks), out)
         if self.post_blocks is not None:
@@ -228,7 +228,7 @@ class TransformerDecoder(nn.Module, ModelMixin, GenerationMixin):
                             x = hooks[0](start + j, x)
                         x, res, _, _ = m(x, res, mask, attention_bias, pos_emb, None, False, unpad_params)
                         if hooks is not None:
-                            x = hooks[1](start + j, x)
+                            x, res = hooks[1](start + j, x, res)
                     return x, res
 
                 out, residual = utils.checkpoint.checkpoint(run, out, residual, use_reentrant=False)
@@ -243,7 +243,7 @@ class TransformerDecoder(nn.Module, ModelMixin, GenerationMixin):
                     out, residual, mask, attention_bias, pos_emb=pos_emb, use_cache=use_cache,
                     cache=cache[index], unpad_params=unpad_params)
                 if hooks is not None:
-                    out = hooks[1](index, out)
+                    out, residual = hooks[1](index, out, residual)
                 if use_cache:
                     if hasattr(cache, "update"):      # a cache manager keeps its own per-layer state
                         cache.update(index, next_cache)

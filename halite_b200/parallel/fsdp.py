@@ -20,6 +20,13 @@ buys one collective per step instead of two. The AdamW kernels and the gathers a
 by unit in the order the next forward uses the units, so that forward waits for the embedding's
 gather only and every other gather hides under compute.
 
+`reshard_after_forward=True` selects the memory-lean (ZeRO-3) schedule instead: a rank keeps only
+its own bf16 shard of every unit (`local_shard`); a unit's `full_param` storage is allocated and
+gathered right before the unit's forward (the next unit's gather is started at the same time),
+released after it, gathered again before the unit's backward and released after it; the fp32
+`full_grad` storage exists from the unit's backward until its reduce-scatter has finished. The
+buffers are resized in place, so parameter and gradient views stay valid throughout.
+
 With dp_replicate > 1 (HSDP) gradient shards are additionally all-reduced across replicas;
 with dp_shard == 1 (DDP) a unit's "shard" is the whole buffer.
 """
@@ -50,6 +57,29 @@ class _UnitBoundary(torch.autograd.Function):
     def backward(ctx, g):
         ctx.unit.post_backward()
         return g, None
+
+
+class _UnitPreBackward(torch.autograd.Function):
+    """Identity placed on a unit's output: its backward runs before any gradient inside the unit
+    is computed (used to gather a resharded unit's parameters again)."""
+
+    @staticmethod
+    def forward(ctx, x, unit):
+        ctx.unit = unit
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        ctx.unit.pre_backward()
+        return g, None
+
+
+def _free_storage(t):
+    t.untyped_storage().resize_(0)
+
+
+def _alloc_storage(t, numel):
+    t.untyped_storage().resize_(numel * t.element_size())
 
 
 class FlatUnit:
@@ -98,6 +128,15 @@ class FlatUnit:
         self._backward_done = False
         self._needs_reduce = False
         self.defer_reduce = False  # set by `ShardedModel.no_sync()`: backward passes only accumulate
+        # memory-lean schedule (`enable_reshard`): the rank's own shard lives in `local_shard`, the
+        # full buffers are only allocated around the unit's forward / backward
+        self.reshard = False
+        self.local_shard = None
+        self.materialized = True      # `full_param` is allocated and current
+        self.grad_allocated = True
+        self.prev_unit = None         # neighbours in forward order (prefetch targets)
+        self.next_unit = None
+        self.state = None             # the owning ShardedModel
         self.fused = None         # FusedGather state once `enable_fused_gather` has run
         self.fused_reduce = None  # FusedReduce state once `enable_fused_reduce` has run
         self._adopt_params()
@@ -190,7 +229,75 @@ class FlatUnit:
             self._written.add(id(p))
         return acc
 
+    # ------------------------------------------------------------------ memory-lean schedule
+    def enable_reshard(self):
+        if self.ws > 1:
+            self.reshard = True
+
+    def materialize(self, prefetch=None):
+        """Allocate `full_param` and gather it from the ranks' `local_shard`s (on the communication
+        stream when there is one). `prefetch` names a neighbour whose gather is started as well."""
+        if self.reshard and not self.materialized:
+            # The gather rewrites the buffer with the values it held when autograd saved views of
+            # it in the forward pass, so the saved tensors stay valid: keep the version counter.
+            with torch.autograd._unsafe_preserve_version_counter(self.full_param):
+                if self.device.type == "cuda" and self.comm_stream is not None:
+                    _alloc_storage(self.full_param, self.padded)     # on the compute stream: it frees it later
+                    ev = torch.cuda.Event()
+                    ev.record()
+                    with torch.cuda.stream(self.comm_stream):
+                        self.comm_stream.wait_event(ev)
+                        comm.all_gather_flat(self.full_param, self.local_shard, self.shard_group)
+                        self._gather_event = torch.cuda.Event()
+                        self._gather_event.record()
+                else:
+                    _alloc_storage(self.full_param, self.padded)
+                    comm.all_gather_flat(self.full_param, self.local_shard, self.shard_group)
+            self.materialized = True
+        if prefetch is not None:
+            prefetch.materialize()
+
+    def release(self):
+        """Keep only this rank's shard of the parameters."""
+        if not self.reshard or not self.materialized:
+            return
+        self.wait_gather()
+        if self.local_shard is None:
+            self.local_shard = self.full_param[self.lo:self.hi].clone()
+        else:
+            # in-place edits made while the unit was whole (initialisation, a loaded checkpoint)
+            self.local_shard.copy_(self.full_param[self.lo:self.hi])
+        _free_storage(self.full_param)
+        self.materialized = False
+
+    def ensure_grad(self):
+        if not self.grad_allocated:
+            _alloc_storage(self.full_grad, self.padded)
+            self.full_grad.zero_()      # padding and alignment gaps take part in the reduction and the norm
+            self.grad_allocated = True
+
+    def release_grad(self):
+        """Free `full_grad` once its reduction has finished (the current stream waits for it)."""
+        if not self.reshard or not self.grad_allocated or self._needs_reduce:
+            return
+        if self._reduce_event is not None:
+            torch.cuda.current_stream().wait_event(self._reduce_event)
+        _free_storage(self.full_grad)
+        self.grad_allocated = False
+
+    def pre_backward(self):
+        if self.reshard:
+            self.materialize(prefetch=self.prev_unit)
+            self.wait_gather()
+            self.ensure_grad()
+
+    def post_forward(self):
+        if self.reshard:
+            self.release()
+
     def pre_forward(self):
+        if self.reshard:
+            self.materialize(prefetch=self.next_unit)
         self.wait_gather()
         # the backward pass that follows writes gradients: an earlier micro-batch's reduction of
         # this unit must have finished with the buffer (the wait is queued on the stream now, the
@@ -214,6 +321,7 @@ class FlatUnit:
         if self._backward_done:
             return
         self._backward_done = True
+        self.ensure_grad()          # (a unit whose output needed no gradient never saw `pre_backward`)
         # a reduction of an earlier pass may still be reading (or, when the shard is the whole
         # buffer, rewriting) the gradient buffer this pass has just added to
         self.wait_reduce_before_write()
@@ -242,6 +350,10 @@ class FlatUnit:
             self._needs_reduce = True
         else:
             self.start_reduce()
+        if self.reshard:
+            self.release()
+            if self.state is not None:
+                self.state.grad_released_later(self)
 
     def wait_reduce_before_write(self):
         """Order the current stream after a reduction of this unit that is still in flight."""
@@ -282,10 +394,16 @@ class FlatUnit:
     # ------------------------------------------------------------------ optimizer side
     def init_master(self):
         """fp32 master copy of this rank's shard, taken from the current low-precision values."""
-        self.master = self.full_param[self.lo:self.hi].float().clone()
+        self.master = self.param_shard().float().clone()
         return self.master
 
     def param_shard(self):
+        """This rank's low-precision shard (what the optimizer rewrites). On the memory-lean
+        schedule that is `local_shard`; a unit that is whole at this point is released first, so
+        its current values are carried over."""
+        if self.reshard:
+            self.release()
+            return self.local_shard
         return self.full_param[self.lo:self.hi]
 
     def decay_split(self):
@@ -300,6 +418,8 @@ class FlatUnit:
         this rank's shard from inside one of their GEMM launches."""
         if self.ws == 1:
             return
+        if self.reshard:
+            return          # gathered lazily, right before the unit's next forward
         if self.fused is not None and epoch is not None:
             self.fused.publish(epoch)
             return
@@ -316,8 +436,11 @@ class FlatUnit:
 
     def sync_from_rank_shards(self):
         """Make `full_param` identical everywhere (used once after initialisation)."""
+        if self.reshard and not self.materialized:
+            self.materialize()
+            self.wait_gather()
         if self.ws > 1:
-            comm.all_gather_flat(self.full_param, self.param_shard().clone(), self.shard_group)
+            comm.all_gather_flat(self.full_param, self.full_param[self.lo:self.hi].clone(), self.shard_group)
         if self.replicate_group is not None:
             dist.broadcast(self.full_param, src=dist.get_global_rank(self.replicate_group, 0),
                            group=self.replicate_group)
@@ -545,6 +668,11 @@ class ShardedModel:
         self.comm_stream = comm_stream
         self.gather_heap = None
         self.reduce_heap = None
+        self._grad_pending = []
+        for a, b in zip(units[:-1], units[1:]):
+            a.next_unit, b.prev_unit = b, a
+        for u in units:
+            u.state = self
 
     def wait_parameters(self):
         """Make the current stream see whole, current parameters in every unit: waits for the
@@ -552,8 +680,22 @@ class ShardedModel:
         Anything that reads or writes parameters outside the model's own forward (state_dict,
         checkpoint staging, weight export to an engine, in-place re-normalisation) calls this."""
         for u in self.units:
+            u.materialize()
             u.wait_gather()
         self.flush_gathers()
+
+    def grad_released_later(self, unit):
+        """A resharded unit's gradient buffer is freed when the NEXT unit finishes its backward:
+        by then the reduction has had a whole unit's backward to complete, so the wait is free."""
+        older, self._grad_pending = self._grad_pending, [unit]
+        for u in older:
+            if u is not unit:
+                u.release_grad()
+
+    def release_gradients(self):
+        for u in self._grad_pending:
+            u.release_grad()
+        self._grad_pending = []
 
     def no_sync(self):
         """Context manager for gradient accumulation: backward passes inside it only add into the
@@ -592,6 +734,7 @@ class ShardedModel:
     def wait_reductions(self):
         for u in self.units:
             u.wait_reduce()
+        self.release_gradients()
 
     def sync_parameters(self):
         for u in self.units:
@@ -746,8 +889,18 @@ def apply_fsdp(model, mesh=None, param_dtype=torch.bfloat16, reduce_dtype=torch.
             x = _UnitBoundary.apply(x, u)
         return x
 
-    def post_block(i, x):
-        return x
+    def post_block(i, x, residual=None):
+        u = block_units.get(i)
+        if u is None or not u.reshard:
+            return x, residual
+        if torch.is_grad_enabled():
+            # whichever of the block's outputs receives its gradient first brings the unit back
+            if x.requires_grad:
+                x = _UnitPreBackward.apply(x, u)
+            if residual is not None and residual.requires_grad:
+                residual = _UnitPreBackward.apply(residual, u)
+        u.post_forward()
+        return x, residual
 
     model.block_hooks = (pre_block, post_block)
 
@@ -770,6 +923,18 @@ def apply_fsdp(model, mesh=None, param_dtype=torch.bfloat16, reduce_dtype=torch.
     model.register_forward_pre_hook(root_pre_forward, with_kwargs=True)
     # state_dict() hands out views of the flat buffers: they must be whole and current first
     model.register_state_dict_pre_hook(lambda module, prefix, keep_vars: state.wait_parameters())
+    if reshard_after_forward and shard_group is not None and calls_block_hooks:
+        # block units follow the memory-lean schedule; the root (embedding) and head units are used
+        # at both ends of every pass and stay whole, as the reference's outermost wrapper does
+        for u in block_units.values():
+            if u is not head_unit:
+                u.enable_reshard()
+        fused_all_gather = fused_reduce_scatter = False
+    elif reshard_after_forward and shard_group is not None:
+        from halite_b200.logging import logger
+
+        logger.warning("reshard_after_forward: this model's forward does not announce its blocks, so its "
+                       "parameters stay gathered")
     if fused_all_gather is None:
         import os
 

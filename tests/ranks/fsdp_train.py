@@ -21,6 +21,7 @@ mode = sys.argv[1] if len(sys.argv) > 1 else "fsdp"
 # same without `no_sync()` (a reduction per micro-batch, which must still give the right sum)
 micro = "_micro" in mode
 hold_back = micro and not mode.endswith("_sync")
+reshard = "_reshard" in mode      # memory-lean schedule: units are whole only around their own passes
 mode = mode.split("_")[0]
 
 
@@ -49,7 +50,10 @@ steps = 20 if mode == "fsdp" and not micro else 6
 g = torch.Generator().manual_seed(0)
 data = torch.randint(0, 1024, (ws, steps, 4, 257), generator=g)
 model, ref = build(), build()
-model = parallelize(model, pd, pd, param_dtype="float32", reduce_dtype="float32", device="cpu")
+model = parallelize(model, pd, pd, param_dtype="float32", reduce_dtype="float32", device="cpu",
+                    reshard_after_forward=reshard)
+if reshard:
+    assert sum(u.reshard for u in model._hb_fsdp.units) == 4
 opt = build_optimizer(partial(torch.optim.AdamW, lr=3e-4, betas=(0.9, 0.95)), model, weight_decay=0.1)
 ropt = torch.optim.AdamW(group_parameters(ref, 0.1), lr=3e-4, betas=(0.9, 0.95))
 worst = 0.0
@@ -84,6 +88,12 @@ for step in range(steps):
     lt = loss.detach().clone()
     dist.all_reduce(lt)
     worst = max(worst, abs(lt.item() / ws - tot), abs(n.item() - rn.item()))
+if reshard:
+    blocks = [u for u in model._hb_fsdp.units if u.reshard]
+    # between steps a rank holds only its shard of every block, and no full gradient buffer
+    assert all(u.full_param.untyped_storage().size() == 0 for u in blocks), "parameters were left gathered"
+    assert all(u.full_grad.untyped_storage().size() == 0 for u in blocks), "gradient buffers were left allocated"
+    model._hb_fsdp.wait_parameters()      # whole again for the comparison below
 diff = max((a - b).abs().max().item() for a, b in zip(model.parameters(), ref.parameters()))
 print(f"RESULT rank={rank} loss_norm_dev={worst:.3e} param_diff={diff:.3e} final_loss={tot:.4f}")
 assert worst < 1e-4 and diff < 1e-4
