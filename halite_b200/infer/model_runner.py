@@ -144,6 +144,15 @@ class ModelRunner:
         return self.model(fb)
 
     @torch.no_grad()
+    def forward_decode(self, fb: ForwardBatch):
+        """One decode forward: replays the captured graph of the batch's size bucket when CUDA
+        graphs are on (capturing it at first use), else runs eagerly."""
+        graph = self._graph_for(fb.batch_size) if self.server_config.use_cudagraph else None
+        if graph is not None:
+            return self._replay(graph, fb)
+        return self.forward(fb)
+
+    @torch.no_grad()
     def forward_and_sample(self, batch):
         logits = self.forward(batch.forward_batch)
         ids, logprobs = self.sampler(logits, batch.sampling)

@@ -4,7 +4,17 @@ from __future__ import annotations
 
 from typing import Any
 
+import torch
 from torch import nn
+from torch.utils.checkpoint import checkpoint
+
+
+def _run_ff(block, module, x):
+    """The feed-forward half of a block, recomputed in backward when the block's `checkpoint_ff`
+    flag is set (selective activation checkpointing, per-op form)."""
+    if getattr(block, "checkpoint_ff", False) and block.training and torch.is_grad_enabled() and x.requires_grad:
+        return checkpoint(module, x, use_reentrant=False)
+    return module(x)
 
 
 class ResidualBlock(nn.Module):
@@ -54,7 +64,7 @@ class TransformerEncoderBlock(nn.Module):
                 cache: Any = None, use_cache: bool = True, unpad_params=None):
         out, next_cache = self.self_attention(input, attention_mask, attention_bias, pos_emb, cache,
                                               use_cache, unpad_params)
-        out = self.ff(out)
+        out = _run_ff(self, self.ff, out)
         rest = None
         if isinstance(out, tuple):
             out, rest = out
@@ -83,7 +93,7 @@ class FusedTransformerEncoderBlock(nn.Module):
         out, next_cache = sa.module(normed, attention_mask, attention_bias, pos_emb, cache, use_cache,
                                     unpad_params)
         normed, residual = ff.pre_norm(out, residual)
-        out = ff.module(normed)
+        out = _run_ff(self, ff.module, normed)
         rest = None
         if isinstance(out, tuple):
             out, rest = out

@@ -93,8 +93,17 @@ class TransformerDecoder(nn.Module, ModelMixin, GenerationMixin):
             self.adapters = {}
         self.adapters[name] = keys
 
-    def gradient_checkpointing_enable(self, n_layer=1):
-        self.gradient_checkpointing = n_layer
+    def gradient_checkpointing_enable(self, n_layer=1, stride=1, ops=False):
+        """Activation checkpointing. `n_layer` > 0: blocks are recomputed in groups of `n_layer`
+        (1 = every block on its own); with `stride` k only every k-th block is recomputed and the
+        others keep their activations (the "selective layer" form). `ops=True` is the selective
+        per-op form: inside every block the attention half keeps what it saved and the feed-forward
+        half, whose gate / up / activation tensors are most of a block's activation memory, is
+        recomputed from its normalised input (reference: transformers/parallelize.py:64-127)."""
+        self.gradient_checkpointing = int(n_layer)
+        self.checkpoint_stride = max(1, int(stride))
+        for block in self.blocks.values():
+            block.checkpoint_ff = bool(ops)
 
     def enable_input_require_grads(self):
         def hook(module, input, output):
@@ -219,6 +228,7 @@ class TransformerDecoder(nn.Module, ModelMixin, GenerationMixin):
 
         if self.gradient_checkpointing > 0 and self.training:
             step = self.gradient_checkpointing
+            stride = getattr(self, "checkpoint_stride", 1)
             for start in range(0, n_blocks, step):
                 mods = [self.blocks[str(i)] for i in range(start, min(start + step, n_blocks))]
 
@@ -231,7 +241,10 @@ class TransformerDecoder(nn.Module, ModelMixin, GenerationMixin):
                             x, res = hooks[1](start + j, x, res)
                     return x, res
 
-                out, residual = utils.checkpoint.checkpoint(run, out, residual, use_reentrant=False)
+                if (start // step) % stride == 0:
+                    out, residual = utils.checkpoint.checkpoint(run, out, residual, use_reentrant=False)
+                else:
+                    out, residual = run(out, residual)
         else:
             for key, block in self.blocks.items():
                 index = int(key)

@@ -124,6 +124,19 @@ class InferenceEngine:
             state_dict = {k: v.detach() for k, v in sorted(state_dict.items())}
         self.channel.command(Command("load_state_dict", state_dict))
 
+    def update_weights_broadcast(self, src=0, group=None):
+        """Take new weights from rank `src` of `group` with one `dist.broadcast` per parameter,
+        written in place into the worker's model (reference: tokainfer/utils.py:774-782). Inline
+        placement only: the worker's tensors must be reachable from this process."""
+        if not isinstance(self.channel, _InlineChannel):
+            raise RuntimeError("broadcast weight updates need placement='inline'")
+        self.channel.worker.update_weights_broadcast(src, group)
+
+    def cancel(self, request_ids):
+        """Cancel requests by id; safe to call from a callback between scheduling rounds (for
+        example the `on_step` hook of `infer_batch`)."""
+        return self.manager.cancel(request_ids)
+
     def shutdown(self):
         self.channel.close()
 
@@ -144,9 +157,10 @@ class InferenceEngine:
             return i, ids, sp
         return req
 
-    def infer_batch(self, requests):
+    def infer_batch(self, requests, on_step=None):
         """Run every request to completion; returns one `InferenceResult` per request (with `n`
-        samples each), ordered by request id."""
+        samples each), ordered by request id. `on_step(engine)` runs after every batch of results
+        and may call `engine.cancel(...)`."""
         mgr = self.manager
         groups = {}
         for i, req in enumerate(requests):
@@ -165,6 +179,8 @@ class InferenceEngine:
                     if more is None:
                         break
                     mgr.process_output(more)
+                if on_step is not None:
+                    on_step(self)
             elif mgr.waiting and not mgr.running:
                 mgr.schedule_ahead()
                 if not mgr.inflight_steps and not mgr.running:

@@ -59,6 +59,26 @@ class Manager:
             out.append(seq)
         return out
 
+    def cancel(self, request_ids):
+        """Stop the named requests (reference: tokainfer/engine/manager.py cancellation commands): a
+        waiting sequence never starts, a running one gives back its blocks now and the results of
+        forwards already in flight for it are dropped when they arrive. Returns the sequences
+        that were cancelled; they are reported with finish reason "cancelled" and the tokens
+        received so far."""
+        wanted = set(request_ids)
+        hit = []
+        for seq in [s for s in self.waiting if s.request_id in wanted]:
+            self.waiting.remove(seq)
+            seq.finished, seq.finish_reason = True, "cancelled"
+            self.finished.append(seq)
+            hit.append(seq)
+        for seq in [s for s in self.running if s.request_id in wanted and not s.finished]:
+            seq.finished, seq.finish_reason = True, "cancelled"
+            self._release(seq, finished=False)
+            self.finished.append(seq)
+            hit.append(seq)
+        return hit
+
     def idle(self):
         return not self.waiting and not self.running and not self.inflight_steps
 

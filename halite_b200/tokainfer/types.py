@@ -32,7 +32,7 @@ class ServerConfig:
     use_hydragen: bool = False
     hydragen_min_group_size: int = 32
     hydragen_min_prefix_len: int = 256
-    use_cudagraphs: bool = True
+    use_cudagraphs: bool = True                 # decode-only forwards replay a graph per batch-size bucket
     placement: str = "inline"                   # "inline" (same process) or "process"
     dp_size: int = 1
     pp_size: int = 1

@@ -19,8 +19,13 @@ from halite_b200.tokainfer.types import Command, ModelInput, ModelOutput
 class ModelWorker:
     def __init__(self, model, model_config, server_config):
         self.server_config = server_config
+        # decode-only forwards replay one CUDA graph per batch-size bucket (reference:
+        # tokainfer/utils.py:528-635) when `use_cudagraphs` is set
         runner_conf = RunnerConfig(page_size=server_config.page_size, max_total_tokens=server_config.kv_cache_num_tokens,
-                                   max_running_requests=server_config.max_seqs_per_forward, seed=server_config.seed)
+                                   max_running_requests=server_config.max_seqs_per_forward, seed=server_config.seed,
+                                   use_cudagraph=bool(server_config.use_cudagraphs),
+                                   cudagraph_additonal_batch_size=(1, 2, 4, 8),
+                                   cudagraph_max_batch_size=min(512, server_config.max_seqs_per_forward))
         if server_config.kv_cache_num_tokens is None:
             model_config.memory_fraction_static = server_config.memory_fraction
         self.runner = ModelRunner(model, model_config, runner_conf)
@@ -45,6 +50,13 @@ class ModelWorker:
 
     def load_state_dict(self, state_dict, assign=True):
         self.runner.load_state_dict(state_dict, assign=assign)
+
+    @torch.no_grad()
+    def update_weights_broadcast(self, src=0, group=None):
+        import torch.distributed as dist
+
+        for _, p in sorted(self.runner.model.named_parameters()):
+            dist.broadcast(p.data, src=src, group=group)
 
     def handle(self, command: Command):
         if command.kind == "cleanup":
@@ -139,7 +151,7 @@ class ModelWorker:
             req_slots=torch.tensor(inp.batch_indices, dtype=torch.int32, device=dev),
             seq_lens=torch.tensor(seq_lens, dtype=torch.int32, device=dev), page_table=table,
             max_seq_len=max(seq_lens), max_extend_len=1, page_size=ps, seq_lens_cpu=seq_lens)
-        return self._sample(inp, r.forward(fb), rows)
+        return self._sample(inp, r.forward_decode(fb), rows)
 
 
 class LazyModelOutput:

@@ -191,3 +191,39 @@ def test_micro_batches_accumulate_in_every_sharding_unit(zoo):
     opt.step()                                   # consumes the sum (learning rate 0: weights unchanged)
     for x, z in zip(ga, grads([a])):
         torch.testing.assert_close(z, x, atol=1e-6, rtol=1e-6)
+
+
+@pytest.mark.parametrize("config", [{"mode": "full"}, {"mode": "full", "every": 2}, {"mode": "selective", "selective": "2"},
+                                    {"mode": "selective", "selective": "op"}])
+def test_activation_checkpointing_modes_leave_gradients_unchanged(zoo, config):
+    """Full, every-N, every-k-th-block and per-op (feed-forward half) checkpointing recompute
+    activations but must produce the gradients of the plain run."""
+    from halite_b200.conf import instantiate
+    from halite_b200.parallel import parallelize
+    from tests.conftest import tiny_llama_conf
+
+    def grads(ac_config):
+        torch.manual_seed(0)
+        model = instantiate(tiny_llama_conf(zoo, n_layers=4, dim=64, intermediate_size=96, n_heads=2, head_dim=32,
+                                            n_key_value_heads=1, vocab_size=128))
+        model.init_weights()
+        if ac_config is not None:
+            model = parallelize(model, None, None, param_dtype="float32", reduce_dtype="float32", device="cpu",
+                                activation_checkpointing=True, activation_checkpointing_config=ac_config)
+        else:
+            model = parallelize(model, None, None, param_dtype="float32", reduce_dtype="float32", device="cpu")
+        model.train()
+        x = torch.randint(0, 128, (2, 17), generator=torch.Generator().manual_seed(1))
+        loss = torch.nn.functional.cross_entropy(model(x[:, :-1]).logits.flatten(0, 1), x[:, 1:].flatten())
+        loss.backward()
+        model._hb_fsdp.finish_backward()
+        return loss.item(), [u.full_grad.clone() for u in model._hb_fsdp.units]
+
+    base_loss, base = grads(None)
+    loss, got = grads(config)
+    assert abs(loss - base_loss) < 1e-6
+    for a, b in zip(base, got):
+        torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
+
+    with pytest.raises(ValueError):
+        grads({"mode": "sometimes"})

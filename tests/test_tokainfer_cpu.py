@@ -224,3 +224,35 @@ def test_engine_with_worker_process_and_lifecycle():
         assert again.output_ids[0] == out.output_ids[0]
     finally:
         eng.shutdown()
+
+
+def test_cancel_releases_blocks_and_keeps_other_requests_exact():
+    """A request cancelled while it runs (and one cancelled before it starts) gives its blocks and
+    batch index back, reports finish reason "cancelled" with the tokens received so far, and the
+    requests that were not cancelled still match dense greedy decoding."""
+    model, imodel = build_pair()
+    conf = ServerConfig(kv_cache_num_tokens=4096, scheduling_steps_ahead=2, max_seqs_per_forward=3)
+    eng = InferenceEngine(imodel, None, model_config(), conf)
+    eng.load_state_dict(model.state_dict())
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (12, 30, 21, 8, 16)]
+    calls = {"n": 0}
+
+    def on_step(engine):
+        calls["n"] += 1
+        if calls["n"] == 3:
+            hit = engine.cancel([1, 4])          # 1 is running by now, 4 is still waiting (3 slots)
+            assert {s.request_id for s in hit} == {1, 4}
+
+    res = eng.infer_batch([InferenceRequest(i, p, {"max_new_tokens": 24, "top_k": 1}) for i, p in enumerate(prompts)],
+                          on_step=on_step)
+    by_id = {r.id: r for r in res}
+    assert by_id[1].finish_reason == ["cancelled"] and 0 < len(by_id[1].output_ids[0]) < 24
+    assert by_id[4].finish_reason == ["cancelled"] and by_id[4].output_ids[0] == []
+    assert by_id[1].output_ids[0] == dense_greedy(model, prompts[1], 24)[: len(by_id[1].output_ids[0])]
+    for i in (0, 2, 3):
+        assert by_id[i].output_ids[0] == dense_greedy(model, prompts[i], 24) and by_id[i].finish_reason == ["length"]
+    mgr = eng.manager
+    mgr.allocator.sanity_checks(set())
+    assert mgr.allocator.num_free_blocks() == mgr.num_blocks
+    assert mgr.batch_indices.available() == mgr.batch_indices.max_indices
