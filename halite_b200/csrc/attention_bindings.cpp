@@ -5,6 +5,7 @@
 
 #include "attention.h"
 #include "launch_count.h"
+#include "reshard.h"
 
 namespace {
 
@@ -102,6 +103,18 @@ at::Tensor attention_bwd(const at::Tensor& q, const at::Tensor& k, const at::Ten
   return dq;
 }
 
+// `table`: int64 [n, 14] on the device, rows laid out as hb::ReshardSegment
+// (dst, src_base[8], src_byte0, src_pitch, shard_bytes, row_bytes, rows).
+void reshard_copy(const at::Tensor& table) {
+  static_assert(sizeof(hb::ReshardSegment) == 14 * sizeof(int64_t), "segment layout");
+  TORCH_CHECK(table.is_cuda() && table.scalar_type() == at::kLong && table.is_contiguous() && table.dim() == 2 &&
+                  table.size(1) == 14, "segment table must be a contiguous CUDA int64 [n, 14] tensor");
+  c10::cuda::CUDAGuard guard(table.device());
+  HB_ATTN_OK(hb::reshard_copy(reinterpret_cast<const hb::ReshardSegment*>(table.data_ptr<int64_t>()),
+                              (int)table.size(0), at::cuda::getCurrentCUDAStream().stream()),
+             1);
+}
+
 }  // namespace
 
 void register_attention(pybind11::module_& m) {
@@ -109,6 +122,7 @@ void register_attention(pybind11::module_& m) {
   m.def("attention_fwd", &attention_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("seg_start") = py::none(),
         py::arg("seg_end") = py::none(), py::arg("seq_len") = 0, py::arg("causal") = true, py::arg("window") = 0,
         py::arg("scale") = 1.0, py::arg("softcap") = 0.0, py::arg("status") = py::none());
+  m.def("reshard_copy", &reshard_copy, py::arg("table"));
   m.def("attention_bwd", &attention_bwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"), py::arg("d_out"),
         py::arg("lse"), py::arg("dk"), py::arg("dv"), py::arg("seg_start") = py::none(),
         py::arg("seg_end") = py::none(), py::arg("seq_len") = 0, py::arg("causal") = true, py::arg("window") = 0,

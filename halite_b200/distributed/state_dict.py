@@ -17,8 +17,8 @@ def _full(t):
 
 def reshard_state_dict(source, target, device=None, dtype=None, tp_rank=0, tp_size=1, tp_plan=None,
                        in_place=False):
-    """Returns {key: tensor} for every key of `target`. `tp_plan` maps key -> ("shard", dim)
-    for tensors the inference model holds a 1/tp_size slice of. With `in_place` the values are
+    """Returns {key: tensor} for every key of `target`. `tp_plan` maps key -> ("shard", dim) or
+    ("shard_parts", dim, parts) for tensors the inference model holds a 1/tp_size slice of. With `in_place` the values are
     copied into `target`'s own tensors (which keep their addresses) and `target` is returned."""
     out = {}
     for key, ref in target.items():
@@ -32,10 +32,18 @@ def reshard_state_dict(source, target, device=None, dtype=None, tp_rank=0, tp_si
             src_key = alt[0]
         t = _full(source[src_key]).detach()
         if tp_plan and key in tp_plan and tp_size > 1:
-            kind, dim = tp_plan[key]
+            kind, dim = tp_plan[key][0], tp_plan[key][1]
             if kind == "shard":
                 n = t.shape[dim] // tp_size
                 t = t.narrow(dim, tp_rank * n, n)
+            elif kind == "shard_parts":
+                # consecutive blocks along `dim` (q | k | v rows) are each cut for this rank
+                pieces, at = [], 0
+                for n in tp_plan[key][2]:
+                    step = n // tp_size
+                    pieces.append(t.narrow(dim, at + tp_rank * step, step))
+                    at += n
+                t = torch.cat(pieces, dim)
         if in_place:
             if tuple(t.shape) != tuple(ref.shape):
                 raise ValueError(f"shape mismatch for {key}: {tuple(t.shape)} vs {tuple(ref.shape)}")

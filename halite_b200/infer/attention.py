@@ -17,6 +17,7 @@ from halite_b200 import ops
 from halite_b200.models.initialize import init_weights
 from halite_b200.models.position import RotaryTable, apply_rotary_emb
 from halite_b200.ops import paged_attention as pa
+from halite_b200.infer.tensor_parallel import row_parallel_linear
 
 
 def _is_plain_rope(fn):
@@ -128,7 +129,7 @@ class InferSelfAttentionQKV(nn.Module):
         if self.layer_type is not None and isinstance(pos_emb, dict):
             pos_emb = pos_emb[self.layer_type]
         out = self.attention(q, k, v, forward_batch, pos_emb)
-        return ops.linear(out, self.out.weight, self.out.bias)
+        return row_parallel_linear(self, out, self.out)
 
 
 class InferSelfAttention(nn.Module):
@@ -165,4 +166,4 @@ class InferSelfAttention(nn.Module):
         if self.layer_type is not None and isinstance(pos_emb, dict):
             pos_emb = pos_emb[self.layer_type]
         out = a(q, k, v, forward_batch, pos_emb)
-        return ops.linear(out, self.out.weight, self.out.bias)
+        return row_parallel_linear(self, out, self.out)

@@ -10,7 +10,6 @@
 from __future__ import annotations
 
 import copy
-import uuid
 from typing import Any
 
 from torch import nn
@@ -22,8 +21,18 @@ from halite_b200.infer.types import InferenceResult, ModelConfig, ServerConfig
 
 class InferenceEngine:
     def __init__(self, model: nn.Module, tokenizer: Any, model_config: ModelConfig,
-                 server_config: ServerConfig | None = None):
+                 server_config: ServerConfig | None = None, tp_group=None):
+        """`model_config.tp_size` > 1 runs the engine tensor-parallel over `tp_group`: every rank of
+        the group constructs the engine, loads the same state dict and calls `infer_batch` with the
+        same requests; each keeps its slice of the weights and its KV heads."""
         server_config = server_config or ServerConfig()
+        self._ids = 0
+        if model_config.tp_size > 1 and getattr(model, "_infer_tp", None) is None:
+            import torch.distributed as dist
+
+            from halite_b200.infer.tensor_parallel import apply_infer_tp
+
+            apply_infer_tp(model, dist.get_rank(tp_group), model_config.tp_size, tp_group)
         self.model_runner = ModelRunner(model, model_config, server_config)
         self.scheduler = Scheduler(self.model_runner, tokenizer, server_config)
         self.model_config = model_config
@@ -52,6 +61,15 @@ class InferenceEngine:
     def load_state_dict(self, state_dict, assign=True):
         self.model_runner.load_state_dict(state_dict, assign=assign)
 
+    def load_from_model(self, train_model):
+        """Weights straight from a sharded training model (one reshard kernel launch)."""
+        self.model_runner.load_from_model(train_model)
+
+    def _new_id(self):
+        # a counter, not a random id: tensor-parallel ranks must name (and order) requests alike
+        self._ids += 1
+        return f"_hb-internal-{self._ids:09d}"
+
     @property
     def stats(self):
         return self.scheduler.stats
@@ -71,7 +89,7 @@ class InferenceEngine:
         seeds = []
         for r in requests:
             s = copy.copy(r)
-            s.id = uuid.uuid4().hex
+            s.id = self._new_id()
             s.sampling_params = copy.copy(r.sampling_params)
             s.sampling_params.max_new_tokens = 0
             s.output_ids, s.output_logprobs = [], []
@@ -81,7 +99,7 @@ class InferenceEngine:
         for r in requests:
             for _ in range(n):
                 c = copy.copy(r)
-                c.id = uuid.uuid4().hex
+                c.id = self._new_id()
                 c.output_ids, c.output_logprobs = [], []
                 owner[c.id] = r.id
                 copies.append(c)

@@ -55,6 +55,8 @@ class ModelRunner:
         self.graphs = {}
         self.graph_state = None
         self.workspace = None
+        self._resharder = None
+        self._resharder_src = None
         self.initialize()
 
     # ------------------------------------------------------------------ lifecycle
@@ -107,6 +109,7 @@ class ModelRunner:
     def cleanup(self):
         """Give the device memory back (weights and pools) so training can use it."""
         self.model.to("meta")
+        self._resharder = None                 # its destination tensors are gone with the weights
         if hasattr(self.model, "set_kv_pool"):
             self.model.set_kv_pool(None)       # the attention layers hold the pool too
         self.req_pool = None
@@ -120,14 +123,16 @@ class ModelRunner:
     def load_state_dict(self, state_dict, assign=True):
         from halite_b200.distributed.state_dict import reshard_state_dict
 
+        tp = getattr(self.model, "_infer_tp", None)
+        tp_kw = {} if tp is None else dict(tp_rank=tp.rank, tp_size=tp.size, tp_plan=self.model._infer_tp_plan)
         resident = self.server_config.keep_resident and not any(p.is_meta for p in self.model.parameters())
         if resident:
             # same storage, new values: captured graphs and tensor maps stay valid
-            reshard_state_dict(state_dict, self.model.state_dict(), device=self.device, in_place=True)
+            reshard_state_dict(state_dict, self.model.state_dict(), device=self.device, in_place=True, **tp_kw)
             return
         self.model.to("meta")
         target = self.model.state_dict()
-        sd = reshard_state_dict(state_dict, target, device=self.device)
+        sd = reshard_state_dict(state_dict, target, device=self.device, **tp_kw)
         if not assign:
             self.model.to_empty(device=self.device)
         self.model.load_state_dict(sd, assign=assign)
@@ -136,6 +141,37 @@ class ModelRunner:
         if hasattr(self.model, "set_kv_pool") and self.kv_pool is not None:
             self.model.set_kv_pool(self.kv_pool)
         self.graphs = {}
+
+    def load_from_model(self, train_model):
+        """Take the weights of a sharded training model with the one-launch reshard kernel
+        (`parallel/reshard.py`): the engine's tensors are allocated once in its own layout (this
+        rank's tensor-parallel slices) and filled straight from the flat unit buffers, or from the
+        ranks' shards over NVLink when the trainer keeps only shards. Falls back to
+        `load_state_dict(train_model.state_dict())` off the GPU or for an unsharded model."""
+        if self.device.type != "cuda" or getattr(train_model, "_hb_fsdp", None) is None:
+            return self.load_state_dict(train_model.state_dict())
+        from halite_b200.parallel.reshard import FusedResharder
+
+        tp = getattr(self.model, "_infer_tp", None)
+        if any(p.is_meta for p in self.model.parameters()) or self._resharder is None \
+                or self._resharder_src is not train_model:
+            self.model.to("meta")
+            target = {k: torch.empty(v.shape, dtype=next(iter(train_model._hb_fsdp.units)).param_dtype,
+                                     device=self.device)
+                      for k, v in self.model.state_dict().items()}
+            self.model.load_state_dict(target, assign=True)
+            if hasattr(self.model, "init_buffers"):
+                self.model.init_buffers(self.device)
+            if hasattr(self.model, "set_kv_pool") and self.kv_pool is not None:
+                self.model.set_kv_pool(self.kv_pool)
+            self.graphs = {}
+            # after packing, q | k | v (gate | up) are views of one matrix: the state dict still
+            # names them separately and every view is contiguous, which is all the kernel needs
+            live = dict(self.model.state_dict())
+            self._resharder = FusedResharder(train_model, live, tp.rank if tp else 0, tp.size if tp else 1,
+                                             getattr(self.model, "_infer_tp_plan", None))
+            self._resharder_src = train_model
+        self._resharder.run()
 
     # ------------------------------------------------------------------ forward
     @torch.no_grad()

@@ -148,6 +148,10 @@ class FeedForward(nn.Module):
         out = ops.linear(input, self.linear1.weight, self.linear1.bias)
         out = self.activation(out)
         out = self.dropout(out)
+        if getattr(self, "_infer_tp", None) is not None:       # inference engine, row-parallel output
+            from halite_b200.infer.tensor_parallel import row_parallel_linear
+
+            return row_parallel_linear(self, out, self.linear2)
         return ops.linear(out, self.linear2.weight, self.linear2.bias)
 
     def tp_plan(self):
@@ -232,6 +236,10 @@ class GatedFeedForward(nn.Module):
             else:
                 out = proj * self.activation(gate)
         out = self.dropout(out)
+        if getattr(self, "_infer_tp", None) is not None:       # inference engine, row-parallel output
+            from halite_b200.infer.tensor_parallel import row_parallel_linear
+
+            return row_parallel_linear(self, out, self.linear_out)
         return _project(self.linear_out, out)
 
     def tp_plan(self):

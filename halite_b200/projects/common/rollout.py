@@ -163,6 +163,14 @@ class RolloutGenerator:
     def load_state_dict(self, state_dict, assign=True):
         self.inference_engine.load_state_dict(state_dict, assign=assign)
 
+    def load_from_model(self, model):
+        """Weight hand-over from a (sharded) training model; engines that have a fused reshard
+        path use it, the others go through the state dict."""
+        if hasattr(self.inference_engine, "load_from_model"):
+            self.inference_engine.load_from_model(model)
+        else:
+            self.inference_engine.load_state_dict(model.state_dict())
+
     def generate(self, rollouts):
         results = self.inference_engine.infer_batch([r.to_inference_request() for r in rollouts])
         by_id = {res.id: res for res in results}

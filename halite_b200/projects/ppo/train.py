@@ -192,7 +192,7 @@ class PPOLoop:
         clean_memory()
         gen = self.rollout_generator
         gen.initialize()
-        gen.load_state_dict(self.actor.state_dict())
+        gen.load_from_model(self.actor)
         rollout = gen.generate(self.request_builder(batch))
         gen.cleanup()
         clean_memory()

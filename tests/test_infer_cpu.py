@@ -272,3 +272,14 @@ def test_native_radix_tree_agrees_with_python_under_random_traffic():
     assert alloc.alloc(8) is None and alloc.available() == 7
     alloc.free(first)
     assert alloc.available() == 10 and alloc.capacity() == 10
+
+
+def test_tensor_parallel_engine_matches_dense_on_two_ranks():
+    """tp=2 over Gloo: each rank holds its slice of the projections and its KV heads, the ranks
+    take identical scheduling and sampling decisions, and the tokens equal dense decoding."""
+    import os
+
+    from tests.helpers import ROOT, run_ranks
+
+    outs = run_ranks(os.path.join(ROOT, "tests/ranks/infer_tp.py"), 2, timeout=600)
+    assert all(o.count("TP_OK") == 2 for o in outs), outs[0][-3000:]
