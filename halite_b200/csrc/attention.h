@@ -42,13 +42,25 @@ struct AttnArgs {
 // out = softmax(mask(scale * q k^T)) v, plus the log-sum-exp per (head, token).
 cudaError_t attention_fwd(const AttnArgs& a, void* out, float* lse);
 
+// Optional inverse rotation of dQ on its way out (q was rotated in place before the forward):
+// cos / sin fp32 [max_position, rot_dim / 2], one position per token. cos == nullptr: none.
+struct AttnDqRotation {
+  const float* cos = nullptr;
+  const float* sin = nullptr;
+  const void* positions = nullptr;
+  bool pos_is_i64 = true;
+  int rot_dim = 0;
+  bool interleaved = true;
+};
+
 // Gradients. `o`, `d_o`: [total, n_heads, head_dim] contiguous bf16; `lse` from the forward.
 // `delta` fp32 [n_heads, total] and `dq_accum` fp32 [total, n_heads, head_dim] are scratch the
-// caller provides (dq_accum is zeroed here). dq: bf16 [total, n_heads, head_dim] contiguous;
-// dk, dv: bf16 [total, n_kv_heads, head_dim] with `dk_tok_stride` / `dv_tok_stride` elements
-// between tokens.
+// caller provides (dq_accum is zeroed here). dq: bf16 [total, n_heads, head_dim] and dk, dv:
+// bf16 [total, n_kv_heads, head_dim], each with its own number of elements between tokens, so
+// all three may be slots of one packed qkv gradient.
 cudaError_t attention_bwd(const AttnArgs& a, const void* o, const void* d_o, const float* lse,
-                          float* delta, float* dq_accum, void* dq, void* dk, long dk_tok_stride,
-                          void* dv, long dv_tok_stride);
+                          float* delta, float* dq_accum, void* dq, long dq_tok_stride,
+                          const AttnDqRotation& rot, void* dk, long dk_tok_stride, void* dv,
+                          long dv_tok_stride);
 
 }  // namespace hb

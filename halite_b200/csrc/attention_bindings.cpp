@@ -78,13 +78,15 @@ std::tuple<at::Tensor, at::Tensor> attention_fwd(const at::Tensor& q, const at::
   return {out, lse};
 }
 
-// dk / dv are written into the given views (slices of a packed gradient are fine); returns dq
-// as a new contiguous tensor shaped like q.
-at::Tensor attention_bwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& out,
-                         const at::Tensor& d_out, const at::Tensor& lse, at::Tensor& dk, at::Tensor& dv,
-                         const c10::optional<at::Tensor>& seg_start, const c10::optional<at::Tensor>& seg_end,
-                         int64_t seq_len, bool causal, int64_t window, double scale, double softcap,
-                         const c10::optional<at::Tensor>& status) {
+// dq / dk / dv are written into the given views (slots of a packed gradient are fine). With
+// cos / sin / positions, dq is rotated back on its way out (inverse RoPE).
+void attention_bwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& out,
+                   const at::Tensor& d_out, const at::Tensor& lse, at::Tensor& dq, at::Tensor& dk, at::Tensor& dv,
+                   const c10::optional<at::Tensor>& seg_start, const c10::optional<at::Tensor>& seg_end,
+                   int64_t seq_len, bool causal, int64_t window, double scale, double softcap,
+                   const c10::optional<at::Tensor>& status, const c10::optional<at::Tensor>& cos,
+                   const c10::optional<at::Tensor>& sin, const c10::optional<at::Tensor>& positions, int64_t rot_dim,
+                   bool interleaved) {
   c10::cuda::CUDAGuard guard(q.device());
   hb::AttnArgs a = make_args(q, k, v, seg_start, seg_end, seq_len, causal, window, scale, softcap, status);
   TORCH_CHECK(out.is_contiguous() && d_out.is_contiguous() && out.scalar_type() == at::kBFloat16 &&
@@ -92,15 +94,31 @@ at::Tensor attention_bwd(const at::Tensor& q, const at::Tensor& k, const at::Ten
               "out / d_out must be contiguous bf16 shaped like q");
   TORCH_CHECK(lse.is_contiguous() && lse.scalar_type() == at::kFloat && lse.numel() == (int64_t)a.n_heads * a.total,
               "lse must be fp32 [heads, tokens]");
-  TORCH_CHECK(dk.sizes() == k.sizes() && dv.sizes() == v.sizes(), "dk / dv must be shaped like k / v");
-  const int64_t dks = token_stride(dk, "dk"), dvs = token_stride(dv, "dv");
+  TORCH_CHECK(dq.sizes() == q.sizes() && dk.sizes() == k.sizes() && dv.sizes() == v.sizes(),
+              "dq / dk / dv must be shaped like q / k / v");
+  const int64_t dqs = token_stride(dq, "dq"), dks = token_stride(dk, "dk"), dvs = token_stride(dv, "dv");
+  hb::AttnDqRotation rot;
+  if (cos.has_value() && rot_dim > 0) {
+    TORCH_CHECK(sin.has_value() && positions.has_value(), "rotation needs cos, sin and positions");
+    TORCH_CHECK(cos->is_cuda() && cos->scalar_type() == at::kFloat && cos->is_contiguous() &&
+                    sin->scalar_type() == at::kFloat && sin->is_contiguous() && cos->size(-1) * 2 == rot_dim,
+                "cos / sin must be contiguous fp32 [max_position, rot_dim / 2]");
+    TORCH_CHECK(positions->is_cuda() && positions->is_contiguous() && positions->numel() == a.total &&
+                    (positions->scalar_type() == at::kLong || positions->scalar_type() == at::kInt),
+                "positions must be contiguous CUDA int32 / int64, one per token");
+    rot.cos = cos->data_ptr<float>();
+    rot.sin = sin->data_ptr<float>();
+    rot.positions = positions->data_ptr();
+    rot.pos_is_i64 = positions->scalar_type() == at::kLong;
+    rot.rot_dim = (int)rot_dim;
+    rot.interleaved = interleaved;
+  }
   at::Tensor delta = at::empty_like(lse);
   at::Tensor dq_accum = at::empty(q.sizes(), q.options().dtype(at::kFloat));
-  at::Tensor dq = at::empty(q.sizes(), q.options());
   HB_ATTN_OK(hb::attention_bwd(a, out.data_ptr(), d_out.data_ptr(), lse.data_ptr<float>(), delta.data_ptr<float>(),
-                               dq_accum.data_ptr<float>(), dq.data_ptr(), dk.data_ptr(), dks, dv.data_ptr(), dvs),
+                               dq_accum.data_ptr<float>(), dq.data_ptr(), dqs, rot, dk.data_ptr(), dks, dv.data_ptr(),
+                               dvs),
              3);
-  return dq;
 }
 
 // `table`: int64 [n, 14] on the device, rows laid out as hb::ReshardSegment
@@ -124,7 +142,9 @@ void register_attention(pybind11::module_& m) {
         py::arg("scale") = 1.0, py::arg("softcap") = 0.0, py::arg("status") = py::none());
   m.def("reshard_copy", &reshard_copy, py::arg("table"));
   m.def("attention_bwd", &attention_bwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"), py::arg("d_out"),
-        py::arg("lse"), py::arg("dk"), py::arg("dv"), py::arg("seg_start") = py::none(),
+        py::arg("lse"), py::arg("dq"), py::arg("dk"), py::arg("dv"), py::arg("seg_start") = py::none(),
         py::arg("seg_end") = py::none(), py::arg("seq_len") = 0, py::arg("causal") = true, py::arg("window") = 0,
-        py::arg("scale") = 1.0, py::arg("softcap") = 0.0, py::arg("status") = py::none());
+        py::arg("scale") = 1.0, py::arg("softcap") = 0.0, py::arg("status") = py::none(),
+        py::arg("cos") = py::none(), py::arg("sin") = py::none(), py::arg("positions") = py::none(),
+        py::arg("rot_dim") = 0, py::arg("interleaved") = true);
 }

@@ -9,7 +9,8 @@
 //   warp 0 (all lanes)  TMEM allocation (all 512 columns: S_0 S_1 O_0 O_1)
 //   warps 2-5 / 6-9     softmax of tile 0 / tile 1: one thread per query row, online softmax
 //                       with deferred rescaling (O_t is only rescaled when a row's maximum grew
-//                       by more than 2^8), P_t written back to TMEM with tcgen05.st
+//                       by more than 2^8), P_t written back to TMEM with tcgen05.st in two halves
+//                       so that O_t += P_t V_j starts on the first half
 // While one tile's rows are in the softmax, the tensor cores work on the other tile.
 //
 // Backward (`attn_bwd_kernel`): one CTA per 128 key/value rows of one KV head; it walks the query
@@ -57,14 +58,33 @@ struct AttnParams {
 };
 
 // ---------------------------------------------------------------- extra tcgen05 forms
-// D[tmem] (+)= A[tmem] * B[smem]: A is a 128-lane x K tile of packed bf16 pairs in tensor memory.
-__device__ __forceinline__ void umma_bf16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b,
-                                             uint32_t idesc, uint32_t accumulate) {
+// Shared-memory matrix descriptors, split in halves: every operand tile here uses the 128-byte
+// swizzle with 1024 bytes between 8-row groups, so the high word is one constant and the low word
+// is (address >> 4) | (bytes between 64-wide chunks >> 4) << 16. Stepping an operand along K adds
+// a constant to the low word, which keeps the issuing thread's instruction stream short.
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+  return ((saddr & 0x3ffffu) >> 4) | (((lbo_bytes >> 4) & 0x3fffu) << 16);
+}
+__device__ __forceinline__ void umma_ss(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                        uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
-      "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}" ::"r"(tmem_d),
+      "r"(a_lo), "r"(b_lo), "r"(kDescHi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(tmem_d),
+      "r"(tmem_a), "r"(b_lo), "r"(kDescHi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&v)[32]) {
@@ -162,7 +182,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   __shared__ __align__(8) uint64_t bar_kv_full[kStages];
   __shared__ __align__(8) uint64_t bar_kv_empty[kStages];
   __shared__ __align__(8) uint64_t bar_s_full[2];
-  __shared__ __align__(8) uint64_t bar_p_ready[2];
+  __shared__ __align__(8) uint64_t bar_p_ready[2][2];   // [tile][half]: one phase per key tile each, so the
+                                                        // softmax never runs two phases ahead of the waiter
   __shared__ __align__(8) uint64_t bar_o_full[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
@@ -221,7 +242,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     for (int t = 0; t < 2; ++t) {
       mbar_init(smem_u32(&bar_q_full[t]), 1);
       mbar_init(smem_u32(&bar_s_full[t]), 1);
-      mbar_init(smem_u32(&bar_p_ready[t]), 4);
+      mbar_init(smem_u32(&bar_p_ready[t][0]), 4);
+      mbar_init(smem_u32(&bar_p_ready[t][1]), 4);
       mbar_init(smem_u32(&bar_o_full[t]), 1);
     }
     for (int s = 0; s < kStages; ++s) {
@@ -275,20 +297,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     constexpr uint32_t idesc_qk = make_idesc_bf16(kTile, kTile, false, false);
     constexpr uint32_t idesc_pv = make_idesc_bf16(kTile, D, false, true);
     bool ok = true;
+    const uint32_t q_lo[2] = {desc_lo(q_smem[0], 0), desc_lo(q_smem[1], 0)};
     auto issue_s = [&](int t, uint32_t k_addr) {
+      const uint32_t k_lo = desc_lo(k_addr, 0);
 #pragma unroll
       for (int ks = 0; ks < D / 16; ++ks) {
-        const uint32_t off = (ks >> 2) * C::kChunkBytes + (ks & 3) * 32;
-        umma_bf16(tmem_base + t * kTile, make_smem_desc(q_smem[t] + off, 0, 1024),
-                  make_smem_desc(k_addr + off, 0, 1024), idesc_qk, ks != 0);
+        const uint32_t off = static_cast<uint32_t>(((ks >> 2) * C::kChunkBytes + (ks & 3) * 32) >> 4);
+        umma_ss(tmem_base + t * kTile, q_lo[t] + off, k_lo + off, idesc_qk, ks != 0);
       }
       umma_commit(smem_u32(&bar_s_full[t]));
     };
-    auto issue_pv = [&](int t, uint32_t v_addr, bool acc) {
+    // O_t += P_t V_j for one half of the key tile (P arrives in two halves of 64 keys, so the
+    // first product runs while the second half is still in the exponentials)
+    auto issue_pv = [&](int t, uint32_t v_addr, bool acc, int half) {
+      const uint32_t v_lo = desc_lo(v_addr, C::kChunkBytes);
 #pragma unroll
-      for (int ks = 0; ks < kTile / 16; ++ks)
-        umma_bf16_ta(tmem_base + C::kOCol + t * D, tmem_base + t * kTile + ks * 8,
-                     make_smem_desc(v_addr + ks * 2048, C::kChunkBytes, 1024), idesc_pv, acc || ks != 0);
+      for (int k4 = 0; k4 < kTile / 32; ++k4) {
+        const int ks = half * (kTile / 32) + k4;
+        umma_ts(tmem_base + C::kOCol + t * D, tmem_base + t * kTile + ks * 8,
+                v_lo + static_cast<uint32_t>((ks * 2048) >> 4), idesc_pv, acc || ks != 0);
+      }
     };
     auto wait_entry = [&](int e) -> bool {
       return mbar_wait(smem_u32(&bar_kv_full[e % kStages]), (e / kStages) & 1, &abort_flag, p.status,
@@ -315,11 +343,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       bool have_next = false;
       for (int t = 0; t < 2 && ok; ++t) {
         if (jb[t] <= j && j < je[t]) {
-          ok = mbar_wait(smem_u32(&bar_p_ready[t]), n_p[t] & 1, &abort_flag, p.status, kTimeoutTmemEmpty);
+          for (int half = 0; half < 2 && ok; ++half) {
+            ok = mbar_wait(smem_u32(&bar_p_ready[t][half]), n_p[t] & 1, &abort_flag, p.status, kTimeoutTmemEmpty);
+            if (!ok) break;
+            tc_fence_after();
+            issue_pv(t, entry_addr(e_v), j > jb[t], half);
+          }
           if (!ok) break;
           ++n_p[t];
-          tc_fence_after();
-          issue_pv(t, entry_addr(e_v), j > jb[t]);
           if (j == je[t] - 1) umma_commit(smem_u32(&bar_o_full[t]));
         }
         if (next && jb[t] <= j + 1 && j + 1 < je[t]) {
@@ -428,12 +459,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             pk[i] = pack_bf16x2(e0, e1);
           }
           tmem_st_32x16(s_addr + c * 16, pk);
+          if (c & 1) {
+            // one half of P (64 keys) is complete: hand it to the tensor cores
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_p_ready[t][c >> 1]));
+          }
         }
         l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-        tmem_st_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bar_p_ready[t]));
       }
       if (ok) {
         ok = mbar_wait(smem_u32(&bar_o_full[t]), 0, &abort_flag, p.status, kTimeoutTmemFull);
@@ -531,14 +565,84 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
   }
 }
 
-__global__ void attn_dq_convert_kernel(const float4* __restrict__ src, uint2* __restrict__ dst, long n4) {
-  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4;
-       i += static_cast<long>(gridDim.x) * blockDim.x) {
-    const float4 v = src[i];
-    uint2 o;
-    o.x = pack_bf16x2(v.x, v.y);
-    o.y = pack_bf16x2(v.z, v.w);
-    dst[i] = o;
+// Last pass over dQ: the fp32 accumulator becomes bf16, is rotated back (the inverse of the RoPE
+// that was applied to q in place, when tables are given) and lands at its place in the caller's
+// gradient tensor, whose tokens may be `dst_stride` elements apart (a slot of a packed qkv
+// gradient). One thread per 8 elements; the interleaved layout pairs neighbours, the half layout
+// pairs element i with i + rot_dim / 2.
+struct DqFinish {
+  const float* cos;
+  const float* sin;
+  const void* positions;
+  int pos_is_i64;
+  int rot_dim;          // 0: no rotation
+  int interleaved;
+};
+
+template <int D>
+__global__ void attn_dq_finish_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dst, long dst_stride,
+                                      int total, int heads, DqFinish f) {
+  constexpr int kVec = D / 8;
+  const long n = static_cast<long>(total) * heads * kVec;
+  const int half = f.rot_dim >> 1;
+  for (long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < n;
+       idx += static_cast<long>(gridDim.x) * blockDim.x) {
+    const int j = static_cast<int>(idx % kVec);
+    const long th = idx / kVec;
+    const int h = static_cast<int>(th % heads);
+    const long t = th / heads;
+    const float* a = acc + (t * heads + h) * D;
+    __nv_bfloat16* d = dst + t * dst_stride + h * D;
+    auto load8 = [&](int e0, float (&v)[8]) {
+      const float4 x = *reinterpret_cast<const float4*>(a + e0);
+      const float4 y = *reinterpret_cast<const float4*>(a + e0 + 4);
+      v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w; v[4] = y.x; v[5] = y.y; v[6] = y.z; v[7] = y.w;
+    };
+    auto store8 = [&](int e0, const float (&v)[8]) {
+      uint4 o;
+      o.x = pack_bf16x2(v[0], v[1]);
+      o.y = pack_bf16x2(v[2], v[3]);
+      o.z = pack_bf16x2(v[4], v[5]);
+      o.w = pack_bf16x2(v[6], v[7]);
+      *reinterpret_cast<uint4*>(d + e0) = o;
+    };
+    float v[8];
+    if (8 * j >= f.rot_dim) {
+      load8(8 * j, v);
+      store8(8 * j, v);
+      continue;
+    }
+    const long p = f.pos_is_i64 ? static_cast<long>(static_cast<const int64_t*>(f.positions)[t])
+                                : static_cast<long>(static_cast<const int32_t*>(f.positions)[t]);
+    if (f.interleaved) {
+      load8(8 * j, v);
+      const float4 c = *reinterpret_cast<const float4*>(f.cos + p * half + 4 * j);
+      const float4 sn = *reinterpret_cast<const float4*>(f.sin + p * half + 4 * j);
+      const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+      float o[8];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        o[2 * k] = v[2 * k] * cc[k] + v[2 * k + 1] * ss[k];
+        o[2 * k + 1] = v[2 * k + 1] * cc[k] - v[2 * k] * ss[k];
+      }
+      store8(8 * j, o);
+    } else {
+      if (8 * j >= half) continue;            // written by the thread that owns the first half
+      float hi[8], cc[8], ss[8], olo[8], ohi[8];
+      load8(8 * j, v);
+      load8(8 * j + half, hi);
+      *reinterpret_cast<float4*>(cc) = *reinterpret_cast<const float4*>(f.cos + p * half + 8 * j);
+      *reinterpret_cast<float4*>(cc + 4) = *reinterpret_cast<const float4*>(f.cos + p * half + 8 * j + 4);
+      *reinterpret_cast<float4*>(ss) = *reinterpret_cast<const float4*>(f.sin + p * half + 8 * j);
+      *reinterpret_cast<float4*>(ss + 4) = *reinterpret_cast<const float4*>(f.sin + p * half + 8 * j + 4);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        olo[k] = v[k] * cc[k] + hi[k] * ss[k];
+        ohi[k] = hi[k] * cc[k] - v[k] * ss[k];
+      }
+      store8(8 * j, olo);
+      store8(8 * j + half, ohi);
+    }
   }
 }
 
@@ -671,18 +775,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     constexpr uint32_t idesc_acc = make_idesc_bf16(kTile, D, false, true);       // dV, dK
     constexpr uint32_t idesc_dq = make_idesc_bf16(kTile, D, true, true);         // dQ
     bool ok = mbar_wait(smem_u32(&bar_kv_full), 0, &abort_flag, p.status, kTimeoutFull);
+    const uint32_t k_lo = desc_lo(k_smem, 0), v_lo = desc_lo(v_smem, 0);
+    const uint32_t k_mn_lo = desc_lo(k_smem, C::kChunkBytes), ds_lo = desc_lo(ds_smem, 0),
+                   ds_mn_lo = desc_lo(ds_smem, C::kChunkBytes);
     auto issue_s = [&](int it) -> bool {
       const int e_q = 2 * it;
       if (!mbar_wait(smem_u32(&bar_ring_full[e_q % C::kRing]), (e_q / C::kRing) & 1, &abort_flag, p.status,
                      kTimeoutFull))
         return false;
       tc_fence_after();
-      const uint32_t q_addr = ring + (e_q % C::kRing) * C::kTileBytes;
+      const uint32_t q_lo = desc_lo(ring + (e_q % C::kRing) * C::kTileBytes, 0);
 #pragma unroll
       for (int ks = 0; ks < D / 16; ++ks) {
-        const uint32_t off = (ks >> 2) * C::kChunkBytes + (ks & 3) * 32;
-        umma_bf16(tmem_base, make_smem_desc(k_smem + off, 0, 1024), make_smem_desc(q_addr + off, 0, 1024),
-                  idesc_kk, ks != 0);
+        const uint32_t off = static_cast<uint32_t>(((ks >> 2) * C::kChunkBytes + (ks & 3) * 32) >> 4);
+        umma_ss(tmem_base, k_lo + off, q_lo + off, idesc_kk, ks != 0);
       }
       umma_commit(smem_u32(&bar_s_full));
       return true;
@@ -700,11 +806,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         ok = mbar_wait(smem_u32(&bar_dq_free), (it - 1) & 1, &abort_flag, p.status, kTimeoutTmemEmpty);
       if (!ok) break;
       tc_fence_after();
+      const uint32_t o_lo = desc_lo(o_addr, 0), o_mn_lo = desc_lo(o_addr, C::kChunkBytes);
+      const uint32_t q_mn_lo = desc_lo(q_addr, C::kChunkBytes);
 #pragma unroll
       for (int ks = 0; ks < D / 16; ++ks) {
-        const uint32_t off = (ks >> 2) * C::kChunkBytes + (ks & 3) * 32;
-        umma_bf16(tmem_base + C::kDpCol, make_smem_desc(v_smem + off, 0, 1024),
-                  make_smem_desc(o_addr + off, 0, 1024), idesc_kk, ks != 0);
+        const uint32_t off = static_cast<uint32_t>(((ks >> 2) * C::kChunkBytes + (ks & 3) * 32) >> 4);
+        umma_ss(tmem_base + C::kDpCol, v_lo + off, o_lo + off, idesc_kk, ks != 0);
       }
       umma_commit(smem_u32(&bar_dp_full));
       // dV += P^T dO
@@ -713,8 +820,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tc_fence_after();
 #pragma unroll
       for (int ks = 0; ks < kTile / 16; ++ks)
-        umma_bf16_ta(tmem_base + C::kDvCol, tmem_base + C::kPCol + ks * 8,
-                     make_smem_desc(o_addr + ks * 2048, C::kChunkBytes, 1024), idesc_acc, it > 0 || ks != 0);
+        umma_ts(tmem_base + C::kDvCol, tmem_base + C::kPCol + ks * 8, o_mn_lo + static_cast<uint32_t>((ks * 2048) >> 4),
+                idesc_acc, it > 0 || ks != 0);
       umma_commit(smem_u32(&bar_ring_empty[e_o % C::kRing]));
       // S^T of the next tile, over the P that dV has just been issued on (the tensor cores run
       // one CTA's instructions in issue order)
@@ -728,14 +835,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tc_fence_after();
 #pragma unroll
       for (int ks = 0; ks < kTile / 16; ++ks) {
-        const uint32_t a_off = (ks >> 2) * C::kChunkBytes + (ks & 3) * 32;
-        umma_bf16(tmem_base + C::kDkCol, make_smem_desc(ds_smem + a_off, 0, 1024),
-                  make_smem_desc(q_addr + ks * 2048, C::kChunkBytes, 1024), idesc_acc, it > 0 || ks != 0);
+        const uint32_t a_off = static_cast<uint32_t>(((ks >> 2) * C::kChunkBytes + (ks & 3) * 32) >> 4);
+        umma_ss(tmem_base + C::kDkCol, ds_lo + a_off, q_mn_lo + static_cast<uint32_t>((ks * 2048) >> 4), idesc_acc,
+                it > 0 || ks != 0);
       }
 #pragma unroll
       for (int ks = 0; ks < kTile / 16; ++ks)
-        umma_bf16(tmem_base + C::kDpCol, make_smem_desc(ds_smem + ks * 2048, C::kChunkBytes, 1024),
-                  make_smem_desc(k_smem + ks * 2048, C::kChunkBytes, 1024), idesc_dq, ks != 0);
+        umma_ss(tmem_base + C::kDpCol, ds_mn_lo + static_cast<uint32_t>((ks * 2048) >> 4),
+                k_mn_lo + static_cast<uint32_t>((ks * 2048) >> 4), idesc_dq, ks != 0);
       umma_commit(smem_u32(&bar_dq_full));
       umma_commit(smem_u32(&bar_ring_empty[e_q % C::kRing]));
     }
@@ -1144,7 +1251,8 @@ cudaError_t launch_fwd(const AttnArgs& a, void* out, float* lse) {
 
 template <int D, bool SC>
 cudaError_t launch_bwd(const AttnArgs& a, const void* o, const void* d_o, const float* lse, float* delta,
-                       float* dq_accum, void* dq, void* dk, long dk_stride, void* dv, long dv_stride) {
+                       float* dq_accum, void* dq, long dq_stride, const AttnDqRotation& rot, void* dk, long dk_stride,
+                       void* dv, long dv_stride) {
   using C = BwdCfg<D>;
   CUtensorMap tq, tk, tv, tdo, tdq;
   if (!make_tmap_heads(&tq, a.q, a.total, a.n_heads, D, a.q_tok_stride) ||
@@ -1180,10 +1288,17 @@ cudaError_t launch_bwd(const AttnArgs& a, const void* o, const void* d_o, const 
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   {
-    const long n4 = static_cast<long>(n / 4);
-    const int grid = static_cast<int>(std::min<long>((n4 + 255) / 256, 148L * 16));
-    attn_dq_convert_kernel<<<grid, 256, 0, a.stream>>>(reinterpret_cast<const float4*>(dq_accum),
-                                                       reinterpret_cast<uint2*>(dq), n4);
+    DqFinish f;
+    f.cos = rot.cos;
+    f.sin = rot.sin;
+    f.positions = rot.positions;
+    f.pos_is_i64 = rot.pos_is_i64 ? 1 : 0;
+    f.rot_dim = (rot.cos && rot.sin && rot.positions) ? rot.rot_dim : 0;
+    f.interleaved = rot.interleaved ? 1 : 0;
+    const long nvec = static_cast<long>(n / 8);
+    const int grid = static_cast<int>(std::min<long>((nvec + 255) / 256, 148L * 16));
+    attn_dq_finish_kernel<D><<<grid, 256, 0, a.stream>>>(dq_accum, static_cast<__nv_bfloat16*>(dq), dq_stride, a.total,
+                                                         a.n_heads, f);
     e = cudaGetLastError();
   }
   return e;
@@ -1200,16 +1315,19 @@ cudaError_t attention_fwd(const AttnArgs& a, void* out, float* lse) {
 }
 
 cudaError_t attention_bwd(const AttnArgs& a, const void* o, const void* d_o, const float* lse, float* delta,
-                          float* dq_accum, void* dq, void* dk, long dk_tok_stride, void* dv, long dv_tok_stride) {
+                          float* dq_accum, void* dq, long dq_tok_stride, const AttnDqRotation& rot, void* dk,
+                          long dk_tok_stride, void* dv, long dv_tok_stride) {
   cudaError_t e = check_args(a);
   if (e != cudaSuccess || a.total <= 0) return e;
-  if (dk_tok_stride % 8 || dv_tok_stride % 8) return cudaErrorInvalidValue;
+  if (dk_tok_stride % 8 || dv_tok_stride % 8 || dq_tok_stride % 8) return cudaErrorInvalidValue;
+  if (rot.cos && (rot.rot_dim <= 0 || rot.rot_dim > a.head_dim || rot.rot_dim % (rot.interleaved ? 8 : 16)))
+    return cudaErrorInvalidValue;
   const bool sc = a.softcap > 0.f;
-  if (a.head_dim == 128)
-    return sc ? launch_bwd<128, true>(a, o, d_o, lse, delta, dq_accum, dq, dk, dk_tok_stride, dv, dv_tok_stride)
-              : launch_bwd<128, false>(a, o, d_o, lse, delta, dq_accum, dq, dk, dk_tok_stride, dv, dv_tok_stride);
-  return sc ? launch_bwd<64, true>(a, o, d_o, lse, delta, dq_accum, dq, dk, dk_tok_stride, dv, dv_tok_stride)
-            : launch_bwd<64, false>(a, o, d_o, lse, delta, dq_accum, dq, dk, dk_tok_stride, dv, dv_tok_stride);
+#define HB_ATTN_BWD(DD, SS) \
+  launch_bwd<DD, SS>(a, o, d_o, lse, delta, dq_accum, dq, dq_tok_stride, rot, dk, dk_tok_stride, dv, dv_tok_stride)
+  if (a.head_dim == 128) return sc ? HB_ATTN_BWD(128, true) : HB_ATTN_BWD(128, false);
+  return sc ? HB_ATTN_BWD(64, true) : HB_ATTN_BWD(64, false);
+#undef HB_ATTN_BWD
 }
 
 }  // namespace hb

@@ -150,10 +150,11 @@ class _AttentionFn(torch.autograd.Function):
         C = ops.ext()
         q, k, v, out, lse, seg_start, seg_end = ctx.saved_tensors
         seq_len, causal, window, scale, softcap = ctx.cfg
+        dq = torch.empty(q.shape, device=q.device, dtype=q.dtype)
         dk = torch.empty(k.shape, device=k.device, dtype=k.dtype)
         dv = torch.empty(v.shape, device=v.device, dtype=v.dtype)
-        dq = C.attention_bwd(q, k, v, out, dout.contiguous(), lse, dk, dv, seg_start, seg_end, seq_len, causal,
-                             window, scale, softcap, ops.status_word(q.device))
+        C.attention_bwd(q, k, v, out, dout.contiguous(), lse, dq, dk, dv, seg_start, seg_end, seq_len, causal,
+                        window, scale, softcap, ops.status_word(q.device))
         return dq, dk, dv, None, None, None, None, None, None, None
 
 
@@ -271,12 +272,18 @@ class _PackedQKVAttention(torch.autograd.Function):
         gv = dqkv[..., qd + kd:].unflatten(-1, (Hk, D))
         cos, sin, pos, interleaved = ctx.rope
         rot = cos.shape[-1] * 2 if cos is not None else 0
-        # dV lands in its slot of the packed gradient; dK goes there directly when nothing has to
-        # be rotated back, else through the inverse rotation like dQ
+        # dQ and dV land in their slots of the packed gradient straight from the kernels (dQ is
+        # rotated back on its way out of the fp32 accumulator); dK goes there directly when nothing
+        # has to be rotated, else through one inverse-rotation pass
+        vec_ok = rot == 0 or rot % (8 if interleaved else 16) == 0
         dk = gk if rot == 0 else torch.empty(B, S, Hk, D, device=qkv.device, dtype=qkv.dtype)
-        dq = C.attention_bwd(q, k, v, out, dout.reshape(B, S, H, D).contiguous(), lse, dk, gv, None, None, S,
-                             causal, 0, scale, 0.0, ops.status_word(qkv.device))
-        C.rope_copy(dq, gq, cos if rot else None, sin if rot else None, pos if rot else None, rot, interleaved, True)
+        dq = gq if vec_ok else torch.empty(B, S, H, D, device=qkv.device, dtype=qkv.dtype)
+        C.attention_bwd(q, k, v, out, dout.reshape(B, S, H, D).contiguous(), lse, dq, dk, gv, None, None, S,
+                        causal, 0, scale, 0.0, ops.status_word(qkv.device),
+                        cos if rot and vec_ok else None, sin if rot and vec_ok else None,
+                        pos if rot and vec_ok else None, rot if vec_ok else 0, interleaved)
+        if not vec_ok:
+            C.rope_copy(dq, gq, cos, sin, pos, rot, interleaved, True)
         if rot:
             C.rope_copy(dk, gk, cos, sin, pos, rot, interleaved, True)
         return dqkv, None, None, None, None, None, None, None, None, None
