@@ -260,9 +260,11 @@ def run_ours(args):
     gather_mode = "none (one rank)" if world == 1 else "NCCL all-gather per unit, overlapped"
     if fused_units:
         carried = sum(u.fused.launches - u.fused.standalone for u in fused_units)
+        heap = getattr(model._hb_fsdp, "reduce_heap", None)
+        nvls = "yes" if heap is not None and heap.multicast_ptr and os.environ.get("HB_FSDP_NVLS", "1") != "0" else "no"
         gather_mode = (f"{len(fused_units)} block units: peers' shards copied over NVLink by CTAs inside GEMM launches "
                        f"({carried} carried, {sum(u.fused.standalone for u in fused_units)} launched alone so far); "
-                       "root unit: NCCL")
+                       f"gradient reduction through NVLS multimem: {nvls}; root and head units: NCCL")
     tokens_per_step = seqs * S * world
     value = tokens_per_step * K / (ms / 1e3)
     e2e = tokens_per_step * K / (e2e_ms / 1e3)

@@ -58,6 +58,7 @@ bool fill_gather(const c10::optional<py::dict>& d, hb::GatherParams& gp) {
     gp.reduce_out = reinterpret_cast<float*>(g["reduce_out_ptr"].cast<int64_t>());
     gp.reduce_numel = g["reduce_numel"].cast<int64_t>();
     gp.reduce_scale = g["reduce_scale"].cast<float>();
+    if (g.contains("mc_src_ptr")) gp.mc_src = reinterpret_cast<const float*>(g["mc_src_ptr"].cast<int64_t>());
   }
   return true;
 }

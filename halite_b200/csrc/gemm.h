@@ -45,6 +45,10 @@ struct GatherParams {
   float* reduce_out = nullptr;
   long reduce_numel = 0;
   float reduce_scale = 1.f;
+  // Reduce mode through the switch: when the buffers are bound to an NVLink multicast object,
+  // `mc_src` is the multicast address of this rank's range; one `multimem.ld_reduce` per 16 bytes
+  // then returns the sum over all ranks (added inside NVSwitch) instead of one load per rank.
+  const float* mc_src = nullptr;
 };
 
 // Fused GEMM -> reduce-scatter over the M dimension. Output rows are split into `n_chunks`

@@ -259,7 +259,33 @@ __device__ __forceinline__ void reduce_copy_cta(const GatherParams& gp, int cta,
       if (gp.ready && c != gp.first_chunk && !wait_flag(gp.ready + c, gp.epoch, true, abort_flag, status)) s_ok = 0;
   }
   __syncthreads();
-  if (s_ok) {
+  if (s_ok && gp.mc_src != nullptr) {
+    // in-switch reduction: one multimem load per 16 bytes brings back the sum over all ranks
+    const long n4 = gp.reduce_numel >> 2;
+    float4* out = reinterpret_cast<float4*>(gp.reduce_out);
+    const float4* src = reinterpret_cast<const float4*>(gp.mc_src);
+    const long stride = static_cast<long>(gp.n_copy_ctas) * blockDim.x;
+    constexpr int kUnroll = 4;
+    for (long base = static_cast<long>(cta) * blockDim.x + threadIdx.x; base < n4; base += stride * kUnroll) {
+      float4 v[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const long i = base + u * stride;
+        if (i < n4)
+          asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=f"(v[u].x), "=f"(v[u].y), "=f"(v[u].z), "=f"(v[u].w)
+                       : "l"(src + i)
+                       : "memory");
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const long i = base + u * stride;
+        if (i < n4)
+          out[i] = make_float4(v[u].x * gp.reduce_scale, v[u].y * gp.reduce_scale, v[u].z * gp.reduce_scale,
+                               v[u].w * gp.reduce_scale);
+      }
+    }
+  } else if (s_ok) {
     const long n4 = gp.reduce_numel >> 2;
     float4* out = reinterpret_cast<float4*>(gp.reduce_out);
     const long stride = static_cast<long>(gp.n_copy_ctas) * blockDim.x;

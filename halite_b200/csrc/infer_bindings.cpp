@@ -89,7 +89,8 @@ void kv_append(at::Tensor& k_cache, at::Tensor& v_cache, const at::Tensor& k, co
 
 void paged_decode(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache,
                   at::Tensor& out, const at::Tensor& page_table, const at::Tensor& req_slots,
-                  const at::Tensor& seq_lens, const c10::optional<at::Tensor>& workspace, double scale) {
+                  const at::Tensor& seq_lens, const c10::optional<at::Tensor>& workspace, double scale,
+                  const c10::optional<at::Tensor>& status) {
   check_heads(q, "q");
   check_cache(k_cache, "k_cache");
   check_cache(v_cache, "v_cache");
@@ -115,6 +116,7 @@ void paged_decode(const at::Tensor& q, const at::Tensor& k_cache, const at::Tens
   a.q_stride = q.stride(0);
   a.num_pages = k_cache.size(0);
   a.scale = (float)scale;
+  if (status.has_value()) a.status = status->data_ptr<int>();
   a.splits = hb::paged_decode_splits(a.batch, a.hk,
                                      at::cuda::getCurrentDeviceProperties()->multiProcessorCount);
   if (a.splits > 1) {
@@ -140,7 +142,7 @@ void paged_decode(const at::Tensor& q, const at::Tensor& k_cache, const at::Tens
 void paged_prefill(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache,
                    at::Tensor& out, const at::Tensor& page_table, const at::Tensor& req_slots,
                    const at::Tensor& qo_indptr, const at::Tensor& seq_lens, int64_t max_extend,
-                   double scale) {
+                   double scale, const c10::optional<at::Tensor>& status) {
   check_heads(q, "q");
   check_heads(out, "out");
   check_cache(k_cache, "k_cache");
@@ -170,6 +172,7 @@ void paged_prefill(const at::Tensor& q, const at::Tensor& k_cache, const at::Ten
   a.o_stride = out.stride(0);
   a.num_pages = k_cache.size(0);
   a.scale = (float)scale;
+  if (status.has_value()) a.status = status->data_ptr<int>();
   HB_CUDA_OK(hb::paged_prefill(a, cur_stream()));
 }
 
@@ -201,7 +204,9 @@ void register_infer(pybind11::module_& m) {
   m.def("kv_append", &kv_append);
   m.def("paged_decode", &paged_decode, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"),
         py::arg("out"), py::arg("page_table"), py::arg("req_slots"), py::arg("seq_lens"),
-        py::arg("workspace"), py::arg("scale"));
-  m.def("paged_prefill", &paged_prefill);
+        py::arg("workspace"), py::arg("scale"), py::arg("status") = py::none());
+  m.def("paged_prefill", &paged_prefill, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"), py::arg("out"),
+        py::arg("page_table"), py::arg("req_slots"), py::arg("qo_indptr"), py::arg("seq_lens"), py::arg("max_extend"),
+        py::arg("scale"), py::arg("status") = py::none());
   m.def("sample_gumbel", &sample_gumbel);
 }

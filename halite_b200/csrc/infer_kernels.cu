@@ -120,6 +120,7 @@ struct DecodeSmem {
 };
 
 constexpr int kDecodeThreads = 256;
+constexpr int kBadPageId = 8;      // status code: a page table entry named a page outside the pool
 
 template <int D, int G>
 __global__ void __launch_bounds__(kDecodeThreads)
@@ -127,7 +128,8 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
                     const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ page_table,
                     const int* __restrict__ req_slots, const int* __restrict__ seq_lens,
                     float* __restrict__ ws, __nv_bfloat16* __restrict__ out, int hq, int hk,
-                    int max_pages, int splits, long q_stride, float scale_log2, long num_pages) {
+                    int max_pages, int splits, long q_stride, float scale_log2, long num_pages,
+                    int* __restrict__ status) {
   using S = DecodeSmem<D>;
   constexpr int TILE = S::kTile;
   constexpr int ROW = S::kRow;
@@ -171,8 +173,13 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       long slot = 0;
       if (valid) {
         const int pi = t >> 4;
-        int pg = pi < max_pages ? pt[pi] : 0;
-        if (pg < 0 || pg >= num_pages) pg = 0;
+        int pg = pi < max_pages ? pt[pi] : -1;
+        if (pg < 0 || pg >= num_pages) {
+          // a page id outside the pool: read the scratch page (the access stays in bounds) and
+          // report it through the status word, the way every bounded wait reports a failure
+          if (status) atomicCAS(status, 0, kBadPageId);
+          pg = 0;
+        }
         slot = static_cast<long>(pg) * kPage + (t & 15);
       }
       const long off = (slot * hk + kh) * D + ch * 8;
@@ -414,7 +421,7 @@ paged_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
                      const int* __restrict__ page_table, const int* __restrict__ req_slots,
                      const int* __restrict__ qo_indptr, const int* __restrict__ seq_lens, int hq,
                      int hk, int max_pages, int q_tiles, long q_stride, long o_stride,
-                     float scale_log2, long num_pages) {
+                     float scale_log2, long num_pages, int* __restrict__ status) {
   constexpr int BM = 64, BN = 64, CH = D / 8;  // CH: 16-byte chunks per row
   extern __shared__ __align__(16) uint8_t smem[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem);
@@ -462,8 +469,11 @@ paged_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
       const int r = i / CH, c = i % CH;
       const int t = n0 + r;
       const bool ok = t < seq;
-      int pg = ok ? pt[t >> 4] : 0;
-      if (pg < 0 || pg >= num_pages) pg = 0;
+      int pg = ok ? ((t >> 4) < max_pages ? pt[t >> 4] : -1) : 0;
+      if (pg < 0 || pg >= num_pages) {
+        if (status) atomicCAS(status, 0, kBadPageId);      // reported, and read from the scratch page
+        pg = 0;
+      }
       const long slot = static_cast<long>(pg) * kPage + (t & 15);
       const long off = (slot * hk + kh) * D + c * 8;
       cp_async16(sKa + (r * CH + (c ^ (r & 7))) * 16, k_cache + off, ok);
@@ -704,7 +714,7 @@ static cudaError_t launch_decode(const PagedDecodeArgs& a, cudaStream_t stream) 
       static_cast<const __nv_bfloat16*>(a.q), static_cast<const __nv_bfloat16*>(a.k_cache),
       static_cast<const __nv_bfloat16*>(a.v_cache), a.page_table, a.req_slots, a.seq_lens, a.workspace,
       static_cast<__nv_bfloat16*>(a.out), a.hq, a.hk, a.max_pages, a.splits, a.q_stride,
-      a.scale * 1.4426950408889634f, a.num_pages);
+      a.scale * 1.4426950408889634f, a.num_pages, a.status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess || a.splits == 1) return e;
   decode_merge_kernel<D><<<a.batch * a.hq, D, 0, stream>>>(a.workspace, static_cast<__nv_bfloat16*>(a.out), a.splits);
@@ -744,11 +754,11 @@ cudaError_t paged_prefill(const PagedPrefillArgs& a, cudaStream_t stream) {
     }
     paged_prefill_kernel<128><<<grid, 128, smem, stream>>>(Q, K, V, O, a.page_table, a.req_slots, a.qo_indptr,
                                                            a.seq_lens, a.hq, a.hk, a.max_pages, q_tiles,
-                                                           a.q_stride, a.o_stride, sl2, a.num_pages);
+                                                           a.q_stride, a.o_stride, sl2, a.num_pages, a.status);
   } else {
     paged_prefill_kernel<64><<<grid, 128, smem, stream>>>(Q, K, V, O, a.page_table, a.req_slots, a.qo_indptr,
                                                           a.seq_lens, a.hq, a.hk, a.max_pages, q_tiles,
-                                                          a.q_stride, a.o_stride, sl2, a.num_pages);
+                                                          a.q_stride, a.o_stride, sl2, a.num_pages, a.status);
   }
   return cudaGetLastError();
 }

@@ -36,6 +36,7 @@ struct PagedDecodeArgs {
   int batch = 0, hq = 0, hk = 0, dim = 0, max_pages = 0, splits = 1;
   long q_stride = 0, num_pages = 0;
   float scale = 1.f;
+  int* status = nullptr;        // device int: set to 8 when a page id lies outside the pool
 };
 cudaError_t paged_decode(const PagedDecodeArgs& a, cudaStream_t stream);
 int paged_decode_splits(int batch, int hk, int sm_count);
@@ -51,6 +52,7 @@ struct PagedPrefillArgs {
   const int* seq_lens = nullptr;    // [batch] keys per request (prefix + new)
   int batch = 0, hq = 0, hk = 0, dim = 0, max_pages = 0, max_extend = 0;
   long q_stride = 0, o_stride = 0, num_pages = 0;
+  int* status = nullptr;            // device int: set to 8 when a page id lies outside the pool
   float scale = 1.f;
 };
 cudaError_t paged_prefill(const PagedPrefillArgs& a, cudaStream_t stream);

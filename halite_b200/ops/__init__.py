@@ -59,7 +59,8 @@ def check_status(device=None):
         code = int(t.item())
         if code != 0:
             t.zero_()
-            raise RuntimeError(f"halite_b200 kernel on cuda:{key} gave up a bounded wait (code {code})")
+            what = "read a page id outside the KV pool" if code == 8 else "gave up a bounded wait"
+            raise RuntimeError(f"halite_b200 kernel on cuda:{key} {what} (code {code})")
 
 
 from .linear import linear, gemm, matmul_nt  # noqa: E402

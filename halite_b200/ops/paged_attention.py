@@ -81,7 +81,7 @@ def paged_prefill_attention(q, k_cache, v_cache, fb, scale=None, softcap=0.0, wi
             q = q.contiguous()
         out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
         ops.ext().paged_prefill(q, k_cache, v_cache, out, fb.page_table, fb.req_slots, fb.qo_indptr,
-                                fb.seq_lens, fb.max_extend_len, float(scale))
+                                fb.seq_lens, fb.max_extend_len, float(scale), ops.status_word(q.device))
         return out
     return paged_attention_reference(q, k_cache, v_cache, fb, scale, softcap, window)
 
@@ -94,6 +94,6 @@ def paged_decode_attention(q, k_cache, v_cache, fb, scale=None, softcap=0.0, win
             q = q.contiguous()
         out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
         ops.ext().paged_decode(q, k_cache, v_cache, out, fb.page_table, fb.req_slots, fb.seq_lens,
-                               workspace, float(scale))
+                               workspace, float(scale), ops.status_word(q.device))
         return out
     return paged_attention_reference(q, k_cache, v_cache, fb, scale, softcap, window)

@@ -521,17 +521,23 @@ class FusedGather:
 class FusedReduce:
     """Reduce-scatter of one unit's fp32 gradients carried by a GEMM launch of the backward pass:
     a few CTAs of that launch read this rank's range out of every rank's symmetric-memory
-    `full_grad` with plain loads over NVLink, add the ranks in rank order, scale by 1 / ranks and
-    write the rank's `grad_shard`, while the other CTAs compute. Flags as in `FusedGather`:
+    `full_grad` over NVLink (one `multimem.ld_reduce` per 16 bytes when the heap has an NVLS
+    multicast mapping: the switch adds the ranks' copies; else one plain load per rank, added in
+    rank order), scale by 1 / ranks and write the rank's `grad_shard`, while the other CTAs compute. Flags as in `FusedGather`:
     `ready[owner]` = epoch once a rank's gradients of the unit are complete, `done[reader]` =
     epoch once a rank has read everybody's range (the buffer may be overwritten after that)."""
 
     COPY_CTAS = 32
 
     def __init__(self, unit, heap, offset, f_ready, f_done):
+        import os
+
         self.unit, self.heap, self.offset = unit, heap, offset
         self.f_ready, self.f_done = f_ready, f_done
         self.counter = torch.zeros(1, dtype=torch.int32, device=unit.device)
+        # HB_FSDP_NVLS=0 keeps the plain peer loads (needed where a rank may leave while its memory
+        # is bound to the multicast object, and on switches without in-network reduction)
+        self.use_multimem = os.environ.get("HB_FSDP_NVLS", "1") != "0"
         self.epoch = 0
         self.pending = 0
         self.launches = 0
@@ -562,7 +568,14 @@ class FusedReduce:
         u, h = self.unit, self.heap
         self.launches += 1
         mine = self.offset + u.lo * 4      # this rank's range inside every rank's fp32 buffer
+        extra = {}
+        if h.multicast_ptr and self.use_multimem:
+            # the heap is bound to an NVLink multicast object: the switch adds the ranks' copies
+            from halite_b200.parallel.symm import _FLAG_BYTES
+
+            extra["mc_src_ptr"] = h.multicast_ptr + _FLAG_BYTES + mine
         return dict(
+            **extra,
             src_ptrs=[h.data_ptr(c, mine) for c in range(u.ws)],
             peer_done_ptrs=[0 if c == u.rank else h.flag_ptr(c, self.f_done + u.rank) for c in range(u.ws)],
             dst_ptr=0, chunk_bytes=16, granule_bytes=16, n_copy_ctas=self.COPY_CTAS, flags_ptr=0,

@@ -232,3 +232,26 @@ def test_tokainfer_engine_gpu_matches_dense(zoo):
         assert len(r.output_ids[0]) == 24
     assert worst < 0.15, worst
     eng.manager.allocator.sanity_checks(set())
+
+
+def test_page_id_outside_the_pool_raises_the_status_word():
+    """A corrupted page table entry is not silently served from page 0: the kernel still reads
+    in bounds, and the status word makes the next `check_status()` raise."""
+    import halite_b200.ops as ops
+
+    C = ops.ext()
+    ops.check_status()
+    pages, hk, hq, D = 8, 2, 4, 128
+    k_cache = torch.randn(pages, 16, hk, D, device="cuda").bfloat16()
+    v_cache = torch.randn(pages, 16, hk, D, device="cuda").bfloat16()
+    q = torch.randn(1, hq, D, device="cuda").bfloat16()
+    out = torch.empty_like(q)
+    table = torch.tensor([[1, 99, 3, 0]], dtype=torch.int32, device="cuda")       # 99: no such page
+    slots = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lens = torch.tensor([40], dtype=torch.int32, device="cuda")
+    C.paged_decode(q, k_cache, v_cache, out, table, slots, lens, None, 0.1, ops.status_word("cuda"))
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="page id"):
+        ops.check_status()
+    ops.check_status()          # cleared by the report
+    assert torch.isfinite(out.float()).all()
