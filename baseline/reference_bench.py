@@ -31,6 +31,27 @@ def _unavailable(reason: str):
         print(json.dumps({"impl": "reference", "unavailable": reason.replace("\n", " ")[:300]}), flush=True)
 
 
+def _model_config(name):
+    """Path of the reference config file for `name`. The reference ships only the 3B file; the 8B one is
+    that same file with the dimensions of Llama-3-8B substituted (written next to it so that its relative
+    imports resolve), so the model is still built by the reference's own config code."""
+    src = os.path.join(REF, "configs/models/llama/llama3_2_3b.py")
+    if name == "llama-3.2-3b":
+        return src
+    text = open(src).read()
+    for old, new in (("dim = 3072", "dim = 4096"), ("n_heads = 24", "n_heads = 32"), ("n_layers=28", "n_layers=32"),
+                     ("intermediate_size=8192", "intermediate_size=14336")):
+        if old not in text:
+            raise RuntimeError(f"the reference's 3B config no longer contains {old!r}")
+        text = text.replace(old, new)
+    dst = os.path.join(REF, "configs/models/llama/llama3_8b.py")
+    tmp = f"{dst}.{os.getpid()}.tmp"
+    with open(tmp, "w") as f:
+        f.write(text)
+    os.replace(tmp, dst)
+    return dst
+
+
 def run(args):
     if not os.path.isdir(os.path.join(REF, "halite")):
         _unavailable("baseline/_ref/halite is missing (the reference was not installed with pip --target baseline/_ref)")
@@ -76,15 +97,29 @@ def _run(args):
     from halite.parallel.fsdp import apply_fsdp
     from halite.transformers.parallelize import apply_compile
 
-    conf = load_config(os.path.join(REF, "configs/models/llama/llama3_2_3b.py"))
-    pdims = ParallelDims(dp_replicate=1, dp_shard=-1, tp=1, pp=1)
+    tp = getattr(args, "tp", 1) or 1
+    M = getattr(args, "micro_batches", 1) or 1
+    model_name = getattr(args, "model", "llama-3.2-3b")
+    conf = load_config(_model_config(model_name))
+    pdims = ParallelDims(dp_replicate=1, dp_shard=-1, tp=tp, pp=1)
     mesh = pdims.build_mesh("cuda")
+    dp = world // tp
+    dp_rank = rank // tp
 
     torch.manual_seed(0)
     with torch.device("meta"):
         model = instantiate(conf.model)
-    if world > 1:
+    if args.layers:
+        for key in list(model.blocks._modules)[args.layers:]:
+            del model.blocks._modules[key]
+    if dp > 1:
         model = instantiate(conf.parallelize)(model=model, mesh=mesh, parallel_dims=pdims)
+    elif tp > 1:
+        # one data-parallel rank: the reference's parallelize() would skip sharding (and with it bf16
+        # parameters), so force its FSDP wrapper on the one-rank dp mesh as the one-GPU run does
+        model = instantiate(conf.parallelize)(model=model, mesh=mesh, parallel_dims=pdims, force_fsdp=True)
+        if not any(type(m).__name__.startswith("FSDP") for m in model.modules()):
+            apply_fsdp(model, mesh["dp"], "bfloat16", "float32", True)
     else:
         apply_compile(model, None)
         apply_fsdp(model, mesh["dp"], "bfloat16", "float32", True)
@@ -102,18 +137,28 @@ def _run(args):
     model.train()
 
     seqs, S, W, K = args.seqs_per_gpu, args.seq_len, args.warmup, args.steps
-    g = torch.Generator().manual_seed(1234 + rank)
+    g = torch.Generator().manual_seed(1234 + (dp_rank if tp > 1 else rank))
     host = [torch.randint(0, VOCAB, (seqs, S + 1), generator=g, dtype=torch.int64).pin_memory()
             for _ in range(W + 2 * K + 2)]
 
     def step(tokens):
         optimizer.zero_grad()
-        # the reference's collator hands the loop separate contiguous input / target tensors
-        inputs, labels = tokens[:, :-1].contiguous(), tokens[:, 1:].contiguous()
-        out = model(inputs)
-        loss, _ = criterion(out.logits, labels)
-        del out
-        loss.backward()
+        total = None
+        for i, chunk in enumerate(tokens.chunk(M)):
+            # the reference's collator hands the loop separate contiguous input / target tensors
+            inputs, labels = chunk[:, :-1].contiguous(), chunk[:, 1:].contiguous()
+            if M > 1 and hasattr(model, "set_requires_gradient_sync"):
+                model.set_requires_gradient_sync(i == M - 1)     # FSDP2: reduce once per optimizer step
+            out = model(inputs)
+            logits = out.logits
+            if hasattr(logits, "full_tensor"):
+                logits = logits.full_tensor()
+            loss, _ = criterion(logits, labels)
+            del out, logits
+            loss = loss / M
+            loss.backward()
+            total = loss.detach() if total is None else total + loss.detach()
+        loss = total
         nn.utils.clip_grad_norm_(model.parameters(), 1.0, foreach=True)
         scheduler.step()
         optimizer.step()
@@ -137,16 +182,18 @@ def _run(args):
                 _ = float(l.item())
         e2e_ms = te.max_ms()
 
-    tokens_per_step = seqs * S * world
+    tokens_per_step = seqs * S * dp
+    label = {"llama-3.2-3b": "Llama-3.2-3B FSDP, seq 4096", "llama-3-8b": "Llama-3-8B TP2 x FSDP, seq 8192"}[model_name]
     if rank == 0:
         print(json.dumps({
-            "metric": "train tokens/s (Llama-3.2-3B FSDP, seq 4096)",
+            "metric": f"train tokens/s ({label})",
             "value": tokens_per_step * K / (ms / 1e3), "unit": "tokens/s", "n_gpus": world,
             "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic uniform-random tokens, random-init weights", "impl": "reference",
-            "config": {"model": "llama-3.2-3b", "global_batch": seqs * world, "seq_len": S,
-                       "parallelism": f"fsdp{world}", "loss": f"CrossEntropyLoss(fast={fast})",
+            "config": {"model": model_name if not args.layers else f"{model_name}-{args.layers}layers-INVALID",
+                       "global_batch": seqs * dp, "seq_len": S, "micro_batches": M,
+                       "parallelism": f"fsdp{world}" if tp == 1 else f"tp{tp} x fsdp{dp}", "loss": f"CrossEntropyLoss(fast={fast})",
                        "stack": "FSDP2 + torch.compile per block + SDPA + cuBLAS",
                        "l2": "inputs larger than L2"},
             "e2e": {"value": tokens_per_step * K / (e2e_ms / 1e3), "unit": "tokens/s",

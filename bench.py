@@ -27,6 +27,14 @@ MODEL_NAME = "llama-3.2-3b"
 SEQ_LEN = 4096
 SEQS_PER_GPU = 8
 VOCAB = 128256
+# --model llama-3-8b is the second training configuration: tensor parallel 2 x FSDP 4 on 8 GPUs,
+# sequence length 8192, global batch 32 (8 sequences per data-parallel rank, run as 2 micro-batches of 4)
+TRAIN_MODELS = {
+    "llama-3.2-3b": {"conf": "configs/models/llama/llama3_2_3b_bench.py", "dim": 3072, "label": "Llama-3.2-3B FSDP, seq 4096",
+                     "tp": 1, "seq_len": 4096, "seqs_per_dp_rank": 8, "micro_batches": 1},
+    "llama-3-8b": {"conf": "configs/models/llama/llama3_8b_bench.py", "dim": 4096, "label": "Llama-3-8B TP2 x FSDP, seq 8192",
+                   "tp": 2, "seq_len": 8192, "seqs_per_dp_rank": 8, "micro_batches": 2},
+}
 
 
 def parse():
@@ -41,10 +49,22 @@ def parse():
     ap.add_argument("--requests-per-gpu", type=int, default=128, help="rollout: 1024 requests per 8-GPU box")
     ap.add_argument("--new-tokens", type=int, default=512)
     ap.add_argument("--prompts-per-gpu", type=int, default=64, help="ppo: 512 prompts per 8-GPU box")
-    ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
-    ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
+    ap.add_argument("--model", default=MODEL_NAME, choices=sorted(TRAIN_MODELS),
+                    help="train: llama-3.2-3b is the headline; llama-3-8b runs tensor parallel 2 x FSDP (gpus / 2)")
+    ap.add_argument("--tp", type=int, default=None, help="train: tensor-parallel degree (default: the model's preset)")
+    ap.add_argument("--micro-batches", type=int, default=None,
+                    help="train: forward/backward passes per optimizer step (gradients accumulate, one reduction)")
+    ap.add_argument("--seq-len", type=int, default=None)
+    ap.add_argument("--seqs-per-gpu", type=int, default=None,
+                    help="train: sequences per data-parallel rank and step (a rank is tp GPUs)")
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (marks the run invalid)")
-    return ap.parse_args()
+    args = ap.parse_args()
+    preset = TRAIN_MODELS[args.model]
+    args.tp = args.tp or preset["tp"]
+    args.seq_len = args.seq_len or preset["seq_len"]
+    args.seqs_per_gpu = args.seqs_per_gpu or preset["seqs_per_dp_rank"]
+    args.micro_batches = args.micro_batches or preset["micro_batches"]
+    return args
 
 
 def init_dist(n_gpus):
@@ -133,8 +153,8 @@ def run_rollout_ours(args):
     engine = InferenceEngine(
         infer, None,
         ModelConfig(n_heads=mc.n_heads, n_key_value_heads=mc.n_key_value_heads, head_dim=mc.head_dim,
-                    n_layers=mc.n_layers, context_len=min(mc.context_len, 4096), device="cuda",
-                    kv_cache_dtype=torch.bfloat16, vocab_size=mc.vocab_size, memory_fraction_static=0.8),
+                    n_layers=mc.n_layers, context_len=min(mc.context_len, 4096), device=f"cuda:{local}",
+                    gpu_id=local, kv_cache_dtype=torch.bfloat16, vocab_size=mc.vocab_size, memory_fraction_static=0.8),
         ServerConfig(decode_steps_ahead=8, use_cudagraph=True))
 
     def to_requests(specs):
@@ -197,17 +217,24 @@ def run_ours(args):
 
     from halite_b200 import ops
     from halite_b200.conf import instantiate, load_config
+    import contextlib
+
     from halite_b200.optim import build_optimizer, cycle_scheduler
+    from halite_b200.optim.sharded_adamw import clip_grad_norm_
     from halite_b200.parallel import ParallelDims, parallelize
     from halite_b200.projects.common.train_fn import optimization_step
     from halite_b200.utils.timing import ClockSampler, DeviceTimer
     from functools import partial
 
     C = ops.ext()
-    conf = load_config(os.path.join(ROOT, "configs/models/llama/llama3_2_3b_bench.py"))
+    preset = TRAIN_MODELS[args.model]
+    conf = load_config(os.path.join(ROOT, preset["conf"]))
     if args.layers:
         conf.model.blocks = conf.model.blocks[: args.layers]
-    pd = ParallelDims(dp_replicate=1, dp_shard=world, tp=1, pp=1, world_size=world)
+    tp = args.tp
+    if world % tp:
+        raise SystemExit(f"--tp {tp} does not divide {world} GPUs")
+    pd = ParallelDims(dp_replicate=1, dp_shard=world // tp, tp=tp, pp=1, world_size=world)
     pd.build_mesh("cuda")
     torch.manual_seed(0)
     with torch.device("meta"):
@@ -220,14 +247,32 @@ def run_ours(args):
     scheduler = cycle_scheduler(optimizer, lr=3e-4, n_iter=10000, warmup=100)
     model.train()
 
-    seqs, S = args.seqs_per_gpu, args.seq_len
+    seqs, S, M = args.seqs_per_gpu, args.seq_len, args.micro_batches
     W, K = args.warmup, args.steps
-    host = make_batches(W + 2 * K + 2, seqs, S, rank)
+    dp = world // tp
+    # the ranks of one tensor-parallel group step on the same sequences
+    host = make_batches(W + 2 * K + 2, seqs, S, pd.dp_rank if tp > 1 else rank)
+    fsdp = model._hb_fsdp
 
     def step(tokens_dev):
-        batch = {"input": tokens_dev[:, :-1], "target": tokens_dev[:, 1:]}
-        return optimization_step(model, batch, optimizer, scheduler, clip_grad_norm=1.0,
-                                calc_loss_in_model=True)
+        if M == 1:
+            batch = {"input": tokens_dev[:, :-1], "target": tokens_dev[:, 1:]}
+            return optimization_step(model, batch, optimizer, scheduler, clip_grad_norm=1.0,
+                                    calc_loss_in_model=True)
+        total = None
+        for i, chunk in enumerate(tokens_dev.chunk(M)):
+            # only the last micro-batch's backward starts the gradient reductions
+            hold = fsdp.no_sync() if i < M - 1 else contextlib.nullcontext()
+            with hold:
+                loss = model(chunk[:, :-1], target=chunk[:, 1:]).loss / M
+                loss.backward()
+            total = loss.detach() if total is None else total + loss.detach()
+        fsdp.finish_backward()
+        clip_grad_norm_(model, 1.0, optimizer)
+        scheduler.step()
+        optimizer.step()
+        optimizer.zero_grad(set_to_none=True)
+        return {"loss": total}
 
     # ---- warm-up (untimed)
     it = iter(host)
@@ -265,24 +310,25 @@ def run_ours(args):
         gather_mode = (f"{len(fused_units)} block units: peers' shards copied over NVLink by CTAs inside GEMM launches "
                        f"({carried} carried, {sum(u.fused.standalone for u in fused_units)} launched alone so far); "
                        f"gradient reduction through NVLS multimem: {nvls}; root and head units: NCCL")
-    tokens_per_step = seqs * S * world
+    tokens_per_step = seqs * S * dp
     value = tokens_per_step * K / (ms / 1e3)
     e2e = tokens_per_step * K / (e2e_ms / 1e3)
-    n_params = sum(u.numel for u in model._hb_fsdp.units)
-    n_matmul = n_params - model.embedding.embed_weight.numel()   # the embedding lookup is no GEMM
-    flops_per_token = 6 * n_matmul + 6 * len(model.blocks) * S * 3072  # causal attention: 12*L*S*D/2
+    n_params = sum(u.numel for u in model._hb_fsdp.units) * tp      # units hold this rank's tensor-parallel slice
+    n_matmul = n_params - model.embedding.embed_weight.numel() * tp  # the embedding lookup is no GEMM
+    flops_per_token = 6 * n_matmul + 6 * len(model.blocks) * S * preset["dim"]  # causal attention: 12*L*S*D/2
     peak_mem = torch.cuda.max_memory_allocated() / 2 ** 30
     if rank == 0:
         result = {
-            "metric": "train tokens/s (Llama-3.2-3B FSDP, seq 4096)", "value": value, "unit": "tokens/s",
+            "metric": f"train tokens/s ({preset['label']})", "value": value, "unit": "tokens/s",
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic uniform-random tokens, random-init weights",
             "impl": "ours",
-            "config": {"model": MODEL_NAME if not args.layers else f"{MODEL_NAME}-{args.layers}layers-INVALID",
-                       "global_batch": seqs * world, "seq_len": S,
-                       "parallelism": f"fsdp{world}", "optimizer": "AdamW fp32 master, clip 1.0",
-                       "l2": "inputs larger than L2 (activations of 32768 tokens/GPU)",
+            "config": {"model": args.model if not args.layers else f"{args.model}-{args.layers}layers-INVALID",
+                       "global_batch": seqs * dp, "seq_len": S, "micro_batches": M,
+                       "parallelism": f"fsdp{world}" if tp == 1 else f"tp{tp} x fsdp{dp}",
+                       "optimizer": "AdamW fp32 master, clip 1.0",
+                       "l2": f"inputs larger than L2 (activations of {seqs * S // M} tokens per pass)",
                        "attention": "own tcgen05 kernels (forward + backward) inside the packed-QKV op",
                        "fsdp_all_gather": gather_mode},
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": e2e_ms / K,
@@ -291,7 +337,7 @@ def run_ours(args):
             "clocks": clocks.summary(),
             "loss": loss_dev,
             "mfu_of_measured_sustained": None,
-            "model_tflops_per_gpu": flops_per_token * seqs * S / (ms / K / 1e3) / 1e12,
+            "model_tflops_per_gpu": flops_per_token * tokens_per_step / world / (ms / K / 1e3) / 1e12,
             "peak_mem_gib": peak_mem,
         }
         try:

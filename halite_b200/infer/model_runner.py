@@ -39,7 +39,8 @@ class ModelRunner:
         self.sampler = Sampler(seed=server_config.seed)
         self.device = torch.device(model_config.device)
         if self.device.type == "cuda" and self.device.index is None:
-            self.device = torch.device("cuda", model_config.gpu_id)
+            # "cuda" without an index: `gpu_id` when it names a device, else the process's current one
+            self.device = torch.device("cuda", model_config.gpu_id or torch.cuda.current_device())
         self.page_size = server_config.page_size
         dtype = model_config.kv_cache_dtype
         if dtype == "auto":

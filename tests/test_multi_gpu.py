@@ -35,3 +35,11 @@ def test_fsdp_parameter_gather_carried_by_gemm_launches():
     env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE="0")
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0 and "RESULT ok" in out.stdout, (out.stdout + out.stderr)[-3000:]
+
+
+def test_tensor_parallel_training_with_collectives_inside_the_gemms():
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", str(free_port()), os.path.join(ROOT, "tests/ranks/tp_train_gpu.py")]
+    env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE="0")
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0 and "RESULT ok" in out.stdout, (out.stdout + out.stderr)[-3000:]
