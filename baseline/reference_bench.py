@@ -115,14 +115,16 @@ def _run(args):
     if dp > 1:
         model = instantiate(conf.parallelize)(model=model, mesh=mesh, parallel_dims=pdims)
     elif tp > 1:
-        # one data-parallel rank: the reference's parallelize() would skip sharding (and with it bf16
-        # parameters), so force its FSDP wrapper on the one-rank dp mesh as the one-GPU run does
-        model = instantiate(conf.parallelize)(model=model, mesh=mesh, parallel_dims=pdims, force_fsdp=True)
-        if not any(type(m).__name__.startswith("FSDP") for m in model.modules()):
-            apply_fsdp(model, mesh["dp"], "bfloat16", "float32", True)
-    else:
+        # one data-parallel rank: the reference's mesh then has no dp dimension and its parallelize() would
+        # skip sharding (and with it bf16 parameters); call its own apply_tp / apply_compile / apply_fsdp on a
+        # (1, tp) mesh, as the one-GPU run does with a one-rank mesh
+        from halite.transformers.parallelize import apply_tp
+        from torch.distributed.device_mesh import init_device_mesh
+
+        mesh2 = init_device_mesh("cuda", (1, tp), mesh_dim_names=("dp", "tp"))
+        apply_tp(model, mesh2["tp"], None)
         apply_compile(model, None)
-        apply_fsdp(model, mesh["dp"], "bfloat16", "float32", True)
+        apply_fsdp(model, mesh2["dp"], "bfloat16", "float32", True)
     model.to_empty(device=device)
     model.init_weights(device)
 

