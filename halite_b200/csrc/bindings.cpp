@@ -186,6 +186,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("a_mn") = false, py::arg("b_mn") = false, py::arg("accumulate") = false,
         py::arg("block_n") = 0, py::arg("max_ctas") = 0, py::arg("status") = py::none(),
         py::arg("gather") = py::none(), py::arg("scatter") = py::none(), py::arg("group") = py::none());
+  m.def("gemm_set_peer_wait_sm_margin", [](int sms) { hb::gemm_set_peer_wait_sm_margin(sms); }, py::arg("sms"));
+  m.def("gemm_peer_wait_sm_margin", []() { return hb::gemm_peer_wait_sm_margin(); });
   m.def("gemm_set_dynamic_schedule", [](bool on, bool force) { hb::gemm_set_dynamic_schedule(on, force); },
         "CTA-pair GEMM: hand work items out through a counter (true) or in fixed shares (false)",
         py::arg("on"), py::arg("force") = false);

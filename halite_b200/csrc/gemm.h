@@ -117,6 +117,10 @@ int gemm_pick_bn(int M, int N);
 // Pair kernel: hand work items out through a counter, or in fixed shares (default). A setting from
 // the environment (HB_GEMM_DYNAMIC=0/1) wins unless `force`.
 void gemm_set_dynamic_schedule(bool on, bool force = false);
+// SMs left free by GEMM launches whose CTAs spin on a peer GPU's progress (tile-dependent gather, scatter),
+// so that a collective of another process group running beside them always finds room. 0 = none.
+void gemm_set_peer_wait_sm_margin(int sms);
+int gemm_peer_wait_sm_margin();
 
 bool make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
                        uint64_t ld, uint32_t box_rows, uint32_t box_cols);

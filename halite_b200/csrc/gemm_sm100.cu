@@ -1454,6 +1454,18 @@ int sm_count() {
   return n;
 }
 
+// SMs that launches whose CTAs spin on another GPU's progress (the tile-dependent gather mode and the
+// scatter mode) leave free. Such a kernel holds every SM it runs on until its peer catches up; when the
+// peer is itself held back by a collective of ANOTHER process group whose kernel cannot become resident
+// on some GPU because a spinning kernel fills it, the ranks wait in a circle. With a margin at least as
+// large as the collective library's CTA count, those kernels always find an SM.
+int g_peer_wait_sm_margin = 0;
+
+int peer_wait_sm_count() {
+  const int n = sm_count() - g_peer_wait_sm_margin;
+  return n < 8 ? 8 : n;
+}
+
 template <int BN, bool A_MN, bool B_MN, typename OutT>
 cudaError_t launch(const GemmArgs& g) {
   using C = Cfg<BN>;
@@ -1506,11 +1518,14 @@ cudaError_t launch(const GemmArgs& g) {
       return cudaErrorInvalidValue;
     if (gp.reduce_out && (gp.reduce_numel % 4 || (reinterpret_cast<uintptr_t>(gp.reduce_out) & 15)))
       return cudaErrorInvalidValue;
-    const int compute = tiles < sm_count() - gp.n_copy_ctas ? tiles : sm_count() - gp.n_copy_ctas;
+    const int sms = gp.dep != 0 ? peer_wait_sm_count() : sm_count();
+    if (gp.n_copy_ctas >= sms) return cudaErrorInvalidValue;
+    const int compute = tiles < sms - gp.n_copy_ctas ? tiles : sms - gp.n_copy_ctas;
     grid = compute + gp.n_copy_ctas;
     if (gp.done_counter) cudaMemsetAsync(gp.done_counter, 0, sizeof(int), g.stream);
   } else {
-    grid = tiles < sm_count() ? tiles : sm_count();
+    const int sms = g.scatter ? peer_wait_sm_count() : sm_count();
+    grid = tiles < sms ? tiles : sms;
     if (g.max_ctas > 0 && grid > g.max_ctas) grid = g.max_ctas;
   }
   SplitParams kp;
@@ -1837,6 +1852,12 @@ cudaError_t wait_flags(const int* flags, int n, int epoch, int* status, cudaStre
   wait_flags_kernel<<<1, 32, 0, stream>>>(flags, n, epoch, status);
   return cudaGetLastError();
 }
+
+void gemm_set_peer_wait_sm_margin(int sms) {
+  g_peer_wait_sm_margin = sms < 0 ? 0 : (sms > sm_count() / 2 ? sm_count() / 2 : sms);
+}
+
+int gemm_peer_wait_sm_margin() { return g_peer_wait_sm_margin; }
 
 void gemm_set_dynamic_schedule(bool on, bool force) {
   (void)dynamic_schedule_enabled();   // reads the environment once

@@ -438,6 +438,30 @@ def _shard_linear(lin, how, tp, attn=None):
     lin._hb_tp_kind = how
 
 
+def _reserve_sms_for_other_groups(parallel_dims, tp):
+    """The fused collective GEMMs spin on the tensor-parallel peer while they hold their SMs. When the
+    ranks also run collectives of another group beside them (FSDP all-gathers and reduce-scatters over
+    the data-parallel group), a peer can be held back by such a collective whose kernel finds no free SM
+    on a third GPU that is itself spinning, and the ranks wait in a circle until the bounded waits give
+    up. So the spinning launches leave `HB_TP_SM_MARGIN` SMs (default 20) free; the collective library
+    must use no more CTAs than that (`NCCL_MAX_CTAS`, read by NCCL when its communicators are made)."""
+    import os
+    import warnings
+
+    if tp.fused is False or not torch.cuda.is_available():
+        return
+    others = getattr(parallel_dims, "world_size", tp.size) // tp.size
+    if others <= 1:
+        return
+    margin = int(os.environ.get("HB_TP_SM_MARGIN", "20"))
+    ops.ext().gemm_set_peer_wait_sm_margin(margin)
+    cap = os.environ.get("NCCL_MAX_CTAS")
+    if cap is None or int(cap) > margin:
+        warnings.warn(f"tensor parallelism with fused collective GEMMs beside data-parallel collectives: set "
+                      f"NCCL_MAX_CTAS <= {margin} before the process groups are made (it is {cap}); otherwise the "
+                      f"two can wait on each other until the kernels' bounded waits give up", stacklevel=3)
+
+
 def apply_tp(model, parallel_dims, loss_parallel=True, enable_async_tp=True, heap_bytes=None, **unused):
     """Shard the model's linears / embedding / head over the `tp` mesh dimension according to
     each module's `tp_plan()` and switch the modules to their tensor-parallel forward."""
@@ -465,6 +489,7 @@ def apply_tp(model, parallel_dims, loss_parallel=True, enable_async_tp=True, hea
                     setattr(module, a, getattr(module, a) // tp.size)
     model._hb_tp = tp
     model._hb_loss_parallel = loss_parallel
+    _reserve_sms_for_other_groups(parallel_dims, tp)
     # parameters that stay replicated over TP but see only a token shard (norm scales) need
     # their gradients summed over the group
     sharded = set()

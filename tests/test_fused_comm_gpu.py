@@ -13,13 +13,35 @@ def _i32(n, val=0):
     return torch.full((n,), val, dtype=torch.int32, device="cuda")
 
 
+@pytest.fixture
+def sm_margin():
+    """Leave 20 SMs free in the launches that spin on a peer, as tensor parallelism beside
+    data-parallel collectives does."""
+    from halite_b200 import ops
+
+    ops.ext().gemm_set_peer_wait_sm_margin(20)
+    yield 20
+    ops.ext().gemm_set_peer_wait_sm_margin(0)
+
+
 @pytest.mark.parametrize("rank", [0, 1, 2])
 def test_allgather_gemm_a_operand(rank):
+    _allgather_gemm_a_operand(rank, 3, 256, 1024, 1536)
+
+
+def test_fused_modes_keep_working_with_an_sm_margin(sm_margin):
+    from halite_b200 import ops
+
+    assert ops.ext().gemm_peer_wait_sm_margin() == 20
+    _allgather_gemm_a_operand(1, 2, 2048, 1024, 4096)       # 512 tiles on 128 - 8 compute CTAs
+    _gemm_reduce_scatter(0, 2, 2048, 512, 4096)
+
+
+def _allgather_gemm_a_operand(rank, world, rows, K, N):
     from halite_b200 import ops
     from halite_b200.ops import gemm
 
     torch.manual_seed(0)
-    world, rows, K, N = 3, 256, 1024, 1536
     shards = [torch.randn(rows, K, device="cuda").bfloat16() for _ in range(world)]
     w = (0.05 * torch.randn(N, K, device="cuda")).bfloat16()
     staging = torch.zeros(world * rows, K, device="cuda", dtype=torch.bfloat16)
@@ -121,11 +143,14 @@ def test_reduce_scatter_slice_carried_by_a_gemm_launch(gemm_shape):
 
 @pytest.mark.parametrize("rank", [0, 1])
 def test_gemm_reduce_scatter(rank):
+    _gemm_reduce_scatter(rank, 2, 384, 768, 1024)
+
+
+def _gemm_reduce_scatter(rank, world, rows, K, N):
     from halite_b200 import ops
     from halite_b200.ops import gemm
 
     torch.manual_seed(2)
-    world, rows, K, N = 2, 384, 768, 1024
     x = torch.randn(world * rows, K, device="cuda").bfloat16()
     w = (0.05 * torch.randn(N, K, device="cuda")).bfloat16()
     partial = torch.zeros(rows, N, device="cuda", dtype=torch.bfloat16)
