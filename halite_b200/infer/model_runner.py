@@ -233,8 +233,24 @@ class ModelRunner:
             range(sc.cudagraph_step, sc.cudagraph_max_batch_size + 1, sc.cudagraph_step))
         return sorted(s for s in sizes if s > 0)
 
+    def _graph_capturable(self):
+        """A decode forward can be captured only when every attention layer runs the paged kernels: the
+        plain-PyTorch path they fall back to (other head sizes or cache types, soft-cap, windows) reads
+        lengths on the host."""
+        if getattr(self, "_capturable", None) is None:
+            mc = self.model_config
+            ok = self.kv_cache_dtype == torch.bfloat16 and mc.head_dim in (64, 128)
+            for m in self.model.modules():
+                if getattr(m, "softcap", 0.0) or getattr(m, "window_size", None) is not None:
+                    ok = False
+            first = next((p for p in self.model.parameters() if p.is_floating_point()), None)
+            if first is not None and first.dtype != torch.bfloat16:
+                ok = False
+            self._capturable = ok
+        return self._capturable
+
     def _graph_for(self, batch_size):
-        if self.device.type != "cuda":
+        if self.device.type != "cuda" or not self._graph_capturable():
             return None
         sizes = self.graph_sizes()
         bucket = next((s for s in sizes if s >= batch_size), None)
