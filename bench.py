@@ -212,6 +212,9 @@ def run_ours(args):
     import torch
     import torch.distributed as dist
 
+    if args.tp > 1 and args.gpus > args.tp:
+        # the fused tensor-parallel GEMMs leave 20 SMs to the data-parallel collectives: keep NCCL within them
+        os.environ.setdefault("NCCL_MAX_CTAS", "16")
     rank, world, local = init_dist(args.gpus)
     dev = torch.device("cuda", local)
 
