@@ -82,6 +82,14 @@ def main(argv=None):
         out = ours()
         rows["ours_bwd_ms"] = timed(lambda: torch.autograd.grad(out, (q, k, v), go, retain_graph=True), args.iters, flush)
     ops.check_status()
+    if hasattr(ops.ext(), "attention_profile_read") and not args.no_backward:
+        # a build with the backward kernel's cycle counters: one more backward, counters per query tile
+        ops.ext().attention_profile_read(True)
+        torch.autograd.grad(out, (q, k, v), go, retain_graph=True)
+        torch.cuda.synchronize()
+        c = ops.ext().attention_profile_read(True)
+        tiles = max(c[0], 1)
+        rows["bwd_cycles_per_query_tile"] = {i: round(c[i] / tiles, 1) for i in range(1, 16)}
 
     if not args.no_library and cu is None and not args.window:
         qh, kh, vh = (t.detach().transpose(1, 2).requires_grad_() for t in (q, k, v))

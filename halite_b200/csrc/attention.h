@@ -19,7 +19,14 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+// #define HB_ATTN_PROFILE 1   // cycle counters of the backward kernel (see attention_sm100.cu)
+
 namespace hb {
+
+#ifdef HB_ATTN_PROFILE
+// 32 cycle counters of the backward kernel's roles, summed over CTAs since the last reset.
+cudaError_t attention_profile_read(unsigned long long* out32, bool reset);
+#endif
 
 struct AttnArgs {
   const void* q = nullptr;

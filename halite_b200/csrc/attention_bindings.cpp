@@ -141,6 +141,13 @@ void register_attention(pybind11::module_& m) {
         py::arg("seg_end") = py::none(), py::arg("seq_len") = 0, py::arg("causal") = true, py::arg("window") = 0,
         py::arg("scale") = 1.0, py::arg("softcap") = 0.0, py::arg("status") = py::none());
   m.def("reshard_copy", &reshard_copy, py::arg("table"));
+#ifdef HB_ATTN_PROFILE
+  m.def("attention_profile_read", [](bool reset) {
+    unsigned long long v[32];
+    HB_ATTN_OK(hb::attention_profile_read(v, reset), 1);
+    return std::vector<unsigned long long>(v, v + 32);
+  }, py::arg("reset") = true);
+#endif
   m.def("attention_bwd", &attention_bwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"), py::arg("d_out"),
         py::arg("lse"), py::arg("dq"), py::arg("dk"), py::arg("dv"), py::arg("seg_start") = py::none(),
         py::arg("seg_end") = py::none(), py::arg("seq_len") = 0, py::arg("causal") = true, py::arg("window") = 0,

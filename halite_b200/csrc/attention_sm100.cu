@@ -520,11 +520,16 @@ struct BwdCfg {
   static constexpr int kChunks = D / 64;
   static constexpr int kChunkBytes = kTile * 128;
   static constexpr int kTileBytes = kChunks * kChunkBytes;
-  static constexpr int kRing = 3;                               // Q_i, dO_i, Q_{i+1}
+  static constexpr int kRing = 3;                               // stages 0 / 1: Q of even / odd query tiles; stage 2: dO
   static constexpr int kDsBytes = 2 * kChunkBytes;              // dS^T: 128 key rows x 128 query columns
   static constexpr int kVecBytes = 8 * 2 * 64 * 4;              // lse, delta of a warp's 64 query columns, one copy per warp
-  static constexpr int kSmemBytes = (2 + kRing) * kTileBytes + kDsBytes + kVecBytes + 1024;
-  static constexpr int kThreads = 384;
+  static constexpr int kDrainBytes = 4 * 4096;                  // one 32 x 32 fp32 staging piece per drain warp
+  static constexpr int kSmemBytes = (2 + kRing) * kTileBytes + kDsBytes + kVecBytes + kDrainBytes + 1024;
+  static constexpr int kThreads = 512;
+  // registers per thread after the warpgroups have traded them (512 threads start with 128 each):
+  // producer / MMA / allocator warps, the two element-wise warpgroups, the dQ drain warpgroup
+  static constexpr int kRegsLight = 64, kRegsElem = 144, kRegsDrain = 160;
+  static_assert(kRegsLight + 2 * kRegsElem + kRegsDrain == 4 * 128, "the register file must add up");
   static constexpr int kTmemCols = 512;
   static constexpr int kPCol = 32;                              // P^T (64 columns of bf16 pairs) inside S^T's columns:
                                                                 // each warpgroup overwrites only columns it has read itself
@@ -646,8 +651,22 @@ __global__ void attn_dq_finish_kernel(const float* __restrict__ acc, __nv_bfloat
   }
 }
 
+// Cycle counters of the backward kernel's roles (compiled in with -DHB_ATTN_PROFILE or a define in
+// attention.h; read with attention_profile_read). Slot: 0 query tiles; MMA thread waits 1 dO ring,
+// 2 dq_free, 3 p_ready, 4 Q ring, 5 ds_ready, 6 its loop; element-wise warp 4 lane 0: 7 wait dP, 8 wait S,
+// 9 step 1 work, 10 step 2 work, 11 its loop; drain warp 12 lane 0: 12 wait dQ, 13 waits for the
+// reduce engine, 14 its loop, 15 TMEM loads.
+#ifdef HB_ATTN_PROFILE
+__device__ unsigned long long hb_attn_prof[32];
+#define HB_PROF_BEGIN(t) const long long t = clock64()
+#define HB_PROF_END(t, slot, on) do { if (on) atomicAdd(&hb_attn_prof[slot], static_cast<unsigned long long>(clock64() - (t))); } while (0)
+#else
+#define HB_PROF_BEGIN(t) do {} while (0)
+#define HB_PROF_END(t, slot, on) do {} while (0)
+#endif
+
 template <int D, bool kSoftcap>
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(512, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                 const __grid_constant__ CUtensorMap tm_dq, const float* __restrict__ lse,
@@ -673,6 +692,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t ring = smem_base + 2 * C::kTileBytes;
   const uint32_t ds_smem = ring + C::kRing * C::kTileBytes;
   float* vec = reinterpret_cast<float*>(smem_raw + (ds_smem + C::kDsBytes - smem_u32(smem_raw)));
+  const uint32_t drain_smem = ds_smem + C::kDsBytes + C::kVecBytes;
   // vec layout: [warp][lse2 | delta][64]: each elementwise warp stages its own copy, so the
   // eight warps never wait for one another
   const int warp = threadIdx.x >> 5;
@@ -718,7 +738,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_init(smem_u32(&bar_p_ready), 8);
     mbar_init(smem_u32(&bar_ds_ready), 8);
     mbar_init(smem_u32(&bar_dq_full), 1);
-    mbar_init(smem_u32(&bar_dq_free), 8);
+    mbar_init(smem_u32(&bar_dq_free), 4);
     mbar_init(smem_u32(&bar_dkv_full), 1);
     fence_barrier_init();
     tma_prefetch_desc(&tm_q);
@@ -736,6 +756,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
 
+  // The four warpgroups trade registers, each at the top of its own branch (so that the code below
+  // it is compiled for that budget): the light one (producer, MMA issuer, allocator) gives some up
+  // and nobody else does, so the requests of the other three always find them.
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::kRegsLight));
   if (warp == 0 && lane == 0) {
     // ------------------------------------------------------------ producer
     {
@@ -747,15 +772,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tma_load_3d(v_smem + c * C::kChunkBytes, &tm_v, full, c * 64, hk, k0);
       }
     }
+    // Q(it) lives from S(it) to dK(it), a whole query tile and a half, so it alternates between two
+    // stages; dO(it) is done after dV(it), in the middle of its tile, and has the third stage to
+    // itself. Either way a load is issued half a query tile or more before its first use.
     bool ok = true;
-    int e = 0;
     for (int it = 0; it < n_it && ok; ++it) {
       const int h = hk * G + it / n_i;
       const int q0 = (ib + it % n_i) * kTile;
 #pragma unroll
-      for (int which = 0; which < 2; ++which, ++e) {
-        const int stage = e % C::kRing;
-        const uint32_t phase = (e / C::kRing) & 1;
+      for (int which = 0; which < 2; ++which) {
+        const int stage = which == 0 ? (it & 1) : 2;
+        const uint32_t phase = which == 0 ? ((it >> 1) & 1) : (it & 1);
         ok = mbar_wait(smem_u32(&bar_ring_empty[stage]), phase ^ 1, &abort_flag, p.status, kTimeoutEmpty);
         if (!ok) break;
         const uint32_t full = smem_u32(&bar_ring_full[stage]);
@@ -779,12 +806,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t k_mn_lo = desc_lo(k_smem, C::kChunkBytes), ds_lo = desc_lo(ds_smem, 0),
                    ds_mn_lo = desc_lo(ds_smem, C::kChunkBytes);
     auto issue_s = [&](int it) -> bool {
-      const int e_q = 2 * it;
-      if (!mbar_wait(smem_u32(&bar_ring_full[e_q % C::kRing]), (e_q / C::kRing) & 1, &abort_flag, p.status,
-                     kTimeoutFull))
+      HB_PROF_BEGIN(tq);
+      if (!mbar_wait(smem_u32(&bar_ring_full[it & 1]), (it >> 1) & 1, &abort_flag, p.status, kTimeoutFull))
         return false;
+      HB_PROF_END(tq, 4, true);
       tc_fence_after();
-      const uint32_t q_lo = desc_lo(ring + (e_q % C::kRing) * C::kTileBytes, 0);
+      const uint32_t q_lo = desc_lo(ring + (it & 1) * C::kTileBytes, 0);
 #pragma unroll
       for (int ks = 0; ks < D / 16; ++ks) {
         const uint32_t off = static_cast<uint32_t>(((ks >> 2) * C::kChunkBytes + (ks & 3) * 32) >> 4);
@@ -794,16 +821,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       return true;
     };
     if (ok && n_it > 0) ok = issue_s(0);
+    HB_PROF_BEGIN(tloop);
     for (int it = 0; it < n_it && ok; ++it) {
-      const int e_q = 2 * it, e_o = 2 * it + 1;
-      const uint32_t q_addr = ring + (e_q % C::kRing) * C::kTileBytes;
-      const uint32_t o_addr = ring + (e_o % C::kRing) * C::kTileBytes;
+      const uint32_t q_addr = ring + (it & 1) * C::kTileBytes;
+      const uint32_t o_addr = ring + 2 * C::kTileBytes;
       const uint32_t par = it & 1;
       // dP^T = V dO^T (its columns held the previous dQ tile until the drain finished)
-      ok = mbar_wait(smem_u32(&bar_ring_full[e_o % C::kRing]), (e_o / C::kRing) & 1, &abort_flag, p.status,
-                     kTimeoutFull);
+      HB_PROF_BEGIN(t1);
+      ok = mbar_wait(smem_u32(&bar_ring_full[2]), it & 1, &abort_flag, p.status, kTimeoutFull);
+      HB_PROF_END(t1, 1, true);
+      HB_PROF_BEGIN(t2);
       if (ok && it > 0)
         ok = mbar_wait(smem_u32(&bar_dq_free), (it - 1) & 1, &abort_flag, p.status, kTimeoutTmemEmpty);
+      HB_PROF_END(t2, 2, true);
       if (!ok) break;
       tc_fence_after();
       const uint32_t o_lo = desc_lo(o_addr, 0), o_mn_lo = desc_lo(o_addr, C::kChunkBytes);
@@ -815,14 +845,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       umma_commit(smem_u32(&bar_dp_full));
       // dV += P^T dO
+      HB_PROF_BEGIN(t3);
       ok = mbar_wait(smem_u32(&bar_p_ready), par, &abort_flag, p.status, kTimeoutTmemEmpty);
+      HB_PROF_END(t3, 3, true);
       if (!ok) break;
       tc_fence_after();
 #pragma unroll
       for (int ks = 0; ks < kTile / 16; ++ks)
         umma_ts(tmem_base + C::kDvCol, tmem_base + C::kPCol + ks * 8, o_mn_lo + static_cast<uint32_t>((ks * 2048) >> 4),
                 idesc_acc, it > 0 || ks != 0);
-      umma_commit(smem_u32(&bar_ring_empty[e_o % C::kRing]));
+      umma_commit(smem_u32(&bar_ring_empty[2]));
       // S^T of the next tile, over the P that dV has just been issued on (the tensor cores run
       // one CTA's instructions in issue order)
       if (it + 1 < n_it) {
@@ -830,7 +862,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (!ok) break;
       }
       // dK += dS^T Q, dQ = dS K
+      HB_PROF_BEGIN(t5);
       ok = mbar_wait(smem_u32(&bar_ds_ready), par, &abort_flag, p.status, kTimeoutTmemEmpty);
+      HB_PROF_END(t5, 5, true);
       if (!ok) break;
       tc_fence_after();
 #pragma unroll
@@ -844,16 +878,22 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         umma_ss(tmem_base + C::kDpCol, ds_mn_lo + static_cast<uint32_t>((ks * 2048) >> 4),
                 k_mn_lo + static_cast<uint32_t>((ks * 2048) >> 4), idesc_dq, ks != 0);
       umma_commit(smem_u32(&bar_dq_full));
-      umma_commit(smem_u32(&bar_ring_empty[e_q % C::kRing]));
+      umma_commit(smem_u32(&bar_ring_empty[it & 1]));
     }
+    HB_PROF_END(tloop, 6, true);
+#ifdef HB_ATTN_PROFILE
+    atomicAdd(&hb_attn_prof[0], static_cast<unsigned long long>(n_it));
+#endif
     if (ok) umma_commit(smem_u32(&bar_dkv_full));
-  } else if (warp >= 4) {
-    // ------------------------------------------------------------ elementwise + drains
+  }
+  } else if (warp < 12) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C::kRegsElem));
+    // ------------------------------------------------------------ elementwise
     // Two warpgroups share every 128 x 128 tile: warps 4-7 take query columns 0-63 of each key
     // row, warps 8-11 columns 64-127 (a warp reads the TMEM lane quarter warp % 4). Per query
-    // tile: P (step 1), dS (step 2), drain of the dQ tile (step 3). Step 1 of the next tile runs
-    // before step 3 of this one, under the dK / dQ products. With soft-capping the plain order is
-    // kept, because step 1 then parks a factor in the dS buffer.
+    // tile: P (step 1) and dS (step 2); step 1 of the next tile runs under the dK / dQ products of
+    // this one. The dQ tile leaves through the drain warpgroup (warps 12-15). With soft-capping
+    // step 1 parks a factor in the dS buffer, so it first waits until dK / dQ have read dS.
     const int wg = (warp - 4) >> 2;            // which half of the columns
     const int wq = warp & 3;
     const int r = wq * 32 + lane;              // key row in steps 1 and 2, query row in the drain
@@ -864,19 +904,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t s_addr = tmem_base + lane_addr + wg * 64;                 // this half of S^T
     const uint32_t p_addr = tmem_base + lane_addr + C::kPCol + wg * 32;      // this half of P^T (bf16 pairs)
     const uint32_t dp_addr = tmem_base + C::kDpCol + lane_addr + wg * 64;    // this half of dP^T
-    const uint32_t dq_addr = tmem_base + C::kDpCol + lane_addr + wg * (D / 2);   // this half of the dQ tile
     const float c2 = kSoftcap ? kLog2e : p.scale * kLog2e;
     const float cap_in = kSoftcap ? p.scale / p.softcap : 0.f;
-    // this thread's 64 columns of dS^T are one 128-byte row of the buffer's half `wg`; the warp's
-    // 32 such rows double as its staging piece for the dQ drain
+    // this thread's 64 columns of dS^T are one 128-byte row of the buffer's half `wg`
     const uint32_t ds_row = ds_smem + wg * C::kChunkBytes + r * 128;
-    const uint32_t piece = ds_smem + wg * C::kChunkBytes + wq * 4096;
     float* lse2 = vec + (warp - 4) * 2 * 64;
     float* dlt = lse2 + 64;
     uint32_t pk[32];
     bool ok = true;
-    bool reduce_in_flight = false;
     float pre[4];
+#ifdef HB_ATTN_PROFILE
+    const bool prof_lane = warp == 4 && lane == 0;
+#endif
 
     // lse / delta of this warp's 64 query columns: fetched early into registers, parked in shared
     // memory right before use
@@ -900,23 +939,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       __syncwarp();
     };
-    // the staging piece / dS rows may only be rewritten once the reductions that read them are done
-    auto wait_reduce_reads = [&]() {
-      if (reduce_in_flight) {
-        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-        __syncwarp();
-        reduce_in_flight = false;
-      }
-    };
     // ---- step 1: P^T = exp2(S^T c2 - lse) as bf16 pairs, into TMEM and into `pk`
     auto step1 = [&](int it) -> bool {
       const int q0 = (ib + it % n_i) * kTile + wg * 64;
       const bool mask_tile = __any_sync(0xffffffffu, q0 < qlo || q0 + 63 > qhi);
+      HB_PROF_BEGIN(tw);
       bool good = mbar_wait(smem_u32(&bar_s_full), it & 1, &abort_flag, p.status, kTimeoutTmemFull);
       good = __all_sync(0xffffffffu, good);
+      HB_PROF_END(tw, 8, prof_lane);
       if (!good) return false;
+      HB_PROF_BEGIN(tk);
       tc_fence_after();
-      if (kSoftcap) wait_reduce_reads();
       uint32_t v[2][32];
       tmem_ld_32x32(s_addr, v[0]);
       tmem_ld_32x32(s_addr + 32, v[1]);
@@ -968,18 +1001,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_p_ready));
+      HB_PROF_END(tk, 9, prof_lane);
       return true;
     };
     // ---- step 2: dS^T = P^T (dP^T - delta) scale, bf16, into shared memory
     auto step2 = [&](int it) -> bool {
+      HB_PROF_BEGIN(tw);
       bool good = mbar_wait(smem_u32(&bar_dp_full), it & 1, &abort_flag, p.status, kTimeoutTmemFull);
       good = __all_sync(0xffffffffu, good);
+      HB_PROF_END(tw, 7, prof_lane);
       if (!good) return false;
+      HB_PROF_BEGIN(tk);
       tc_fence_after();
       uint32_t v[2][32];
       tmem_ld_32x32(dp_addr, v[0]);
       tmem_ld_32x32(dp_addr + 32, v[1]);
-      wait_reduce_reads();
       tmem_ld_wait();
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
@@ -1016,75 +1052,32 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       fence_proxy_async_smem();      // the tensor cores read dS^T through the async proxy
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_ds_ready));
+      HB_PROF_END(tk, 10, prof_lane);
       return true;
     };
-    // ---- step 3: this warp's part of the dQ tile (32 query rows x D / 2 columns) leaves through
-    // its staging piece, 32 columns at a time, as bulk tensor reductions (fp32 add) into dq_accum
-    auto step3 = [&](int it) -> bool {
-      const int h = hk * G + it / n_i;
-      const int q0 = (ib + it % n_i) * kTile;
-      bool good = mbar_wait(smem_u32(&bar_dq_full), it & 1, &abort_flag, p.status, kTimeoutTmemFull);
-      good = __all_sync(0xffffffffu, good);
-      if (!good) return false;
-      tc_fence_after();
-      uint32_t v[D / 64][32];
-#pragma unroll
-      for (int c = 0; c < D / 64; ++c) tmem_ld_32x32(dq_addr + c * 32, v[c]);
-      tmem_ld_wait();
-      // the tile is in registers: its TMEM columns can take the next dP^T already
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_dq_free));
-#pragma unroll
-      for (int c = 0; c < D / 64; ++c) {
-        if (c > 0) {
-          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-          __syncwarp();
-        }
-#pragma unroll
-        for (int g = 0; g < 8; ++g)
-          st_shared_v4(piece + lane * 128 + ((static_cast<uint32_t>(g) ^ (lane & 7)) << 4), v[c][4 * g],
-                       v[c][4 * g + 1], v[c][4 * g + 2], v[c][4 * g + 3]);
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          asm volatile(
-              "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
-                  reinterpret_cast<uint64_t>(&tm_dq)),
-              "r"(piece), "r"(wg * (D / 2) + c * 32), "r"(h), "r"(q0 + wq * 32)
-              : "memory");
-          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        }
-      }
-      reduce_in_flight = true;
-      return true;
-    };
-
     if (n_it > 0) {
       fetch_vectors(0);
       park_vectors();
       ok = step1(0);
     }
+    HB_PROF_BEGIN(tloop);
     for (int it = 0; it < n_it && ok; ++it) {
       const bool more = it + 1 < n_it;
       if (more) fetch_vectors(it + 1);
       ok = step2(it);
       if (!ok) break;
-      if (!kSoftcap && more) {
-        park_vectors();
-        ok = step1(it + 1);
-        if (!ok) break;
-      }
-      ok = step3(it);
-      if (!ok) break;
-      if (kSoftcap && more) {
+      if (more) {
+        if (kSoftcap) {
+          // the factor goes into the dS rows: dK(it) and dQ(it) must have read dS(it)
+          ok = mbar_wait(smem_u32(&bar_dq_full), it & 1, &abort_flag, p.status, kTimeoutTmemFull);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
         park_vectors();
         ok = step1(it + 1);
       }
     }
-    // every reduction this lane issued has to land before the CTA's shared memory goes away
-    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-    __syncwarp();
+    HB_PROF_END(tloop, 11, prof_lane);
     // ---- dK, dV of this key tile: the first warpgroup writes dK, the second dV
     if (ok && n_it > 0) {
       ok = mbar_wait(smem_u32(&bar_dkv_full), 0, &abort_flag, p.status, kTimeoutTmemFull);
@@ -1123,6 +1116,72 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
   }
 
+  else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C::kRegsDrain));
+    // ------------------------------------------------------------ dQ drain
+    // dQ(it) = dS K sits in the columns that take dP of the next query tile. Each warp reads its 32
+    // query rows (all D columns) into registers, frees the columns, and sends the rows out 32
+    // columns at a time through its staging piece as bulk tensor reductions (fp32 add) into dq_accum.
+    const int wq = warp & 3;
+    const uint32_t dq_addr = tmem_base + C::kDpCol + (static_cast<uint32_t>(wq * 32) << 16);
+    const uint32_t piece = drain_smem + wq * 4096;
+    bool ok = true;
+    bool reads_pending = false;
+#ifdef HB_ATTN_PROFILE
+    const bool prof_lane = warp == 12 && lane == 0;
+#endif
+    HB_PROF_BEGIN(tloop);
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int h = hk * G + it / n_i;
+      const int q0 = (ib + it % n_i) * kTile;
+      HB_PROF_BEGIN(tw);
+      ok = mbar_wait(smem_u32(&bar_dq_full), it & 1, &abort_flag, p.status, kTimeoutTmemFull);
+      ok = __all_sync(0xffffffffu, ok);
+      HB_PROF_END(tw, 12, prof_lane);
+      if (!ok) break;
+      HB_PROF_BEGIN(tl);
+      tc_fence_after();
+      uint32_t v[D / 32][32];
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) tmem_ld_32x32(dq_addr + c * 32, v[c]);
+      tmem_ld_wait();
+      // the tile is in registers: its TMEM columns can take the next dP^T already
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_dq_free));
+      HB_PROF_END(tl, 15, prof_lane);
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        if (reads_pending) {
+          // the piece may only be rewritten once the reduction that reads it has done so
+          HB_PROF_BEGIN(tr);
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          __syncwarp();
+          HB_PROF_END(tr, 13, prof_lane);
+        }
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+          st_shared_v4(piece + lane * 128 + ((static_cast<uint32_t>(g) ^ (lane & 7)) << 4), v[c][4 * g],
+                       v[c][4 * g + 1], v[c][4 * g + 2], v[c][4 * g + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          asm volatile(
+              "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                  reinterpret_cast<uint64_t>(&tm_dq)),
+              "r"(piece), "r"(c * 32), "r"(h), "r"(q0 + wq * 32)
+              : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+        reads_pending = true;
+      }
+    }
+    HB_PROF_END(tloop, 14, prof_lane);
+    // every reduction this lane issued has to land before the CTA's shared memory goes away
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    __syncwarp();
+  }
+
   if (abort_flag) {
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
@@ -1135,6 +1194,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 }
 
 // ================================================================== host side
+#ifdef HB_ATTN_PROFILE
+}  // namespace
+cudaError_t attention_profile_read(unsigned long long* out32, bool reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(out32, hb_attn_prof, sizeof(unsigned long long) * 32);
+  if (e != cudaSuccess || !reset) return e;
+  unsigned long long zeros[32] = {};
+  return cudaMemcpyToSymbol(hb_attn_prof, zeros, sizeof(zeros));
+}
+namespace {
+#endif
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
