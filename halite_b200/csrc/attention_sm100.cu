@@ -528,6 +528,12 @@ struct BwdCfg {
   static constexpr int kThreads = 512;
   // registers per thread after the warpgroups have traded them (512 threads start with 128 each):
   // producer / MMA / allocator warps, the two element-wise warpgroups, the dQ drain warpgroup
+  // How dQ leaves the drain warps. false: through a shared-memory staging piece as TMA reduce-add (whole
+  // 128-byte lines). true: as vector reductions from registers (`red.global.add.v2.f32`, a quad of lanes
+  // per 32-byte sector), which takes the staging round trip out of the shared-memory traffic that bounds
+  // the loop, but measured slower (3.30 against 2.59 ms on 8 x 4096 x 24 / 8 heads x 128): the 64
+  // reductions per thread and query tile hold up the load / store pipe, and step 2's stores behind them.
+  static constexpr bool kDqRed = false;
   static constexpr int kRegsLight = 64, kRegsElem = 144, kRegsDrain = 160;
   static_assert(kRegsLight + 2 * kRegsElem + kRegsDrain == 4 * 128, "the register file must add up");
   static constexpr int kTmemCols = 512;
@@ -658,18 +664,30 @@ __global__ void attn_dq_finish_kernel(const float* __restrict__ acc, __nv_bfloat
 // reduce engine, 14 its loop, 15 TMEM loads.
 #ifdef HB_ATTN_PROFILE
 __device__ unsigned long long hb_attn_prof[32];
+// counters live in registers and reach memory once per CTA and role (an atomic per wait slowed the
+// kernel threefold)
+#define HB_PROF_DECL() long long _pacc[6] = {0, 0, 0, 0, 0, 0}
 #define HB_PROF_BEGIN(t) const long long t = clock64()
-#define HB_PROF_END(t, slot, on) do { if (on) atomicAdd(&hb_attn_prof[slot], static_cast<unsigned long long>(clock64() - (t))); } while (0)
+#define HB_PROF_END(t, k) _pacc[k] += clock64() - (t)
+#define HB_PROF_FLUSH(base, n, on)                                                                   \
+  do {                                                                                                \
+    if (on)                                                                                           \
+      for (int _i = 0; _i < (n); ++_i)                                                                \
+        atomicAdd(&hb_attn_prof[(base) + _i], static_cast<unsigned long long>(_pacc[_i]));            \
+  } while (0)
 #else
+#define HB_PROF_DECL() do {} while (0)
 #define HB_PROF_BEGIN(t) do {} while (0)
-#define HB_PROF_END(t, slot, on) do {} while (0)
+#define HB_PROF_END(t, k) do {} while (0)
+#define HB_PROF_FLUSH(base, n, on) do {} while (0)
 #endif
 
 template <int D, bool kSoftcap>
 __global__ void __launch_bounds__(512, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-                const __grid_constant__ CUtensorMap tm_dq, const float* __restrict__ lse,
+                const __grid_constant__ CUtensorMap tm_dq, float* __restrict__ dq_accum,
+                const float* __restrict__ lse,
                 const float* __restrict__ delta, __nv_bfloat16* __restrict__ dk, long dk_stride,
                 __nv_bfloat16* __restrict__ dv, long dv_stride, const __grid_constant__ AttnParams p) {
   using C = BwdCfg<D>;
@@ -801,6 +819,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     constexpr uint32_t idesc_kk = make_idesc_bf16(kTile, kTile, false, false);   // S^T, dP^T
     constexpr uint32_t idesc_acc = make_idesc_bf16(kTile, D, false, true);       // dV, dK
     constexpr uint32_t idesc_dq = make_idesc_bf16(kTile, D, true, true);         // dQ
+    HB_PROF_DECL();
     bool ok = mbar_wait(smem_u32(&bar_kv_full), 0, &abort_flag, p.status, kTimeoutFull);
     const uint32_t k_lo = desc_lo(k_smem, 0), v_lo = desc_lo(v_smem, 0);
     const uint32_t k_mn_lo = desc_lo(k_smem, C::kChunkBytes), ds_lo = desc_lo(ds_smem, 0),
@@ -809,7 +828,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       HB_PROF_BEGIN(tq);
       if (!mbar_wait(smem_u32(&bar_ring_full[it & 1]), (it >> 1) & 1, &abort_flag, p.status, kTimeoutFull))
         return false;
-      HB_PROF_END(tq, 4, true);
+      HB_PROF_END(tq, 3);
       tc_fence_after();
       const uint32_t q_lo = desc_lo(ring + (it & 1) * C::kTileBytes, 0);
 #pragma unroll
@@ -829,11 +848,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // dP^T = V dO^T (its columns held the previous dQ tile until the drain finished)
       HB_PROF_BEGIN(t1);
       ok = mbar_wait(smem_u32(&bar_ring_full[2]), it & 1, &abort_flag, p.status, kTimeoutFull);
-      HB_PROF_END(t1, 1, true);
+      HB_PROF_END(t1, 0);
       HB_PROF_BEGIN(t2);
       if (ok && it > 0)
         ok = mbar_wait(smem_u32(&bar_dq_free), (it - 1) & 1, &abort_flag, p.status, kTimeoutTmemEmpty);
-      HB_PROF_END(t2, 2, true);
+      HB_PROF_END(t2, 1);
       if (!ok) break;
       tc_fence_after();
       const uint32_t o_lo = desc_lo(o_addr, 0), o_mn_lo = desc_lo(o_addr, C::kChunkBytes);
@@ -847,7 +866,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // dV += P^T dO
       HB_PROF_BEGIN(t3);
       ok = mbar_wait(smem_u32(&bar_p_ready), par, &abort_flag, p.status, kTimeoutTmemEmpty);
-      HB_PROF_END(t3, 3, true);
+      HB_PROF_END(t3, 2);
       if (!ok) break;
       tc_fence_after();
 #pragma unroll
@@ -864,7 +883,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // dK += dS^T Q, dQ = dS K
       HB_PROF_BEGIN(t5);
       ok = mbar_wait(smem_u32(&bar_ds_ready), par, &abort_flag, p.status, kTimeoutTmemEmpty);
-      HB_PROF_END(t5, 5, true);
+      HB_PROF_END(t5, 4);
       if (!ok) break;
       tc_fence_after();
 #pragma unroll
@@ -880,7 +899,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       umma_commit(smem_u32(&bar_dq_full));
       umma_commit(smem_u32(&bar_ring_empty[it & 1]));
     }
-    HB_PROF_END(tloop, 6, true);
+    HB_PROF_END(tloop, 5);
+    HB_PROF_FLUSH(1, 6, true);
 #ifdef HB_ATTN_PROFILE
     atomicAdd(&hb_attn_prof[0], static_cast<unsigned long long>(n_it));
 #endif
@@ -912,29 +932,34 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     float* dlt = lse2 + 64;
     uint32_t pk[32];
     bool ok = true;
-    float pre[4];
-#ifdef HB_ATTN_PROFILE
-    const bool prof_lane = warp == 4 && lane == 0;
-#endif
+    float pre[4], nxt[4];
+    HB_PROF_DECL();
 
-    // lse / delta of this warp's 64 query columns: fetched early into registers, parked in shared
-    // memory right before use
-    auto fetch_vectors = [&](int it) {
+    // lse / delta of this warp's 64 query columns: fetched two query tiles ahead into registers (the
+    // loads compete with the tile loads and the dQ reductions for L2), parked in shared memory
+    // right before use
+    auto fetch_vectors = [&](int it, float (&dst)[4]) {
       const int h = hk * G + it / n_i;
       const int q0 = (ib + it % n_i) * kTile + wg * 64;
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         const int q = q0 + lane + 32 * u;
         const bool live = q < p.total;
-        pre[u] = live ? lse[static_cast<size_t>(h) * p.total + q] * kLog2e : INFINITY;
-        pre[2 + u] = live ? delta[static_cast<size_t>(h) * p.total + q] : 0.f;
+        // plain predicated loads: nothing here may depend on the loaded values, or the warp would sit
+        // on the load's latency right here instead of at the park two tiles later
+        dst[u] = INFINITY;
+        dst[2 + u] = 0.f;
+        if (live) {
+          dst[u] = __ldg(lse + static_cast<size_t>(h) * p.total + q);
+          dst[2 + u] = __ldg(delta + static_cast<size_t>(h) * p.total + q);
+        }
       }
     };
     auto park_vectors = [&]() {
       __syncwarp();                 // every lane is done with the previous tile's values
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
-        lse2[lane + 32 * u] = pre[u];
+        lse2[lane + 32 * u] = pre[u] * kLog2e;
         dlt[lane + 32 * u] = pre[2 + u];
       }
       __syncwarp();
@@ -946,7 +971,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       HB_PROF_BEGIN(tw);
       bool good = mbar_wait(smem_u32(&bar_s_full), it & 1, &abort_flag, p.status, kTimeoutTmemFull);
       good = __all_sync(0xffffffffu, good);
-      HB_PROF_END(tw, 8, prof_lane);
+      HB_PROF_END(tw, 1);
       if (!good) return false;
       HB_PROF_BEGIN(tk);
       tc_fence_after();
@@ -1001,7 +1026,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_p_ready));
-      HB_PROF_END(tk, 9, prof_lane);
+      HB_PROF_END(tk, 2);
       return true;
     };
     // ---- step 2: dS^T = P^T (dP^T - delta) scale, bf16, into shared memory
@@ -1009,7 +1034,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       HB_PROF_BEGIN(tw);
       bool good = mbar_wait(smem_u32(&bar_dp_full), it & 1, &abort_flag, p.status, kTimeoutTmemFull);
       good = __all_sync(0xffffffffu, good);
-      HB_PROF_END(tw, 7, prof_lane);
+      HB_PROF_END(tw, 0);
       if (!good) return false;
       HB_PROF_BEGIN(tk);
       tc_fence_after();
@@ -1052,18 +1077,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       fence_proxy_async_smem();      // the tensor cores read dS^T through the async proxy
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_ds_ready));
-      HB_PROF_END(tk, 10, prof_lane);
+      HB_PROF_END(tk, 3);
       return true;
     };
     if (n_it > 0) {
-      fetch_vectors(0);
+      fetch_vectors(0, pre);
       park_vectors();
+      if (n_it > 1) fetch_vectors(1, pre);
       ok = step1(0);
     }
     HB_PROF_BEGIN(tloop);
     for (int it = 0; it < n_it && ok; ++it) {
       const bool more = it + 1 < n_it;
-      if (more) fetch_vectors(it + 1);
+      if (it + 2 < n_it) fetch_vectors(it + 2, nxt);
       ok = step2(it);
       if (!ok) break;
       if (more) {
@@ -1074,10 +1100,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (!ok) break;
         }
         park_vectors();
+#pragma unroll
+        for (int u = 0; u < 4; ++u) pre[u] = nxt[u];
         ok = step1(it + 1);
       }
     }
-    HB_PROF_END(tloop, 11, prof_lane);
+    HB_PROF_END(tloop, 4);
+    HB_PROF_FLUSH(7, 5, warp == 4 && lane == 0);
     // ---- dK, dV of this key tile: the first warpgroup writes dK, the second dV
     if (ok && n_it > 0) {
       ok = mbar_wait(smem_u32(&bar_dkv_full), 0, &abort_flag, p.status, kTimeoutTmemFull);
@@ -1120,16 +1149,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C::kRegsDrain));
     // ------------------------------------------------------------ dQ drain
     // dQ(it) = dS K sits in the columns that take dP of the next query tile. Each warp reads its 32
-    // query rows (all D columns) into registers, frees the columns, and sends the rows out 32
-    // columns at a time through its staging piece as bulk tensor reductions (fp32 add) into dq_accum.
+    // query rows (all D columns) into registers, frees the columns, and adds the rows into dq_accum:
+    // as vector reductions from registers, or (kDqRed false) 32 columns at a time through its
+    // staging piece as bulk tensor reductions.
     const int wq = warp & 3;
     const uint32_t dq_addr = tmem_base + C::kDpCol + (static_cast<uint32_t>(wq * 32) << 16);
     const uint32_t piece = drain_smem + wq * 4096;
     bool ok = true;
     bool reads_pending = false;
-#ifdef HB_ATTN_PROFILE
-    const bool prof_lane = warp == 12 && lane == 0;
-#endif
+    HB_PROF_DECL();
     HB_PROF_BEGIN(tloop);
     for (int it = 0; it < n_it && ok; ++it) {
       const int h = hk * G + it / n_i;
@@ -1137,46 +1165,78 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       HB_PROF_BEGIN(tw);
       ok = mbar_wait(smem_u32(&bar_dq_full), it & 1, &abort_flag, p.status, kTimeoutTmemFull);
       ok = __all_sync(0xffffffffu, ok);
-      HB_PROF_END(tw, 12, prof_lane);
+      HB_PROF_END(tw, 0);
       if (!ok) break;
       HB_PROF_BEGIN(tl);
       tc_fence_after();
-      uint32_t v[D / 32][32];
+      if constexpr (C::kDqRed) {
+        // rows wq * 32 + {0..15} and + {16..31} of the tile, D columns in blocks of 32
+        uint32_t v[2 * (D / 32)][16];
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) tmem_ld_32x32(dq_addr + c * 32, v[c]);
-      tmem_ld_wait();
-      // the tile is in registers: its TMEM columns can take the next dP^T already
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_dq_free));
-      HB_PROF_END(tl, 15, prof_lane);
+        for (int hh = 0; hh < 2; ++hh)
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        if (reads_pending) {
-          // the piece may only be rewritten once the reduction that reads it has done so
-          HB_PROF_BEGIN(tr);
-          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-          __syncwarp();
-          HB_PROF_END(tr, 13, prof_lane);
-        }
-#pragma unroll
-        for (int g = 0; g < 8; ++g)
-          st_shared_v4(piece + lane * 128 + ((static_cast<uint32_t>(g) ^ (lane & 7)) << 4), v[c][4 * g],
-                       v[c][4 * g + 1], v[c][4 * g + 2], v[c][4 * g + 3]);
-        fence_proxy_async_smem();
+          for (int cg = 0; cg < D / 32; ++cg)
+            tmem_ld_16x256b_x4(dq_addr + (static_cast<uint32_t>(hh * 16) << 16) + cg * 32, v[hh * (D / 32) + cg]);
+        tmem_ld_wait();
+        // the tile is in registers: its TMEM columns can take the next dP^T already
+        tc_fence_before();
         __syncwarp();
-        if (lane == 0) {
-          asm volatile(
-              "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
-                  reinterpret_cast<uint64_t>(&tm_dq)),
-              "r"(piece), "r"(c * 32), "r"(h), "r"(q0 + wq * 32)
-              : "memory");
-          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        if (lane == 0) mbar_arrive(smem_u32(&bar_dq_free));
+        HB_PROF_END(tl, 3);
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int row = q0 + wq * 32 + hh * 16 + half * 8 + (lane >> 2);
+            if (row < p.total) {
+              float* dst = dq_accum + (static_cast<size_t>(row) * p.n_heads + h) * D + 2 * (lane & 3);
+#pragma unroll
+              for (int cg = 0; cg < D / 32; ++cg)
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  red_add_v2_f32(dst + cg * 32 + j * 8, v[hh * (D / 32) + cg][4 * j + 2 * half],
+                                 v[hh * (D / 32) + cg][4 * j + 2 * half + 1]);
+            }
+          }
         }
-        reads_pending = true;
+      } else {
+        uint32_t v[D / 32][32];
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) tmem_ld_32x32(dq_addr + c * 32, v[c]);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_dq_free));
+        HB_PROF_END(tl, 3);
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          if (reads_pending) {
+            // the piece may only be rewritten once the reduction that reads it has done so
+            HB_PROF_BEGIN(tr);
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            __syncwarp();
+            HB_PROF_END(tr, 1);
+          }
+#pragma unroll
+          for (int g = 0; g < 8; ++g)
+            st_shared_v4(piece + lane * 128 + ((static_cast<uint32_t>(g) ^ (lane & 7)) << 4), v[c][4 * g],
+                         v[c][4 * g + 1], v[c][4 * g + 2], v[c][4 * g + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            asm volatile(
+                "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                    reinterpret_cast<uint64_t>(&tm_dq)),
+                "r"(piece), "r"(c * 32), "r"(h), "r"(q0 + wq * 32)
+                : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+          reads_pending = true;
+        }
       }
     }
-    HB_PROF_END(tloop, 14, prof_lane);
+    HB_PROF_END(tloop, 2);
+    HB_PROF_FLUSH(12, 4, warp == 12 && lane == 0);
     // every reduction this lane issued has to land before the CTA's shared memory goes away
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     __syncwarp();
@@ -1352,7 +1412,7 @@ cudaError_t launch_bwd(const AttnArgs& a, const void* o, const void* d_o, const 
   }
   const int nkt = (a.total + kTile - 1) / kTile;
   kern<<<nkt * a.n_kv_heads, C::kThreads, C::kSmemBytes, a.stream>>>(
-      tq, tk, tv, tdo, tdq, lse, delta, static_cast<__nv_bfloat16*>(dk), dk_stride,
+      tq, tk, tv, tdo, tdq, dq_accum, lse, delta, static_cast<__nv_bfloat16*>(dk), dk_stride,
       static_cast<__nv_bfloat16*>(dv), dv_stride, to_params(a));
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
