@@ -184,6 +184,8 @@ def _run(args):
                 _ = float(l.item())
         e2e_ms = te.max_ms()
 
+    from bench import train_config
+
     tokens_per_step = seqs * S * dp
     label = {"llama-3.2-3b": "Llama-3.2-3B FSDP, seq 4096", "llama-3-8b": "Llama-3-8B TP2 x FSDP, seq 8192"}[model_name]
     if rank == 0:
@@ -193,11 +195,10 @@ def _run(args):
             "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic uniform-random tokens, random-init weights", "impl": "reference",
-            "config": {"model": model_name if not args.layers else f"{model_name}-{args.layers}layers-INVALID",
-                       "global_batch": seqs * dp, "seq_len": S, "micro_batches": M,
-                       "parallelism": f"fsdp{world}" if tp == 1 else f"tp{tp} x fsdp{dp}", "loss": f"CrossEntropyLoss(fast={fast})",
-                       "stack": "FSDP2 + torch.compile per block + SDPA + cuBLAS",
-                       "l2": "inputs larger than L2"},
+            "config": train_config(args, world),
+            "arm": {"optimizer": "torch AdamW, clip 1.0", "attention": "SDPA (the reference's `torch` processor)",
+                    "loss": f"CrossEntropyLoss(fast={fast}) on materialised logits",
+                    "stack": "FSDP2 + torch.compile per block + SDPA + cuBLAS"},
             "e2e": {"value": tokens_per_step * K / (e2e_ms / 1e3), "unit": "tokens/s",
                     "ms_per_step": e2e_ms / K, "h2d_bytes_per_step": seqs * (S + 1) * 8,
                     "d2h_bytes_per_step": 4},

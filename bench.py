@@ -119,6 +119,17 @@ def rollout_requests(args, rank, tag, warmup=False):
     return out
 
 
+def train_config(args, world):
+    """`config` of a training record: identical in both arms for the same command line."""
+    tp = args.tp
+    dp = world // tp
+    seqs, S, M = args.seqs_per_gpu, args.seq_len, args.micro_batches
+    return {"model": args.model if not args.layers else f"{args.model}-{args.layers}layers-INVALID",
+            "global_batch": seqs * dp, "seq_len": S, "micro_batches": M,
+            "parallelism": f"fsdp{world}" if tp == 1 else f"tp{tp} x fsdp{dp}",
+            "l2": f"inputs larger than L2 (activations of {seqs * S // M} tokens per pass)"}
+
+
 def rollout_config(args, world):
     return {"model": MODEL_NAME, "requests": args.requests_per_gpu * world, "new_tokens": args.new_tokens,
             "prompt_len": "uniform [128, 1024], 25% share a 512-token prefix", "page_size": 16,
@@ -327,13 +338,11 @@ def run_ours(args):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic uniform-random tokens, random-init weights",
             "impl": "ours",
-            "config": {"model": args.model if not args.layers else f"{args.model}-{args.layers}layers-INVALID",
-                       "global_batch": seqs * dp, "seq_len": S, "micro_batches": M,
-                       "parallelism": f"fsdp{world}" if tp == 1 else f"tp{tp} x fsdp{dp}",
-                       "optimizer": "AdamW fp32 master, clip 1.0",
-                       "l2": f"inputs larger than L2 (activations of {seqs * S // M} tokens per pass)",
-                       "attention": "own tcgen05 kernels (forward + backward) inside the packed-QKV op",
-                       "fsdp_all_gather": gather_mode},
+            # the facts both arms share, under the same keys; what is specific to this arm sits in "arm"
+            "config": train_config(args, world),
+            "arm": {"optimizer": "AdamW fp32 master, clip 1.0",
+                    "attention": "own tcgen05 kernels (forward + backward) inside the packed-QKV op",
+                    "loss": "fused linear + cross entropy in the model", "fsdp_all_gather": gather_mode},
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": e2e_ms / K,
                     "h2d_bytes_per_step": seqs * (S + 1) * 8, "d2h_bytes_per_step": 4},
             "gpu_launches": int(launches),
