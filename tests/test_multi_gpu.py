@@ -14,12 +14,23 @@ pytestmark = [pytest.mark.gpu,
               pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2,
                                  reason="needs at least two GPUs")]
 
+# every rank script takes its world size from the launcher: run them on 2 ranks and, where the box
+# has them, on 4 (uneven last granules, more than one concurrent peer, tensor x data parallel meshes)
+WORLDS = [2, 4]
 
-def test_fused_collective_gemms_on_two_gpus():
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", str(free_port()), os.path.join(ROOT, "tests/ranks/fused_tp_ranks.py")]
-    env = dict(os.environ, PYTHONPATH=ROOT)
-    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+
+def _torchrun(script, world, env_extra=None, timeout=600):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world), "--master-addr",
+           "127.0.0.1", "--master-port", str(free_port()), os.path.join(ROOT, script)]
+    env = dict(os.environ, PYTHONPATH=ROOT, **(env_extra or {}))
+    return subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+
+
+@pytest.mark.parametrize("world", WORLDS)
+def test_fused_collective_gemms_over_peer_memory(world):
+    out = _torchrun("tests/ranks/fused_tp_ranks.py", world)
     assert out.returncode == 0 and "RESULT" in out.stdout, (out.stdout + out.stderr)[-3000:]
 
 
@@ -29,17 +40,14 @@ def test_pynccl_communicator_on_two_gpus():
     assert all("RESULT" in o for o in outs), outs[0][-2000:]
 
 
-def test_fsdp_parameter_gather_carried_by_gemm_launches():
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", str(free_port()), os.path.join(ROOT, "tests/ranks/fsdp_fused_gather_ranks.py")]
-    env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE="0")
-    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+@pytest.mark.parametrize("world", WORLDS)
+def test_fsdp_parameter_gather_carried_by_gemm_launches(world):
+    out = _torchrun("tests/ranks/fsdp_fused_gather_ranks.py", world, {"NCCL_NVLS_ENABLE": "0"})
     assert out.returncode == 0 and "RESULT ok" in out.stdout, (out.stdout + out.stderr)[-3000:]
 
 
-def test_tensor_parallel_training_with_collectives_inside_the_gemms():
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", str(free_port()), os.path.join(ROOT, "tests/ranks/tp_train_gpu.py")]
-    env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE="0")
-    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+@pytest.mark.parametrize("world", WORLDS)
+def test_tensor_parallel_training_with_collectives_inside_the_gemms(world):
+    """tp 2 x (world / 2) sharded data-parallel ranks; with 4 ranks the fused GEMMs run beside FSDP collectives."""
+    out = _torchrun("tests/ranks/tp_train_gpu.py", world, {"NCCL_NVLS_ENABLE": "0", "NCCL_MAX_CTAS": "16"})
     assert out.returncode == 0 and "RESULT ok" in out.stdout, (out.stdout + out.stderr)[-3000:]
