@@ -125,6 +125,11 @@ def _run(args):
         apply_tp(model, mesh2["tp"], None)
         apply_compile(model, None)
         apply_fsdp(model, mesh2["dp"], "bfloat16", "float32", True)
+    else:
+        # one GPU: the reference's parallelize() would apply no sharding and therefore no bf16 mixed
+        # precision; call its own apply_compile and apply_fsdp on the one-rank mesh instead
+        apply_compile(model, None)
+        apply_fsdp(model, mesh["dp"], "bfloat16", "float32", True)
     model.to_empty(device=device)
     model.init_weights(device)
 
@@ -157,7 +162,8 @@ def _run(args):
                 logits = logits.full_tensor()
             loss, _ = criterion(logits, labels)
             del out, logits
-            loss = loss / M
+            if M > 1:
+                loss = loss / M
             loss.backward()
             total = loss.detach() if total is None else total + loss.detach()
         loss = total
