@@ -283,3 +283,25 @@ def test_tensor_parallel_engine_matches_dense_on_two_ranks():
 
     outs = run_ranks(os.path.join(ROOT, "tests/ranks/infer_tp.py"), 2, timeout=600)
     assert all(o.count("TP_OK") == 2 for o in outs), outs[0][-3000:]
+
+
+def test_decode_graphs_are_only_captured_when_attention_runs_the_paged_kernels(zoo):
+    """The plain-PyTorch attention path reads lengths on the host, which a stream capture forbids: the
+    runner must decide from the model whether a decode forward is capturable."""
+    _, eng = build(zoo)
+    runner = eng.model_runner
+    assert runner._graph_for(4) is None                      # CPU: never
+    assert runner._graph_capturable() is False               # fp32 cache and weights here
+    runner._capturable = None
+    runner.kv_cache_dtype = torch.bfloat16
+    for p in runner.model.parameters():
+        p.data = p.data.to(torch.bfloat16)
+    assert runner._graph_capturable() is True                # head_dim 64, bf16 everywhere
+    runner._capturable = None
+    runner.model_config.head_dim = 16
+    assert runner._graph_capturable() is False               # a head size the kernels do not cover
+    runner.model_config.head_dim = 64
+    runner._capturable = None
+    attn = next(m for m in runner.model.modules() if hasattr(m, "softcap"))
+    attn.softcap = 30.0
+    assert runner._graph_capturable() is False               # soft-capped scores run the PyTorch path
